@@ -1,0 +1,226 @@
+// Embedding lookup, residual add + RMSNorm, SiLU·up, rotary positions + cache
+// store.  Each replaces a chain of PyTorch calls in the reference
+// (gllm/model/model.py:175-182, gllm/model/layers/norm.py:15-22,
+// gllm/model/transformer.py:58-75, gllm/model/layers/mlp.py:44-47,
+// gllm/model/layers/attention.py:76-119,156-161).
+//
+// T is the activation / weight-matrix type (float or bf16).  The residual
+// stream, norm weights, norm statistics and rotation angles are always fp32.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+// resid[n, :] = table[tokens[n], :] (upcast to fp32).  A token outside the
+// vocabulary sets a status bit and yields zeros: no fault, the host raises.
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                                 float* __restrict__ resid, int n_tokens, int hidden, int vocab,
+                                 int* __restrict__ status) {
+  const int n = blockIdx.x;
+  if (n >= n_tokens) return;
+  const int tok = tokens[n];
+  const bool ok = tok >= 0 && tok < vocab;
+  if (!ok && threadIdx.x == 0) atomicOr(status, GLLM_STATUS_TOKEN_RANGE);
+  const T* row = table + (size_t)(ok ? tok : 0) * hidden;
+  float* dst = resid + (size_t)n * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? to_float(row[i]) : 0.f;
+}
+
+template <typename T>
+static int embedding_launch(const int* tokens, const T* table, float* resid, int n_tokens, int hidden,
+                            int vocab, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
+  embedding_kernel<T><<<n_tokens, threads, 0, stream>>>(tokens, table, resid, n_tokens, hidden, vocab, status);
+  return gllm_launch_result();
+}
+
+GLLM_API int gllm_embedding_f32(const int* tokens, const float* table, float* resid, int n_tokens,
+                                int hidden, int vocab, int* status, cudaStream_t stream) {
+  return embedding_launch<float>(tokens, table, resid, n_tokens, hidden, vocab, status, stream);
+}
+GLLM_API int gllm_embedding_bf16(const int* tokens, const __nv_bfloat16* table, float* resid, int n_tokens,
+                                 int hidden, int vocab, int* status, cudaStream_t stream) {
+  return embedding_launch<__nv_bfloat16>(tokens, table, resid, n_tokens, hidden, vocab, status, stream);
+}
+
+// ------------------------------------------------------ add + RMSNorm (fused)
+// For output row i (source row r = rows ? rows[i] : i):
+//   x = resid[r] (+ branch[r])            fp32
+//   if (!rows) resid[r] = x               the residual stream moves on
+//   out[i] = x * rsqrt(mean(x^2) + eps) * (w or 1 + w)
+// y = x / sqrt(mean + eps) * w as gllm/model/layers/norm.py:20-22, with the
+// statistic in fp32 whatever T is.  One block per row; the row lives in
+// shared memory between the two passes, so it is read from HBM once.
+template <typename T>
+__global__ void add_rmsnorm_kernel(const T* __restrict__ branch, float* __restrict__ resid,
+                                   const float* __restrict__ weight, T* __restrict__ out,
+                                   const int* __restrict__ rows, int n_rows, int hidden, float eps,
+                                   int unit_offset) {
+  extern __shared__ float row_buf[];  // hidden floats + 32 scratch
+  float* scratch = row_buf + hidden;
+  const int i = blockIdx.x;
+  if (i >= n_rows) return;
+  const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+  float* res = resid + r * hidden;
+  const T* br = branch ? branch + r * hidden : nullptr;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    float x = res[c];
+    if (br) x += to_float(br[c]);
+    row_buf[c] = x;
+    if (br && !rows) res[c] = x;
+    ss += x * x;
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  T* o = out + (size_t)i * hidden;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float w = unit_offset ? 1.0f + weight[c] : weight[c];
+    o[c] = from_float<T>(row_buf[c] * inv * w);
+  }
+}
+
+template <typename T>
+static int add_rmsnorm_launch(const T* branch, float* resid, const float* weight, T* out, const int* rows,
+                              int n_rows, int hidden, float eps, int unit_offset, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  size_t smem = (size_t)(hidden + 32) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  add_rmsnorm_kernel<T><<<n_rows, threads, smem, stream>>>(branch, resid, weight, out, rows, n_rows, hidden, eps,
+                                                         unit_offset);
+  return gllm_launch_result();
+}
+
+GLLM_API int gllm_add_rmsnorm_f32(const float* branch, float* resid, const float* weight, float* out,
+                                  const int* rows, int n_rows, int hidden, float eps, int unit_offset,
+                                  cudaStream_t stream) {
+  return add_rmsnorm_launch<float>(branch, resid, weight, out, rows, n_rows, hidden, eps, unit_offset, stream);
+}
+GLLM_API int gllm_add_rmsnorm_bf16(const __nv_bfloat16* branch, float* resid, const float* weight,
+                                   __nv_bfloat16* out, const int* rows, int n_rows, int hidden, float eps,
+                                   int unit_offset, cudaStream_t stream) {
+  return add_rmsnorm_launch<__nv_bfloat16>(branch, resid, weight, out, rows, n_rows, hidden, eps, unit_offset,
+                                           stream);
+}
+
+// ------------------------------------------------------------------ SiLU · up
+// gate_up is [n, 2*inter] with the gate in the first `inter` columns:
+// out = silu(gate) * up, silu(z) = z / (1 + exp(-z))  (gllm/model/layers/mlp.py:44-47)
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_rows, int inter) {
+  const size_t total = (size_t)n_rows * inter;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = idx / inter, c = idx - r * inter;
+    const float g = to_float(gate_up[r * 2 * inter + c]);
+    const float u = to_float(gate_up[r * 2 * inter + inter + c]);
+    const float s = g / (1.0f + expf(-g));
+    out[idx] = from_float<T>(s * u);
+  }
+}
+
+template <typename T>
+static int silu_mul_launch(const T* gate_up, T* out, int n_rows, int inter, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  const size_t total = (size_t)n_rows * inter;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  silu_mul_kernel<T><<<blocks, 256, 0, stream>>>(gate_up, out, n_rows, inter);
+  return gllm_launch_result();
+}
+GLLM_API int gllm_silu_mul_f32(const float* gate_up, float* out, int n_rows, int inter, cudaStream_t stream) {
+  return silu_mul_launch<float>(gate_up, out, n_rows, inter, stream);
+}
+GLLM_API int gllm_silu_mul_bf16(const __nv_bfloat16* gate_up, __nv_bfloat16* out, int n_rows, int inter,
+                                cudaStream_t stream) {
+  return silu_mul_launch<__nv_bfloat16>(gate_up, out, n_rows, inter, stream);
+}
+
+// ------------------------------------------- rotary positions + cache store
+// qkv is [n, (hq + 2*hkv) * d]: q heads, then k heads, then v heads.
+// For every token: rotate q and k in place (first `rotary_dim` dims of each
+// head; pairs are the two halves (i, i + rotary_dim/2) as
+// gllm/model/layers/attention.py:91-118, or neighbours (2i, 2i+1) when
+// `interleaved`), angle = position * inv_freq[i] in fp32, and store the
+// rotated k and the v into the token's cache slot (post-rotation keys are
+// cached, gllm/model/layers/attention.py:156-161).
+// Cache layer layout: [page][k|v][kv_head][block_size][d].
+// inv_freq == nullptr: no rotation.  slot_mapping == nullptr or slot < 0: no store.
+template <typename T>
+__global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, const int* __restrict__ slot_mapping,
+                                  T* __restrict__ cache, int n_tokens, int hq, int hkv, int d, int rotary_dim,
+                                  int interleaved, int block_size, int num_pages, int* __restrict__ status) {
+  const int n = blockIdx.x;
+  if (n >= n_tokens) return;
+  T* row = qkv + (size_t)n * (hq + 2 * hkv) * d;
+  const int half = rotary_dim / 2;
+  if (inv_freq) {
+    const float pos = (float)positions[n];
+    // one (head, pair) per thread-iteration over q and k heads
+    const int pairs = (hq + hkv) * half;
+    for (int idx = threadIdx.x; idx < pairs; idx += blockDim.x) {
+      const int h = idx / half, i = idx - h * half;
+      const float ang = pos * inv_freq[i];
+      float s, c;
+      sincosf(ang, &s, &c);
+      T* head = row + (size_t)h * d;  // q heads then k heads are contiguous
+      const int i0 = interleaved ? 2 * i : i;
+      const int i1 = interleaved ? 2 * i + 1 : i + half;
+      const float x0 = to_float(head[i0]), x1 = to_float(head[i1]);
+      head[i0] = from_float<T>(x0 * c - x1 * s);
+      head[i1] = from_float<T>(x0 * s + x1 * c);
+    }
+  }
+  if (!slot_mapping) return;
+  const int slot = slot_mapping[n];
+  if (slot < 0) return;
+  const int page = slot / block_size, off = slot - page * block_size;
+  if (page >= num_pages) {
+    if (threadIdx.x == 0) atomicOr(status, GLLM_STATUS_PAGE_RANGE);
+    return;
+  }
+  __syncthreads();  // rotated k is complete
+  const T* k = row + (size_t)hq * d;
+  const T* v = k + (size_t)hkv * d;
+  const size_t page_base = (size_t)page * 2 * hkv * block_size * d;
+  for (int idx = threadIdx.x; idx < hkv * d; idx += blockDim.x) {
+    const int h = idx / d, j = idx - h * d;
+    const size_t o = page_base + ((size_t)h * block_size + off) * d + j;
+    cache[o] = k[idx];
+    cache[o + (size_t)hkv * block_size * d] = v[idx];
+  }
+}
+
+template <typename T>
+static int rope_store_launch(T* qkv, const int* positions, const float* inv_freq, const int* slot_mapping,
+                             T* cache, int n_tokens, int hq, int hkv, int d, int rotary_dim, int interleaved,
+                             int block_size, int num_pages, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
+  int work = max((hq + hkv) * (rotary_dim / 2), hkv * d);
+  int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
+  rope_store_kernel<T><<<n_tokens, threads, 0, stream>>>(qkv, positions, inv_freq, slot_mapping, cache, n_tokens,
+                                                        hq, hkv, d, rotary_dim, interleaved, block_size,
+                                                        num_pages, status);
+  return gllm_launch_result();
+}
+GLLM_API int gllm_rope_store_f32(float* qkv, const int* positions, const float* inv_freq, const int* slot_mapping,
+                                 float* cache, int n_tokens, int hq, int hkv, int d, int rotary_dim,
+                                 int interleaved, int block_size, int num_pages, int* status,
+                                 cudaStream_t stream) {
+  return rope_store_launch<float>(qkv, positions, inv_freq, slot_mapping, cache, n_tokens, hq, hkv, d, rotary_dim,
+                                  interleaved, block_size, num_pages, status, stream);
+}
+GLLM_API int gllm_rope_store_bf16(__nv_bfloat16* qkv, const int* positions, const float* inv_freq,
+                                  const int* slot_mapping, __nv_bfloat16* cache, int n_tokens, int hq, int hkv,
+                                  int d, int rotary_dim, int interleaved, int block_size, int num_pages,
+                                  int* status, cudaStream_t stream) {
+  return rope_store_launch<__nv_bfloat16>(qkv, positions, inv_freq, slot_mapping, cache, n_tokens, hq, hkv, d,
+                                          rotary_dim, interleaved, block_size, num_pages, status, stream);
+}

@@ -1,0 +1,207 @@
+"""The step function: one flat batch in, logits at the wanted places out.
+
+A batch is a list of (request, its next tokens): portions of prompts beside
+single decoded tokens, cut anywhere.  Only the tokens given are run; all that
+came before is read from the cache.  The reference's step is a padded
+``[B, T_q]`` rectangle in which a new request always brings its whole prompt
+(gllm/llm/llm.py:145-308), builds a dense ``[B, T_q, T]`` bias and a gathered
+copy of the context, and computes logits at every position
+(gllm/llm/llm.py:311-340).  Here the batch is flat (no padding rows, no bias,
+no gather), metadata is built in numpy and uploaded in one copy, and logits
+exist only for the rows asked for.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from gllm_b200 import ops
+from gllm_b200.cache.manager import CacheManager
+from gllm_b200.parts.base import GroupView, StepContext
+
+
+@dataclass
+class StepEntry:
+    request_id: object
+    tokens: list[int]
+    # places among ``tokens`` whose logits are wanted (may be empty)
+    want: list[int] = field(default_factory=list)
+
+
+class Workspace:
+    """Named device scratch buffers that kernels share; grown on demand and
+    kept, so steady-state steps allocate nothing."""
+
+    def __init__(self, device):
+        self.device = device
+        self._buffers: dict[str, torch.Tensor] = {}
+
+    def get(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        buf = self._buffers.get(name)
+        if buf is None or buf.numel() < numel or buf.dtype != dtype:
+            buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            self._buffers[name] = buf
+        return buf[:numel]
+
+
+def _align4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class StepRunner:
+    """Owns the staging buffers of the batch metadata and runs steps."""
+
+    def __init__(self, model, cache: CacheManager, max_tokens_per_step: int):
+        self.model = model
+        self.cache = cache
+        self.device = model.device
+        self.dtype = model.dtype
+        self.max_tokens = int(max_tokens_per_step)
+        n_groups = len(cache.groups)
+        cap = _align4(self.max_tokens) * (4 + n_groups) + 4 * _align4(cache.max_batch_size + 1) + 64
+        self._capacity = cap
+        self._pinned = [torch.empty(cap, dtype=torch.int32).pin_memory() if torch.cuda.is_available()
+                        else torch.empty(cap, dtype=torch.int32) for _ in range(2)]
+        self._flip = 0
+        self._meta = torch.empty(cap, dtype=torch.int32, device=self.device)
+        self.workspace = Workspace(self.device)
+        self.mixer_caches = cache.mixer_caches()
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ build
+    def build(self, entries: list[StepEntry]):
+        """Reserve pages, lay the flat batch out on the host and upload it.
+        Returns (tokens, StepContext, logit_rows)."""
+        cache = self.cache
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        seen = set()
+        n_total = 0
+        for e in entries:
+            if e.request_id in seen:
+                raise ValueError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if not e.tokens:
+                raise ValueError(f"request {e.request_id!r} brings no tokens")
+            n_total += len(e.tokens)
+        if n_total > self.max_tokens:
+            raise ValueError(f"step of {n_total} tokens exceeds the limit of {self.max_tokens}")
+        if len(entries) > cache.max_batch_size:
+            raise ValueError("more requests in a step than state slots")
+
+        appended = []
+        slot_maps = {g.index: [] for g in cache.groups}
+        try:
+            for e in entries:
+                if e.request_id not in cache.requests:
+                    cache.add_request(e.request_id)
+                    appended.append((e.request_id, None))
+                before = cache.requests[e.request_id].num_tokens
+                maps = cache.append(e.request_id, len(e.tokens))
+                appended.append((e.request_id, before))
+                for g, m in maps.items():
+                    slot_maps[g].append(m)
+        except Exception:
+            for rid, before in reversed(appended):
+                if before is None:
+                    cache.free_request(rid)
+                else:
+                    cache.rollback(rid, before)
+            raise
+
+        r = len(entries)
+        tokens = np.empty(n_total, dtype=np.int32)
+        positions = np.empty(n_total, dtype=np.int32)
+        token_row = np.empty(n_total, dtype=np.int32)
+        cu_q = np.zeros(r + 1, dtype=np.int32)
+        ctx_lens = np.empty(r, dtype=np.int32)
+        slots = np.empty(r, dtype=np.int32)
+        rows = []
+        q_lens = []
+        off = 0
+        for i, e in enumerate(entries):
+            rc = cache.requests[e.request_id]
+            n = len(e.tokens)
+            tokens[off:off + n] = e.tokens
+            positions[off:off + n] = np.arange(rc.num_tokens, rc.num_tokens + n, dtype=np.int32)
+            token_row[off:off + n] = rc.slot
+            ctx_lens[i] = rc.num_tokens
+            slots[i] = rc.slot
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {e.request_id!r} wants place {w} of {n} tokens")
+                rows.append(off + w)
+            q_lens.append(n)
+            off += n
+            cu_q[i + 1] = off
+        logit_rows = np.asarray(rows, dtype=np.int32)
+
+        # pack everything into one pinned buffer, one copy to the device
+        pinned = self._pinned[self._flip]
+        self._flip ^= 1
+        host = pinned.numpy()
+        cursor = 0
+        views = {}
+
+        def put(name, arr):
+            nonlocal cursor
+            n = arr.size
+            host[cursor:cursor + n] = arr
+            views[name] = (cursor, n)
+            cursor = _align4(cursor + n)
+
+        put("tokens", tokens)
+        put("positions", positions)
+        put("token_row", token_row)
+        put("cu_q", cu_q)
+        put("ctx_lens", ctx_lens)
+        put("slots", slots)
+        put("rows", logit_rows)
+        for g in cache.groups:
+            put(f"slotmap{g.index}", np.concatenate(slot_maps[g.index]))
+        self._meta[:cursor].copy_(pinned[:cursor], non_blocking=True)
+        cache.flush_block_tables()
+
+        def dev(name):
+            start, n = views[name]
+            return self._meta[start:start + n]
+
+        ctx = StepContext(
+            num_tokens=n_total,
+            num_requests=r,
+            dtype=self.dtype,
+            positions=dev("positions"),
+            token_row=dev("token_row"),
+            cu_q=dev("cu_q"),
+            context_lens=dev("ctx_lens"),
+            state_slots=dev("slots"),
+            groups={
+                g.index: GroupView(g.block_size, g.block_table, dev(f"slotmap{g.index}")) for g in cache.groups
+            },
+            q_lens_host=tuple(q_lens),
+            context_lens_host=tuple(int(c) for c in ctx_lens),
+            max_q_len=max(q_lens),
+            max_seq_len=max(int(c) + q for c, q in zip(ctx_lens, q_lens)),
+            workspace=self.workspace,
+        )
+        return dev("tokens"), ctx, dev("rows")
+
+    # -------------------------------------------------------------------- run
+    def run(self, entries: list[StepEntry], check: bool = True) -> torch.Tensor:
+        """Run one step; returns fp32 logits ``[wanted, vocab]`` on the device,
+        in the order of the entries and of their ``want`` lists."""
+        tokens, ctx, rows = self.build(entries)
+        logits = self.model.forward(tokens, ctx, self.mixer_caches, rows)
+        for e in entries:
+            self.cache.commit(e.request_id, len(e.tokens))
+        self.steps_run += 1
+        if check:
+            ops.check_status(self.device)
+        return logits
+
+    def finish(self, request_id) -> None:
+        """The request is over: its pages and its slot are given back."""
+        self.cache.free_request(request_id)

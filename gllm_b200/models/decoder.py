@@ -1,0 +1,109 @@
+"""The generic decoder: builds whatever a ModelSpec describes and runs it.
+
+``forward`` is the model half of the step function: embedding lookup, the
+layer plan, the final norm at the wanted rows only, and the output head in
+fp32.  The reference computes logits at every position and slices afterwards
+(gllm/llm/llm.py:335-340); here the final norm and the head see only the rows
+whose logits were asked for.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from gllm_b200 import ops
+from gllm_b200.models.spec import ModelSpec
+from gllm_b200.parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, build_part
+from gllm_b200.parts.base import Block, MixerCache, Norm, StepContext, TensorExpectation
+
+
+def _build_layer(layer_spec) -> Block:
+    try:
+        block_cls = BLOCKS[layer_spec.block]
+    except KeyError:
+        raise KeyError(f"no block of kind {layer_spec.block!r} is registered; known: {sorted(BLOCKS)}") from None
+    return block_cls(
+        build_part(MIXERS, layer_spec.mixer),
+        build_part(FEED_FORWARDS, layer_spec.feed_forward),
+        build_part(NORMS, layer_spec.mixer_norm),
+        build_part(NORMS, layer_spec.feed_forward_norm),
+    )
+
+
+def expected_tensors_of_spec(spec: ModelSpec) -> dict[str, TensorExpectation]:
+    """Every checkpoint tensor the model will read, in declaration order."""
+    spec.validate()
+    exp: dict[str, TensorExpectation] = {
+        spec.embedding_name: TensorExpectation((spec.vocab_size, spec.hidden_size), "matrix")
+    }
+    for layer_spec in spec.layers:
+        for part in _build_layer(layer_spec).parts():
+            exp.update(part.expected_tensors())
+    exp.update(build_part(NORMS, spec.final_norm).expected_tensors())
+    if spec.head_name is not None:
+        exp[spec.head_name] = TensorExpectation((spec.vocab_size, spec.hidden_size), "matrix")
+    return exp
+
+
+class DecoderModel:
+    """A stack of blocks between an embedding table and an output head."""
+
+    def __init__(self, spec: ModelSpec, dtype: torch.dtype, device: torch.device | str):
+        spec.validate()
+        self.spec = spec
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.layers: list[Block] = [_build_layer(s) for s in spec.layers]
+        self.final_norm: Norm = build_part(NORMS, spec.final_norm)
+        self.embedding: torch.Tensor | None = None
+        self.head: torch.Tensor | None = None
+
+    # ---------------------------------------------------------------- weights
+    def expected_tensors(self) -> dict[str, TensorExpectation]:
+        exp = {self.spec.embedding_name: TensorExpectation((self.spec.vocab_size, self.spec.hidden_size), "matrix")}
+        for block in self.layers:
+            for part in block.parts():
+                exp.update(part.expected_tensors())
+        exp.update(self.final_norm.expected_tensors())
+        if self.spec.head_name is not None:
+            exp[self.spec.head_name] = TensorExpectation((self.spec.vocab_size, self.spec.hidden_size), "matrix")
+        return exp
+
+    def load(self, checkpoint) -> None:
+        checkpoint.validate(self.expected_tensors(), self.spec.ignorable_names)
+        get = checkpoint.getter(self.dtype, self.device)
+        self.embedding = get(self.spec.embedding_name, "matrix")
+        for block in self.layers:
+            for part in block.parts():
+                part.load(get, self.dtype, self.device)
+        self.final_norm.load(get, self.dtype, self.device)
+        self.head = self.embedding if self.spec.head_name is None else get(self.spec.head_name, "matrix")
+
+    # ------------------------------------------------------------------ cache
+    def cache_requirements(self):
+        """Per plan entry: (kv requirement | None, state requirement | None,
+        reads_cache_of | None)."""
+        out = []
+        for entry in self.spec.plan:
+            mixer = self.layers[entry.layer].mixer
+            out.append((mixer.kv_requirement(), mixer.state_requirement(), entry.reads_cache_of))
+        return out
+
+    # ---------------------------------------------------------------- forward
+    def forward(
+        self,
+        tokens: torch.Tensor,
+        ctx: StepContext,
+        caches: list[MixerCache],
+        logit_rows: torch.Tensor,
+        logits_out: torch.Tensor | None = None,
+    ) -> torch.Tensor:
+        """Logits ``[len(logit_rows), vocab]`` fp32 of the flat batch ``tokens``."""
+        resid = ops.embedding(tokens, self.embedding)
+        branch = None
+        for entry_idx, entry in enumerate(self.spec.plan):
+            branch, resid = self.layers[entry.layer].forward(branch, resid, ctx, caches[entry_idx])
+        if logit_rows.numel() == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        final = self.final_norm.forward(branch, resid, self.dtype, rows=logit_rows)
+        return ops.linear(final, self.head, out_dtype=torch.float32, out=logits_out)

@@ -1,0 +1,358 @@
+"""Python entry points of the CUDA kernels.
+
+Every function takes CUDA tensors, checks what the kernel assumes (device,
+dtype, contiguity, sizes it accepts) and launches on the current stream.
+There is no CPU path and no PyTorch fallback: a tensor that is not on a CUDA
+device, or a kernel module that cannot be built, raises.
+
+Naming: ``*_f32`` / ``*_bf16`` symbols are the two instantiations of a kernel
+for the activation and weight-matrix type.  The residual stream, norm weights,
+rotary frequencies, softmax statistics and logits are fp32 in both.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_int64, c_void_p
+
+import torch
+
+from gllm_b200.ops.build import ExtensionError, build_all, load_module
+
+__all__ = [
+    "ExtensionError",
+    "build_all",
+    "embedding",
+    "add_rmsnorm",
+    "silu_mul",
+    "rope_store",
+    "linear",
+    "paged_attention",
+    "status_word",
+    "check_status",
+]
+
+P = c_void_p
+_SIGNATURES = {
+    "elementwise": {
+        "gllm_embedding_{t}": [P, P, P, c_int, c_int, c_int, P, P],
+        "gllm_add_rmsnorm_{t}": [P, P, P, P, P, c_int, c_int, c_float, c_int, P],
+        "gllm_silu_mul_{t}": [P, P, c_int, c_int, P],
+        "gllm_rope_store_{t}": [P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
+    },
+    "gemm_fp32": {
+        "gllm_gemm_f32": [P, P, P, c_int, c_int, c_int, c_int64, c_int64, c_int64, P],
+    },
+    "attention_simt": {
+        "gllm_attention_simt_{t}": [P, c_int64, P, c_int64, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,
+                                    c_int, c_float, c_int, P, P],
+    },
+}
+
+_functions: dict[str, object] = {}
+
+
+def _fn(module: str, name: str):
+    f = _functions.get(name)
+    if f is not None:
+        return f
+    lib = load_module(module)
+    for pattern, argtypes in _SIGNATURES[module].items():
+        for t in ("f32", "bf16"):
+            sym = pattern.format(t=t)
+            if sym in _functions:
+                continue
+            try:
+                func = getattr(lib, sym)
+            except AttributeError:
+                continue
+            func.argtypes = argtypes
+            func.restype = c_int
+            _functions[sym] = func
+    try:
+        return _functions[name]
+    except KeyError:
+        raise ExtensionError(f"kernel module {module!r} exports no symbol {name!r}") from None
+
+
+_cudart_error_string = None
+
+
+def _error_string(code: int) -> str:
+    try:
+        return torch.cuda.cudart().cudaGetErrorString(torch.cuda.cudart().cudaError(code))
+    except Exception:
+        return f"cudaError {code}"
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what}: launch failed: {_error_string(code)} (code {code})")
+
+
+def _suffix(dtype: torch.dtype) -> str:
+    if dtype == torch.float32:
+        return "f32"
+    if dtype == torch.bfloat16:
+        return "bf16"
+    raise TypeError(f"kernels take float32 or bfloat16 activations, not {dtype}")
+
+
+def _cuda(t: torch.Tensor, name: str, dtype: torch.dtype | None = None, contiguous: bool = True) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: this engine has no CPU path")
+    if dtype is not None and t.dtype != dtype:
+        raise TypeError(f"{name} must be {dtype}, is {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+# ------------------------------------------------------------------- status
+_status: dict[int, torch.Tensor] = {}
+
+STATUS_BITS = {
+    1: "a token id outside the vocabulary",
+    2: "a cache page id outside the pool",
+    4: "a bounded wait inside a kernel ran out",
+}
+
+
+def status_word(device: torch.device | int | None = None) -> torch.Tensor:
+    """The device's int32 status word that kernels OR error bits into."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
+    t = _status.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}")
+        _status[idx] = t
+    return t
+
+
+def check_status(device=None) -> None:
+    """Read the status word (a device sync) and raise if a kernel set a bit."""
+    t = status_word(device)
+    value = int(t.item())
+    if value:
+        t.zero_()
+        reasons = [text for bit, text in STATUS_BITS.items() if value & bit] or [f"status {value}"]
+        raise RuntimeError("a kernel reported: " + "; ".join(reasons))
+
+
+# ---------------------------------------------------------------- embedding
+def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 residual rows ``table[tokens]`` (gllm/model/model.py:175-182)."""
+    _cuda(tokens, "tokens", torch.int32)
+    _cuda(table, "table")
+    n, (vocab, hidden) = tokens.numel(), table.shape
+    if out is None:
+        out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    else:
+        _cuda(out, "out", torch.float32)
+    f = _fn("elementwise", f"gllm_embedding_{_suffix(table.dtype)}")
+    _check(f(tokens.data_ptr(), table.data_ptr(), out.data_ptr(), n, hidden, vocab,
+             status_word(table.device).data_ptr(), _stream()), "embedding")
+    return out
+
+
+# ------------------------------------------------------------- add + RMSNorm
+def add_rmsnorm(
+    branch: torch.Tensor | None,
+    resid: torch.Tensor,
+    weight: torch.Tensor,
+    eps: float,
+    out_dtype: torch.dtype,
+    rows: torch.Tensor | None = None,
+    unit_offset: bool = False,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """``resid += branch`` (fp32, in place) then RMSNorm of the sum.
+
+    With ``rows`` only those rows are normed and ``resid`` is left untouched.
+    """
+    _cuda(resid, "resid", torch.float32)
+    _cuda(weight, "weight", torch.float32)
+    hidden = resid.shape[-1]
+    if weight.numel() != hidden:
+        raise ValueError(f"norm weight has {weight.numel()} elements, rows have {hidden}")
+    if branch is not None:
+        _cuda(branch, "branch", out_dtype)
+        if branch.shape != resid.shape:
+            raise ValueError("branch and resid differ in shape")
+    if rows is not None:
+        _cuda(rows, "rows", torch.int32)
+        n_rows = rows.numel()
+    else:
+        n_rows = resid.numel() // hidden
+    if out is None:
+        out = torch.empty((n_rows, hidden), dtype=out_dtype, device=resid.device)
+    else:
+        _cuda(out, "out", out_dtype)
+    f = _fn("elementwise", f"gllm_add_rmsnorm_{_suffix(out_dtype)}")
+    _check(f(_ptr(branch), resid.data_ptr(), weight.data_ptr(), out.data_ptr(), _ptr(rows), n_rows, hidden,
+             float(eps), int(unit_offset), _stream()), "add_rmsnorm")
+    return out
+
+
+# ------------------------------------------------------------------ SiLU·up
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``silu(gate) * up`` of ``[n, 2*inter]`` (gate first)."""
+    _cuda(gate_up, "gate_up")
+    n, two_i = gate_up.shape
+    if two_i % 2:
+        raise ValueError("gate_up must have an even number of columns")
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
+    f = _fn("elementwise", f"gllm_silu_mul_{_suffix(gate_up.dtype)}")
+    _check(f(gate_up.data_ptr(), out.data_ptr(), n, inter, _stream()), "silu_mul")
+    return out
+
+
+# --------------------------------------------------- rotary + cache store
+def rope_store(
+    qkv: torch.Tensor,
+    positions: torch.Tensor,
+    inv_freq: torch.Tensor | None,
+    slot_mapping: torch.Tensor | None,
+    cache_layer: torch.Tensor | None,
+    num_heads: int,
+    num_kv_heads: int,
+    head_dim: int,
+    rotary_dim: int,
+    interleaved: bool = False,
+) -> None:
+    """Rotate q and k of ``qkv`` in place and store k, v into the cache.
+
+    ``cache_layer`` is ``[pages, 2, kv_heads, block_size, head_dim]``.
+    """
+    _cuda(qkv, "qkv")
+    _cuda(positions, "positions", torch.int32)
+    n = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim:
+        raise ValueError("qkv width does not equal (heads + 2*kv_heads) * head_dim")
+    if inv_freq is not None:
+        _cuda(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise ValueError("inv_freq must hold rotary_dim/2 frequencies")
+    block_size = num_pages = 0
+    if slot_mapping is not None:
+        _cuda(slot_mapping, "slot_mapping", torch.int32)
+        _cuda(cache_layer, "cache_layer", qkv.dtype)
+        num_pages, two, hkv, block_size, d = cache_layer.shape
+        if two != 2 or hkv != num_kv_heads or d != head_dim:
+            raise ValueError("cache layer shape does not match the mixer's heads")
+    f = _fn("elementwise", f"gllm_rope_store_{_suffix(qkv.dtype)}")
+    _check(f(qkv.data_ptr(), positions.data_ptr(), _ptr(inv_freq), _ptr(slot_mapping),
+             _ptr(cache_layer) if slot_mapping is not None else None, n, num_heads, num_kv_heads, head_dim,
+             rotary_dim, int(interleaved), block_size, num_pages, status_word(qkv.device).data_ptr(), _stream()),
+           "rope_store")
+
+
+# ------------------------------------------------------------------- linear
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
+           out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ weight.T`` with ``weight`` stored ``[out, in]``
+    (gllm/model/layers/linear.py:20).  fp32 inputs run the FFMA kernel (no
+    tensor-core mode); bf16 inputs run the tensor-core kernels with fp32
+    accumulation."""
+    _cuda(x, "x")
+    _cuda(weight, "weight", x.dtype)
+    m, k = x.shape
+    n, k2 = weight.shape
+    if k != k2:
+        raise ValueError(f"x has {k} columns, weight has {k2}")
+    out_dtype = out_dtype or x.dtype
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    else:
+        _cuda(out, "out", out_dtype)
+    if x.dtype == torch.float32:
+        if out_dtype != torch.float32:
+            raise TypeError("the fp32 product writes fp32")
+        f = _fn("gemm_fp32", "gllm_gemm_f32")
+        _check(f(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, k, k, n, _stream()), "gemm_f32")
+        return out
+    from gllm_b200.ops import gemm_bf16
+
+    return gemm_bf16.linear_bf16(x, weight, out)
+
+
+# ---------------------------------------------------------------- attention
+def paged_attention_simt(
+    q: torch.Tensor,
+    q_stride: int,
+    cache_layer: torch.Tensor,
+    block_table: torch.Tensor,
+    positions: torch.Tensor,
+    token_row: torch.Tensor,
+    num_heads: int,
+    scale: float,
+    window: int,
+    out: torch.Tensor,
+) -> torch.Tensor:
+    num_pages, _, hkv, block_size, d = cache_layer.shape
+    n = positions.numel()
+    f = _fn("attention_simt", f"gllm_attention_simt_{_suffix(q.dtype)}")
+    _check(f(q.data_ptr(), q_stride, out.data_ptr(), out.shape[1], cache_layer.data_ptr(), block_table.data_ptr(),
+             block_table.stride(0), positions.data_ptr(), token_row.data_ptr(), n, num_heads, hkv, d, block_size,
+             num_pages, float(scale), int(window), status_word(q.device).data_ptr(), _stream()), "attention_simt")
+    return out
+
+
+def paged_attention(
+    qkv: torch.Tensor,
+    cache_layer: torch.Tensor,
+    block_table: torch.Tensor,
+    positions: torch.Tensor,
+    token_row: torch.Tensor,
+    num_heads: int,
+    scale: float,
+    window: int | None = None,
+    batch=None,
+    out: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """Causal attention of every token of the batch over its request's cache.
+
+    ``qkv`` is ``[n, (heads + 2*kv_heads) * head_dim]`` with rotated queries in
+    its first ``heads * head_dim`` columns; the keys and values of the batch's
+    own tokens are already in ``cache_layer``.  ``token_row[i]`` is the row of
+    ``block_table`` that token ``i``'s request uses.  ``batch`` optionally
+    carries per-request metadata that the tensor-core kernels need.
+    """
+    _cuda(qkv, "qkv")
+    _cuda(cache_layer, "cache_layer", qkv.dtype)
+    _cuda(block_table, "block_table", torch.int32, contiguous=False)
+    _cuda(positions, "positions", torch.int32)
+    _cuda(token_row, "token_row", torch.int32)
+    num_pages, two, hkv, block_size, d = cache_layer.shape
+    if two != 2:
+        raise ValueError("cache layer must be [pages, 2, kv_heads, block_size, head_dim]")
+    if d % 16 or d > 256:
+        raise ValueError(f"head_dim {d} is not supported: it must be a multiple of 16 up to 256")
+    if num_heads % hkv:
+        raise ValueError("the number of query heads must be a multiple of the number of kv heads")
+    n = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * hkv) * d:
+        raise ValueError("qkv width does not equal (heads + 2*kv_heads) * head_dim")
+    if block_table.stride(1) != 1:
+        raise ValueError("block_table rows must be contiguous")
+    if out is None:
+        out = torch.empty((n, num_heads * d), dtype=qkv.dtype, device=qkv.device)
+    win = int(window) if window else 0
+    if qkv.dtype == torch.bfloat16:
+        from gllm_b200.ops import attention_bf16
+
+        if attention_bf16.supports(d, block_size) and batch is not None:
+            return attention_bf16.paged_attention_bf16(qkv, cache_layer, block_table, positions, token_row,
+                                                       num_heads, scale, win, batch, out)
+    return paged_attention_simt(qkv, qkv.shape[1], cache_layer, block_table, positions, token_row, num_heads,
+                                scale, win, out)

@@ -1,0 +1,21 @@
+"""Pre-norm arrangement: ``x += mixer(norm(x)); x += feed_forward(norm(x))``.
+
+The reference defers each layer's last residual add to the next layer
+(gllm/model/transformer.py:58-78): a layer receives the previous feed-forward
+output and the residual, adds them, and returns its own feed-forward output
+un-added.  The same protocol is kept here because it lets every add fuse into
+the norm kernel that follows it.
+"""
+
+from __future__ import annotations
+
+from gllm_b200.parts.base import Block, register_block
+
+
+@register_block("prenorm")
+class PreNormBlock(Block):
+    def forward(self, branch, resid, ctx, cache):
+        x = self.mixer_norm.forward(branch, resid, ctx.dtype)
+        mixed = self.mixer.forward(x, ctx, cache)
+        x = self.feed_forward_norm.forward(mixed, resid, ctx.dtype)
+        return self.feed_forward.forward(x, ctx), resid
