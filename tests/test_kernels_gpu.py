@@ -1,0 +1,202 @@
+"""Each kernel alone against a plain PyTorch fp32/fp64 restatement of the same
+operation, at sizes other than the tiny models' and the 1B model's."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from gllm_b200 import ops as _ops
+
+    return _ops
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(ops, dtype):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(389, 72, generator=g).to(dtype).cuda()
+    tokens = torch.randint(0, 389, (57,), generator=g).int().cuda()
+    out = ops.embedding(tokens, table)
+    assert out.dtype == torch.float32
+    torch.testing.assert_close(out, table[tokens.long()].float(), rtol=0, atol=0)
+    ops.check_status()
+    bad = tokens.clone()
+    bad[3] = 389
+    ops.embedding(bad, table)
+    with pytest.raises(RuntimeError, match="token id"):
+        ops.check_status()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [72, 96, 2048, 2880])
+def test_add_rmsnorm(ops, dtype, hidden):
+    g = torch.Generator().manual_seed(1)
+    n = 19
+    resid = torch.randn(n, hidden, generator=g).cuda()
+    branch = torch.randn(n, hidden, generator=g).to(dtype).cuda()
+    w = (1 + 0.1 * torch.randn(hidden, generator=g)).cuda()
+    eps = 3e-5
+    x = resid.double() + branch.double()
+    want = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w.double()
+    r = resid.clone()
+    got = ops.add_rmsnorm(branch, r, w, eps, dtype)
+    torch.testing.assert_close(r.double(), x, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(got.double(), want, **tol(dtype))
+    # rows: gather, residual untouched, no branch
+    rows = torch.tensor([4, 0, 18], dtype=torch.int32).cuda()
+    r2 = resid.clone()
+    got = ops.add_rmsnorm(None, r2, w, eps, dtype, rows=rows)
+    x2 = resid.double()[rows.long()]
+    want2 = x2 / torch.sqrt((x2 * x2).mean(-1, keepdim=True) + eps) * w.double()
+    torch.testing.assert_close(got.double(), want2, **tol(dtype))
+    torch.testing.assert_close(r2, resid, rtol=0, atol=0)
+    # unit offset: y = x_hat * (1 + w)
+    got = ops.add_rmsnorm(None, resid.clone(), w - 1, eps, dtype, unit_offset=True)
+    x3 = resid.double()
+    want3 = x3 / torch.sqrt((x3 * x3).mean(-1, keepdim=True) + eps) * w.double()
+    torch.testing.assert_close(got.double(), want3, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(ops, dtype):
+    g = torch.Generator().manual_seed(2)
+    gu = (3 * torch.randn(13, 2 * 104, generator=g)).to(dtype).cuda()
+    got = ops.silu_mul(gu)
+    a, b = gu[:, :104].double(), gu[:, 104:].double()
+    torch.testing.assert_close(got.double(), a * torch.sigmoid(a) * b, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("hq,hkv,d,rot", [(5, 5, 16, 16), (6, 2, 48, 32), (8, 1, 128, 128)])
+def test_rope_store(ops, dtype, interleaved, hq, hkv, d, rot):
+    g = torch.Generator().manual_seed(3)
+    n, bs, pages = 23, 8, 9
+    qkv = torch.randn(n, (hq + 2 * hkv) * d, generator=g).to(dtype).cuda()
+    positions = torch.randint(0, 5000, (n,), generator=g).int().cuda()
+    inv_freq = (10000.0 ** (-torch.arange(rot // 2).double() * 2 / rot)).float().cuda()
+    slots = torch.randperm(pages * bs, generator=g)[:n].int()
+    slots[5] = -1
+    slots = slots.cuda()
+    cache = torch.full((pages, 2, hkv, bs, d), float("nan")).to(dtype).cuda()
+    before = qkv.clone()
+    ops.rope_store(qkv, positions, inv_freq, slots, cache, hq, hkv, d, rot, interleaved)
+    ops.check_status()
+    x = before.double().view(n, hq + 2 * hkv, d)
+    ang = (positions.float()[:, None] * inv_freq[None]).double()
+    c, s = ang.cos()[:, None], ang.sin()[:, None]
+    want = x.clone()
+    rot_part = x[:, : hq + hkv, :rot]
+    if interleaved:
+        x1, x2 = rot_part[..., 0::2], rot_part[..., 1::2]
+        o = torch.stack([x1 * c - x2 * s, x1 * s + x2 * c], -1).flatten(-2)
+    else:
+        x1, x2 = rot_part[..., : rot // 2], rot_part[..., rot // 2:]
+        o = torch.cat([x1 * c - x2 * s, x1 * s + x2 * c], -1)
+    want[:, : hq + hkv, :rot] = o
+    got = qkv.double().view(n, hq + 2 * hkv, d)
+    torch.testing.assert_close(got, want, **tol(dtype))
+    # the cache holds exactly what the activations hold, and nothing else was touched
+    seen = torch.zeros(pages, bs, dtype=torch.bool)
+    for t in range(n):
+        sl = int(slots[t])
+        if sl < 0:
+            continue
+        p, off = divmod(sl, bs)
+        seen[p, off] = True
+        assert torch.equal(cache[p, 0, :, off], qkv.view(n, -1, d)[t, hq:hq + hkv])
+        assert torch.equal(cache[p, 1, :, off], qkv.view(n, -1, d)[t, hq + hkv:])
+    untouched = cache.float().isnan().all(dim=(1, 2, 4)).cpu()
+    assert torch.equal(untouched, ~seen)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 311, 72), (7, 96, 160), (65, 130, 100), (200, 384, 96), (33, 1000, 515)])
+def test_gemm_f32(ops, m, n, k):
+    g = torch.Generator().manual_seed(4)
+    a = torch.randn(m, k, generator=g).cuda()
+    b = torch.randn(n, k, generator=g).cuda()
+    got = ops.linear(a, b)
+    want = a.double() @ b.double().T
+    torch.testing.assert_close(got.double(), want, rtol=1e-5, atol=1e-4)
+    # a row's result does not depend on the rest of the batch: bitwise
+    alone = ops.linear(a[m // 2:m // 2 + 1].contiguous(), b)
+    assert torch.equal(alone[0], got[m // 2])
+
+
+def _paged_case(g, dtype, lens, hq, hkv, d, bs, q_counts):
+    """Requests with ``lens`` cached tokens; the last ``q_counts`` of each are
+    the batch's queries.  Pages are scattered through a NaN-poisoned pool."""
+    total_pages = sum(-(-n // bs) for n in lens) + 3
+    perm = torch.randperm(total_pages, generator=g).tolist()
+    pool = torch.full((total_pages, 2, hkv, bs, d), float("nan")).to(dtype)
+    max_blocks = max(-(-n // bs) for n in lens) + 1
+    table = torch.full((len(lens) + 2, max_blocks), -1, dtype=torch.int32)
+    ks, vs, qs, pos, rows = [], [], [], [], []
+    for r, (n, nq) in enumerate(zip(lens, q_counts)):
+        k = torch.randn(n, hkv, d, generator=g).to(dtype)
+        v = torch.randn(n, hkv, d, generator=g).to(dtype)
+        q = torch.randn(nq, hq, d, generator=g).to(dtype)
+        # make attention peaky so that a single missed key shows: one far key per query head
+        k[0] *= 3
+        k[n // 2] *= 3
+        row = r + 1
+        for b in range(-(-n // bs)):
+            page = perm.pop()
+            table[row, b] = page
+            chunk = slice(b * bs, min(n, (b + 1) * bs))
+            m = chunk.stop - chunk.start
+            pool[page, 0, :, :m] = k[chunk].transpose(0, 1)
+            pool[page, 1, :, :m] = v[chunk].transpose(0, 1)
+        ks.append(k); vs.append(v); qs.append(q)
+        pos += list(range(n - nq, n))
+        rows += [row] * nq
+    return pool, table, ks, vs, qs, torch.tensor(pos, dtype=torch.int32), torch.tensor(rows, dtype=torch.int32)
+
+
+def _plain_attn(q, k, v, qpos, window, scale):
+    hq, hkv = q.shape[1], k.shape[1]
+    k = k.double().repeat_interleave(hq // hkv, 1)
+    v = v.double().repeat_interleave(hq // hkv, 1)
+    s = torch.einsum("qhd,khd->hqk", q.double(), k) * scale
+    kp = torch.arange(k.shape[0])[None, :]
+    hide = kp > qpos[:, None]
+    if window:
+        hide = hide | (kp <= qpos[:, None] - window)
+    s = s.masked_fill(hide[None], float("-inf"))
+    return torch.einsum("hqk,khd->qhd", s.softmax(-1), v)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,bs,window", [
+    (4, 2, 16, 4, None), (3, 1, 32, 8, None), (5, 5, 48, 16, 24), (8, 2, 64, 16, None), (6, 3, 128, 32, 100),
+    (2, 1, 256, 16, None),
+])
+def test_attention_simt(ops, dtype, hq, hkv, d, bs, window):
+    g = torch.Generator().manual_seed(5)
+    lens, q_counts = [1, 37, 130, 300, 64], [1, 37, 1, 45, 2]
+    pool, table, ks, vs, qs, pos, rows = _paged_case(g, dtype, lens, hq, hkv, d, bs, q_counts)
+    n = pos.numel()
+    qkv = torch.zeros(n, (hq + 2 * hkv) * d, dtype=dtype)
+    qkv[:, : hq * d] = torch.cat(qs).reshape(n, hq * d)
+    scale = 1.0 / math.sqrt(d)
+    out = ops.paged_attention(qkv.cuda(), pool.cuda(), table.cuda(), pos.cuda(), rows.cuda(), hq, scale, window=window)
+    ops.check_status()
+    off = 0
+    for r, nq in enumerate(q_counts):
+        qpos = pos[off:off + nq].long()
+        want = _plain_attn(qs[r], ks[r], vs[r], qpos, window, scale)
+        got = out[off:off + nq].double().cpu().view(nq, hq, d)
+        assert not got.isnan().any()
+        torch.testing.assert_close(got, want, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else tol(dtype)))
+        off += nq
