@@ -1,0 +1,368 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine on one B200: decode tokens per second at the
+Llama 3.2 1B sizes with random bf16 weights (batch 8, 2,048 cached tokens per
+request, max_seq_len 4096, block_size 16), plus a 2,048-token prefill, decode
+at batch 1 and 64, the end-to-end figure through ``LLMEngine`` and the decode
+step's roofline fraction.  Prints ONE JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+A "step" is one decode step of the whole batch (forward + greedy sampling).
+``value`` is timed on the device with CUDA events around K steps; ``e2e`` is
+wall-clock around K ``LLMEngine.step()`` calls, each of which copies the step's
+metadata from pinned host memory and reads the sampled tokens back.  The model
+(2.47 GB of weights) is larger than the 126 MB L2, so every step streams its
+inputs from HBM; no explicit L2 flush is used.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def load_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(path):
+        try:
+            with open(path) as f:
+                raw = json.load(f)
+            peaks = dict(FALLBACK_PEAKS)
+            for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+                if k in raw:
+                    peaks[k] = float(raw[k])
+            peaks["source"] = "measured"
+            return peaks
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int = 0):
+        self.device_index = device_index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.device_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {
+            "sm_mhz": sm[len(sm) // 2] if sm else None,
+            "sm_max_mhz": max(mx) if mx else None,
+            "reasons": sorted(reasons),
+            "samples": len(sm),
+        }
+
+
+def make_model_folder(tmp: str, num_layers: int | None) -> str:
+    from gllm_b200.config import load_config
+    from gllm_b200.config.presets import load_preset
+    from gllm_b200.weights import write_random_model
+
+    raw = load_preset("llama-3.2-1b")
+    if num_layers is not None:
+        raw["num_hidden_layers"] = num_layers
+    folder = os.path.join(tmp, "llama-3.2-1b-random")
+    write_random_model(folder, load_config(raw), seed=0, std=0.02)
+    return folder
+
+
+def weight_bytes(engine) -> int:
+    """Bytes of every weight a decode step reads once (the embedding table only
+    through the tied head, or the untied head)."""
+    total = 0
+    seen = set()
+    model = engine.model
+    tensors = [model.head]
+    for block in model.layers:
+        tensors += [block.mixer.w_qkv, block.mixer.w_o, block.feed_forward.w_gate_up, block.feed_forward.w_down,
+                    block.mixer_norm.weight, block.feed_forward_norm.weight]
+    tensors.append(model.final_norm.weight)
+    for t in tensors:
+        if t.data_ptr() not in seen:
+            seen.add(t.data_ptr())
+            total += t.numel() * t.element_size()
+    return total
+
+
+def prefill_flops(cfg, t: int) -> float:
+    """Flops of one whole prompt of ``t`` tokens with logits at the last row."""
+    h, i, d = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim
+    hq, hkv, layers, v = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.num_hidden_layers, cfg.vocab_size
+    per_token = layers * (h * (hq + 2 * hkv) * d + hq * d * h + 3 * h * i)
+    gemm = 2.0 * t * per_token
+    attn = layers * 4.0 * d * hq * t * (t + 1) / 2
+    head = 2.0 * h * v
+    return gemm + attn + head
+
+
+def fill_engine(engine, batch: int, context: int, seed: int = 0):
+    """Admit ``batch`` requests of ``context`` random prompt tokens and run steps
+    until every one of them is decoding."""
+    import torch
+
+    from gllm_b200 import GenerationRequest
+
+    g = torch.Generator().manual_seed(seed)
+    vocab = engine.config.vocab_size
+    states = []
+    for b in range(batch):
+        req = GenerationRequest(
+            prompt_token_ids=torch.randint(0, vocab, (context,), generator=g).tolist(),
+            max_new_tokens=engine.max_seq_len - context, temperature=0.0, ignore_eos=True,
+        )
+        st = engine._make_state(req)
+        engine.scheduler.add(st)
+        states.append(st)
+    while any(s.num_computed < len(s.prompt_token_ids) for s in states):
+        engine.step()
+    return states
+
+
+def drain(engine, states):
+    for s in states:
+        engine.scheduler.abort(s.id)
+
+
+def time_decode(engine, batch: int, context: int, steps: int, warmup: int):
+    """Returns (device ms per step, wall ms per step, launches per step, h2d, d2h)."""
+    import torch
+
+    from gllm_b200 import ops
+
+    states = fill_engine(engine, batch, context)
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    # device-timed
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = ops.launch_count
+    start.record()
+    for _ in range(steps):
+        engine.step()
+    end.record()
+    torch.cuda.synchronize()
+    dev_ms = start.elapsed_time(end) / steps
+    launches = (ops.launch_count - launches0) / steps
+    # end to end (wall clock around the public step call, host tokens in and out)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    torch.cuda.synchronize()
+    wall_ms = (time.perf_counter() - t0) * 1000 / steps
+    h2d = engine.runner.last_h2d_bytes
+    d2h = batch * 4 + 4
+    drain(engine, states)
+    return dev_ms, wall_ms, launches, h2d, d2h
+
+
+def time_prefill(engine, tokens: int, repeats: int, warmup: int):
+    import torch
+
+    from gllm_b200 import GenerationRequest
+
+    g = torch.Generator().manual_seed(1)
+    vocab = engine.config.vocab_size
+    times = []
+    for it in range(warmup + repeats):
+        req = GenerationRequest(prompt_token_ids=torch.randint(0, vocab, (tokens,), generator=g).tolist(),
+                                max_new_tokens=1, temperature=0.0, ignore_eos=True)
+        st = engine._make_state(req)
+        engine.scheduler.add(st)
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.step()
+        end.record()
+        torch.cuda.synchronize()
+        assert st.is_finished, "the prefill step did not finish the one-token request"
+        if it >= warmup:
+            times.append(start.elapsed_time(end))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    from gllm_b200 import GeneratorParams, LLMEngine
+
+    peaks = load_peaks()
+    context, max_seq_len, block_size, prefill_tokens = 2048, 4096, 16, 2048
+    full_layers = 16
+    layers = args.layers or full_layers
+    tmp = tempfile.mkdtemp(prefix="gllm_b200_bench_")
+    try:
+        folder = make_model_folder(tmp, layers if layers != full_layers else None)
+        params = GeneratorParams(block_size=block_size, max_batch_size=64, max_seq_len=max_seq_len,
+                                 model_dtype="bfloat16", max_num_batched_tokens=8192, prefill_chunk=2048)
+        engine = LLMEngine(folder, params, device="cuda:0")
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    cfg = engine.config
+    wbytes = weight_bytes(engine)
+    kv_per_token = engine.cache.bytes_per_token()
+
+    points = {}
+    for b in (1, 64):
+        dev_ms, _, _, _, _ = time_decode(engine, b, context, max(8, args.steps // 4), args.warmup)
+        points[f"decode_b{b}"] = round(b * 1000.0 / dev_ms, 1)
+
+    prefill_ms = time_prefill(engine, prefill_tokens, repeats=5, warmup=max(3, args.warmup))
+    pf_flops = prefill_flops(cfg, prefill_tokens)
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    batch = 8
+    dev_ms, wall_ms, launches, h2d, d2h = time_decode(engine, batch, context, args.steps, args.warmup)
+    clocks = sampler.stop()
+
+    step_bytes = wbytes + batch * (context + args.warmup + args.steps // 2) * kv_per_token
+    achieved = step_bytes / (dev_ms * 1e-3) / 1e9
+    value = batch * 1000.0 / dev_ms
+    record = {
+        "metric": "decode tok/s at batch 8 (Llama 3.2 1B sizes, random bf16 weights, 2,048 cached tokens)",
+        "value": round(value, 1),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(dev_ms, 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic: uniform random token ids, random N(0,0.02) weights (seed 0)",
+        "config": {
+            "model": "llama-3.2-1b sizes",
+            "layers": cfg.num_hidden_layers,
+            "layers_of_full_model": full_layers,
+            "hidden": cfg.hidden_size,
+            "heads": cfg.num_attention_heads,
+            "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim,
+            "intermediate": cfg.intermediate_size,
+            "vocab": cfg.vocab_size,
+            "global_batch": batch,
+            "seq_len": context,
+            "max_seq_len": max_seq_len,
+            "block_size": block_size,
+            "prefill_tokens": prefill_tokens,
+            "parallelism": "single GPU",
+            "l2": "inputs larger than L2 (2.47 GB of weights per step)",
+            "sampling": "greedy, inside the step",
+            "peaks": peaks["source"],
+        },
+        "e2e": {
+            "value": round(batch * 1000.0 / wall_ms, 1),
+            "unit": "tokens/s",
+            "h2d_bytes_per_step": int(h2d),
+            "d2h_bytes_per_step": int(d2h),
+        },
+        "gpu_launches": int(round(launches * args.steps)),
+        "clocks": clocks,
+        "prefill": {
+            "value": round(prefill_tokens * 1000.0 / prefill_ms, 1),
+            "tokens": prefill_tokens,
+            "ms": round(prefill_ms, 4),
+            "frac": round(pf_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
+        },
+        "roofline": {
+            "bound": "hbm",
+            "achieved": round(achieved, 1),
+            "peak": peaks["hbm_gbs"],
+            "unit": "GB/s",
+            "frac": round(achieved / peaks["hbm_gbs"], 4),
+        },
+        "points": points,
+    }
+    return record
+
+
+def run_reference(args) -> dict:
+    return {
+        "impl": "reference",
+        "unavailable": (
+            "pip install of the reference into baseline/_ref installs no modules (its setup.py uses find_packages() "
+            "and the tree has no __init__.py), and its engine downloads a gated checkpoint from the hub at construction"
+        ),
+    }
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the full model (named in config)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps(run_reference(args)))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU only: this engine does not run on {args.gpus} GPUs")
+        return 2
+    args.warmup = max(3, args.warmup)
+    print(json.dumps(run_ours(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

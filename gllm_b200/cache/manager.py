@@ -252,8 +252,10 @@ class CacheManager:
                 group.dirty_rows.add(rc.slot)
 
     # ------------------------------------------------------------ device side
-    def flush_block_tables(self) -> None:
-        """Copy the rows that changed since the last flush to the device."""
+    def flush_block_tables(self) -> int:
+        """Copy the rows that changed since the last flush to the device;
+        returns the bytes copied."""
+        copied = 0
         for group in self.groups:
             if not group.dirty_rows:
                 continue
@@ -262,9 +264,12 @@ class CacheManager:
             host = torch.from_numpy(group.block_table_host)
             if len(rows) > 8:
                 group.block_table.copy_(host, non_blocking=False)
+                copied += host.numel() * 4
             else:
                 for r in rows:
                     group.block_table[r].copy_(host[r], non_blocking=False)
+                    copied += host.shape[1] * 4
+        return copied
 
     def mixer_caches(self) -> list[MixerCache]:
         """One MixerCache per plan entry."""

@@ -1,0 +1,272 @@
+"""The Python entry point: ``LLMEngine``.
+
+Same surface as the reference (gllm/engine/llm_engine.py:13-205):
+``LLMEngine(hf_model, gen_params, device, local_cache_dir)``,
+``generate(list[GenerationRequest]) -> list[GenerationResult]``,
+``enqueue_request(req) -> asyncio.Future``, ``run()``, ``stop()``.
+``hf_model`` is a model folder (config.json + safetensors, optionally
+tokenizer.json); nothing is downloaded.  Underneath are this engine's own
+scheduler (chunked prefill, continuous batching, preemption), step function,
+cache manager, sampler and kernels.
+
+The reference's ``run()`` cannot start (it passes ``block=`` to a function
+whose parameter is ``blocking``, gllm/engine/llm_engine.py:35-38,162) and sets
+each future twice (:141,178); here ``run()`` is the same loop done right:
+futures are resolved once, on their own event loop's thread.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import itertools
+import os
+import queue
+from abc import ABC, abstractmethod
+
+import torch
+
+from gllm_b200 import ops
+from gllm_b200.cache.manager import CacheManager
+from gllm_b200.config.generator_params import GeneratorParams
+from gllm_b200.engine.request import (
+    GenerationRequest,
+    GenerationResult,
+    RequestState,
+    TokenLogProbs,
+)
+from gllm_b200.engine.scheduler import ScheduledStep, Scheduler
+from gllm_b200.engine.step import StepEntry, StepRunner
+from gllm_b200.models.loading import load_model
+from gllm_b200.sampling.sampler import Sampler, SamplingParams
+
+
+class LLMEngineBase(ABC):
+    """gllm/engine/llm_engine_base.py:26-30."""
+
+    @abstractmethod
+    def generate(self, reqs: list[GenerationRequest]) -> list[GenerationResult]:
+        ...
+
+
+class LLMEngine(LLMEngineBase):
+    def __init__(
+        self,
+        hf_model: str,
+        gen_params: GeneratorParams,
+        device: str = "cuda",
+        local_cache_dir: str | None = None,
+    ):
+        if not torch.cuda.is_available():
+            raise RuntimeError("LLMEngine needs a CUDA device: this engine has no CPU path")
+        if not os.path.isdir(hf_model):
+            raise FileNotFoundError(
+                f"{hf_model!r} is not a model folder (config.json + model.safetensors); nothing is downloaded"
+            )
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise RuntimeError("LLMEngine runs on a CUDA device only")
+        if dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        self.device = dev
+        self.gen_params = gen_params
+        self.alive = False
+        self.config, self.model = load_model(hf_model, gen_params.model_dtype, dev)
+        self.cache = CacheManager(
+            self.model.cache_requirements(),
+            block_size=gen_params.block_size,
+            num_blocks=gen_params.resolved_num_blocks(),
+            max_batch_size=gen_params.max_batch_size,
+            max_seq_len=gen_params.max_seq_len,
+            dtype=self.model.dtype,
+            device=dev,
+        )
+        self.runner = StepRunner(self.model, self.cache, gen_params.max_num_batched_tokens)
+        self.scheduler = Scheduler(gen_params, self.cache)
+        self.sampler = Sampler(dev)
+        self.request_queue: queue.Queue = queue.Queue()
+        self._ids = itertools.count()
+        self.tokenizer = None
+        tok_path = os.path.join(hf_model, "tokenizer.json")
+        if os.path.isfile(tok_path):
+            from tokenizers import Tokenizer
+
+            self.tokenizer = Tokenizer.from_file(tok_path)
+        self.counters = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
+
+    # ------------------------------------------------------------- properties
+    @property
+    def eos_token_ids(self) -> list[int]:
+        return list(self.config.eos_token_ids)
+
+    @property
+    def max_batch_size(self) -> int:
+        return self.gen_params.max_batch_size
+
+    @property
+    def max_seq_len(self) -> int:
+        return self.gen_params.max_seq_len
+
+    # -------------------------------------------------------------- tokenizer
+    def tokenize(self, text: str, add_special_tokens: bool = True) -> list[int]:
+        if self.tokenizer is None:
+            raise RuntimeError("the model folder has no tokenizer.json: give prompt_token_ids instead of prompt")
+        return self.tokenizer.encode(text, add_special_tokens=add_special_tokens).ids
+
+    def detokenize(self, token_ids: list[int]) -> str:
+        if self.tokenizer is None:
+            return " ".join(str(t) for t in token_ids)
+        return self.tokenizer.decode(token_ids)
+
+    # -------------------------------------------------------------- admission
+    def _make_state(self, req: GenerationRequest, future=None) -> RequestState:
+        if req.prompt_token_ids is not None:
+            prompt = [int(t) for t in req.prompt_token_ids]
+        elif req.prompt is not None:
+            prompt = self.tokenize(req.prompt)
+        else:
+            raise ValueError("a request needs prompt or prompt_token_ids")
+        vocab = self.config.vocab_size
+        if any(t < 0 or t >= vocab for t in prompt):
+            raise ValueError(f"a prompt token id lies outside the vocabulary of {vocab}")
+        stop = set(int(t) for t in req.stop_token_ids)
+        if not req.ignore_eos:
+            stop |= set(self.eos_token_ids)
+        for s in req.stop_tokens:
+            # each stop string on its own, without special tokens
+            # (the reference joins them into one string first, gllm/engine/llm_engine.py:69-71)
+            stop |= set(self.tokenize(s, add_special_tokens=False))
+        sampling = SamplingParams(
+            temperature=req.temperature, top_k=req.top_k, top_p=req.top_p,
+            max_num_logprobs=req.max_num_logprobs, seed=req.seed,
+        )
+        sampling.validate()
+        return RequestState(
+            id=next(self._ids),
+            prompt_token_ids=prompt,
+            max_new_tokens=req.max_new_tokens,
+            stop_token_ids=stop,
+            sampling=sampling,
+            future=future,
+        )
+
+    def _create_result(self, state: RequestState) -> GenerationResult:
+        wants_lp = state.sampling.max_num_logprobs > 0
+        return GenerationResult(
+            token_ids=list(state.generated_token_ids),
+            logprobs=list(state.generated_logprobs) if wants_lp else None,
+            text=self.detokenize(state.generated_token_ids),
+            finish_reason=state.finish_reason,
+            token_logprobs=list(state.generated_token_logprobs) if wants_lp else None,
+        )
+
+    # ---------------------------------------------------------------- one step
+    def step(self) -> list[RequestState]:
+        """Schedule, run and sample one step; returns the requests it finished."""
+        sched: ScheduledStep = self.scheduler.schedule()
+        self.counters["preemptions"] = self.scheduler.num_preemptions
+        if not sched.entries:
+            return []
+        entries = []
+        sampling_rows = []
+        for e in sched.entries:
+            tokens = e.request.token_slice(e.start, e.num_tokens)
+            entries.append(StepEntry(e.request.id, tokens, [e.num_tokens - 1] if e.samples else []))
+            if e.samples:
+                sampling_rows.append(e.request)
+            if e.num_tokens == 1 and e.start > 0:
+                self.counters["decode_tokens"] += 1
+            else:
+                self.counters["prefill_tokens"] += e.num_tokens
+        logits = self.runner.run(entries, check=False)
+        sampled = {}
+        if sampling_rows:
+            out = self.sampler.forward(
+                logits,
+                [r.sampling for r in sampling_rows],
+                [len(r.generated_token_ids) for r in sampling_rows],
+            )
+            for i, r in enumerate(sampling_rows):
+                sampled[r.id] = out.token_ids[i]
+                if r.sampling.max_num_logprobs > 0:
+                    vals, ids = out.top_logprobs[i]
+                    r.generated_logprobs.append(TokenLogProbs(vals, ids))
+                    r.generated_token_logprobs.append(out.token_logprobs[i])
+        ops.check_status(self.device)
+        self.counters["steps"] += 1
+        return self.scheduler.update(sched, sampled)
+
+    # --------------------------------------------------------------- generate
+    def generate(self, reqs: list[GenerationRequest]) -> list[GenerationResult]:
+        """Run ``reqs`` to completion; results in the order of ``reqs``.  More
+        requests than ``max_batch_size`` are fine: the surplus waits its turn."""
+        states = [self._make_state(r) for r in reqs]
+        for s in states:
+            self.scheduler.add(s)
+        remaining = len(states)
+        while remaining:
+            finished = self.step()
+            remaining -= sum(1 for f in finished if any(f is s for s in states))
+            if not finished and not self.scheduler.has_work:
+                break
+        return [self._create_result(s) for s in states]
+
+    # --------------------------------------------------- continuous batching
+    def enqueue_request(self, req: GenerationRequest) -> asyncio.Future:
+        """From a coroutine: returns a future of the request's GenerationResult."""
+        loop = asyncio.get_running_loop()
+        fut = loop.create_future()
+        if not self.alive:
+            fut.set_exception(RuntimeError("Engine is not running"))
+            return fut
+        self.request_queue.put((req, fut, loop))
+        return fut
+
+    @staticmethod
+    def _resolve(fut, loop, result=None, error=None) -> None:
+        def _set():
+            if fut.done():
+                return
+            if error is not None:
+                fut.set_exception(error)
+            else:
+                fut.set_result(result)
+
+        loop.call_soon_threadsafe(_set)
+
+    def _drain_queue(self, blocking: bool) -> None:
+        items = []
+        if blocking:
+            try:
+                items.append(self.request_queue.get(block=True, timeout=0.05))
+            except queue.Empty:
+                return
+        while True:
+            try:
+                items.append(self.request_queue.get_nowait())
+            except queue.Empty:
+                break
+        for req, fut, loop in items:
+            try:
+                state = self._make_state(req, future=(fut, loop))
+                self.scheduler.add(state)
+            except Exception as e:  # delivered on the request's own future
+                self._resolve(fut, loop, error=e)
+
+    def run(self) -> None:
+        """The serving loop (call it on a thread of its own): admit what was
+        enqueued, run a step, resolve the futures of finished requests."""
+        self.alive = True
+        try:
+            while self.alive:
+                self._drain_queue(blocking=not self.scheduler.has_work)
+                if not self.scheduler.has_work:
+                    continue
+                for state in self.step():
+                    if state.future is not None:
+                        fut, loop = state.future
+                        self._resolve(fut, loop, result=self._create_result(state))
+        finally:
+            self.alive = False
+
+    def stop(self) -> None:
+        self.alive = False

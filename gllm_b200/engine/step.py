@@ -70,6 +70,7 @@ class StepRunner:
         self.workspace = Workspace(self.device)
         self.mixer_caches = cache.mixer_caches()
         self.steps_run = 0
+        self.last_h2d_bytes = 0
 
     # ------------------------------------------------------------------ build
     def build(self, entries: list[StepEntry]):
@@ -163,7 +164,7 @@ class StepRunner:
         for g in cache.groups:
             put(f"slotmap{g.index}", np.concatenate(slot_maps[g.index]))
         self._meta[:cursor].copy_(pinned[:cursor], non_blocking=True)
-        cache.flush_block_tables()
+        self.last_h2d_bytes = cursor * 4 + cache.flush_block_tables()
 
         def dev(name):
             start, n = views[name]

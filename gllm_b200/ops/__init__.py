@@ -30,6 +30,8 @@ __all__ = [
     "paged_attention",
     "status_word",
     "check_status",
+    "sample",
+    "argmax",
 ]
 
 P = c_void_p
@@ -42,6 +44,10 @@ _SIGNATURES = {
     },
     "gemm_fp32": {
         "gllm_gemm_f32": [P, P, P, c_int, c_int, c_int, c_int64, c_int64, c_int64, P],
+    },
+    "sampling": {
+        "gllm_sample": [P, c_int64, c_int, c_int, P, P, P, P, P, P, c_int, P, P, P, P, P, P, P],
+        "gllm_argmax": [P, c_int64, c_int, c_int, P, P],
     },
     "attention_simt": {
         "gllm_attention_simt_{t}": [P, c_int64, P, c_int64, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,
@@ -85,7 +91,13 @@ def _error_string(code: int) -> str:
         return f"cudaError {code}"
 
 
+# number of kernel launches made through this module (benchmarks read it)
+launch_count = 0
+
+
 def _check(code: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
     if code != 0:
         raise RuntimeError(f"{what}: launch failed: {_error_string(code)} (code {code})")
 
@@ -356,3 +368,77 @@ def paged_attention(
                                                        num_heads, scale, win, batch, out)
     return paged_attention_simt(qkv, qkv.shape[1], cache_layer, block_table, positions, token_row, num_heads,
                                 scale, win, out)
+
+
+# ----------------------------------------------------------------- sampling
+MAX_LOGPROBS = 32
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Index of the largest logit of every row (lowest index on ties), int32."""
+    _cuda(logits, "logits", torch.float32, contiguous=False)
+    rows, vocab = logits.shape
+    if logits.stride(1) != 1:
+        raise ValueError("logit rows must be contiguous")
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    f = _fn("sampling", "gllm_argmax")
+    _check(f(logits.data_ptr(), logits.stride(0), rows, vocab, out.data_ptr(), _stream()), "argmax")
+    return out
+
+
+def sample(
+    logits: torch.Tensor,
+    temperature: torch.Tensor,
+    top_k: torch.Tensor,
+    top_p: torch.Tensor,
+    seed: torch.Tensor,
+    counter: torch.Tensor,
+    num_logprobs: torch.Tensor | None = None,
+    max_logprobs: int = 0,
+    return_probs: bool = False,
+):
+    """One token per row from fp32 ``logits [rows, vocab]``.
+
+    Per row: ``temperature`` (0 = greedy), ``top_k`` (0 = whole vocabulary,
+    1 = greedy), ``top_p``, ``seed`` (int64) and ``counter`` (int32) of the
+    counter-based generator.  Returns a dict with ``tokens`` int32,
+    ``logprobs`` (of the sampled tokens), ``num_candidates``, and when
+    ``max_logprobs`` > 0 ``top_logprobs`` / ``top_ids`` ``[rows, max_logprobs]``
+    of which the first ``min(num_logprobs[row], num_candidates[row])`` are valid;
+    with ``return_probs`` also the distribution drawn from, ``[rows, vocab]``.
+    """
+    _cuda(logits, "logits", torch.float32, contiguous=False)
+    rows, vocab = logits.shape
+    if logits.stride(1) != 1:
+        raise ValueError("logit rows must be contiguous")
+    for name, t, dt in (("temperature", temperature, torch.float32), ("top_k", top_k, torch.int32),
+                        ("top_p", top_p, torch.float32), ("seed", seed, torch.int64),
+                        ("counter", counter, torch.int32)):
+        _cuda(t, name, dt)
+        if t.numel() != rows:
+            raise ValueError(f"{name} must have one entry per row")
+    if max_logprobs > MAX_LOGPROBS:
+        raise ValueError(f"at most {MAX_LOGPROBS} log-probabilities per token are supported")
+    dev = logits.device
+    out = {
+        "tokens": torch.empty(rows, dtype=torch.int32, device=dev),
+        "logprobs": torch.empty(rows, dtype=torch.float32, device=dev),
+        "num_candidates": torch.empty(rows, dtype=torch.int32, device=dev),
+    }
+    top_lp = top_id = None
+    if max_logprobs > 0:
+        _cuda(num_logprobs, "num_logprobs", torch.int32)
+        top_lp = torch.zeros((rows, max_logprobs), dtype=torch.float32, device=dev)
+        top_id = torch.full((rows, max_logprobs), -1, dtype=torch.int32, device=dev)
+        out["top_logprobs"], out["top_ids"] = top_lp, top_id
+    probs = torch.empty((rows, vocab), dtype=torch.float32, device=dev) if return_probs else None
+    if probs is not None:
+        out["probs"] = probs
+    f = _fn("sampling", "gllm_sample")
+    _check(f(logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(), top_k.data_ptr(),
+             top_p.data_ptr(), seed.data_ptr(), counter.data_ptr(),
+             _ptr(num_logprobs) if max_logprobs > 0 else None, max_logprobs, out["tokens"].data_ptr(),
+             out["logprobs"].data_ptr(), out["num_candidates"].data_ptr(), _ptr(top_lp), _ptr(top_id),
+             _ptr(probs), _stream()), "sample")
+    return out

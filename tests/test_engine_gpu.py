@@ -1,0 +1,162 @@
+"""Generation through the Python entry point and the command line, against the
+plain implementation: greedy tokens, long decoding, the first tokens of a
+sequence, chunked prefill with preemption, sampling options and the async path."""
+
+import asyncio
+import json
+import os
+import subprocess
+import sys
+import threading
+
+import pytest
+import torch
+
+from plain_llama import plain_forward
+from tiny_models import read_raw, write_tiny
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def plain_greedy_check(cfg, weights, prompt, produced, slack):
+    """Every produced token is the plain implementation's argmax given the
+    tokens before it, or within ``slack`` (of the largest logit) of it."""
+    tokens = list(prompt)
+    for t in produced:
+        logits = plain_forward(cfg, weights, tokens, torch.float64)[-1]
+        best = int(logits.argmax())
+        if t != best:
+            assert float(logits[best] - logits[t]) <= slack * float(logits.abs().max()), (len(tokens), t, best)
+        tokens.append(t)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_greedy_generation_through_the_entry_point(name, dtype, tmp_path):
+    from gllm_b200 import GenerationRequest, GeneratorParams, LLMEngine
+
+    folder = write_tiny(name, str(tmp_path / "m"), sharp=(dtype == "float32"))
+    cfg, weights = read_raw(folder, round_to_bf16=(dtype == "bfloat16"))
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in (1, 7, 16, 23, 40)]
+    # few pages, small portions: chunked prefill, continuous batching and preemption all happen
+    params = GeneratorParams(block_size=8, max_batch_size=3, max_seq_len=64, num_blocks=10, model_dtype=dtype,
+                             max_num_batched_tokens=24, prefill_chunk=8)
+    engine = LLMEngine(folder, params, device="cuda:0")
+    reqs = [GenerationRequest(prompt_token_ids=p, max_new_tokens=12, temperature=0.0, ignore_eos=True) for p in prompts]
+    results = engine.generate(reqs)
+    slack = 1e-5 if dtype == "float32" else 0.05
+    for p, r in zip(prompts, results):
+        assert len(r.token_ids) == 12 and r.finish_reason == "length"
+        plain_greedy_check(cfg, weights, p, r.token_ids, slack)
+    assert engine.counters["preemptions"] >= 1
+    engine.cache.check_invariants()
+    assert engine.cache.num_free_pages() == 10 and not engine.scheduler.has_work
+    # the same requests one by one give the same tokens (float32: exactly)
+    if dtype == "float32":
+        for req, r in zip(reqs, results):
+            assert engine.generate([req])[0].token_ids == r.token_ids
+
+
+def test_long_decoding_and_first_tokens(tmp_path):
+    from gllm_b200 import GenerationRequest, GeneratorParams, LLMEngine
+
+    folder = write_tiny("C", str(tmp_path / "m"))
+    cfg, weights = read_raw(folder)
+    engine = LLMEngine(folder, GeneratorParams(block_size=16, max_batch_size=2, max_seq_len=400, model_dtype="float32"),
+                       device="cuda:0")
+    # a one-token prompt: the very first positions of a sequence, then 300 decoded tokens across 19 pages
+    # and far past the 24-token window of layer 1
+    res = engine.generate([GenerationRequest(prompt_token_ids=[5], max_new_tokens=300, temperature=0.0, ignore_eos=True)])[0]
+    assert len(res.token_ids) == 300
+    tokens = [5] + res.token_ids
+    logits = plain_forward(cfg, weights, tokens[:-1], torch.float64)
+    for i in list(range(0, 20)) + list(range(20, 300, 7)) + [299]:
+        best = int(logits[i].argmax())
+        if tokens[i + 1] != best:
+            assert float(logits[i, best] - logits[i, tokens[i + 1]]) < 1e-5 * float(logits[i].abs().max()), i
+
+
+def test_stop_tokens_logprobs_and_sampling_options(tmp_path):
+    from gllm_b200 import GenerationRequest, GeneratorParams, LLMEngine
+
+    folder = write_tiny("B", str(tmp_path / "m"))
+    cfg, weights = read_raw(folder)
+    engine = LLMEngine(folder, GeneratorParams(block_size=16, max_batch_size=4, max_seq_len=64, model_dtype="float32"),
+                       device="cuda:0")
+    prompt = [9, 8, 7, 6, 5]
+    free_run = engine.generate([GenerationRequest(prompt_token_ids=prompt, max_new_tokens=8, temperature=0.0,
+                                                  ignore_eos=True, max_num_logprobs=3)])[0]
+    assert len(free_run.logprobs) == 8 and free_run.logprobs[0].candidate_token_ids[0] == free_run.token_ids[0]
+    want = torch.log_softmax(plain_forward(cfg, weights, prompt, torch.float64)[-1], -1)
+    assert abs(free_run.logprobs[0].logprobs[0] - float(want.max())) < 1e-4
+    assert abs(free_run.token_logprobs[0] - float(want.max())) < 1e-4
+    # the third token as a stop token: generation ends there and keeps it (gllm/engine/llm_engine.py:124-127)
+    stop = free_run.token_ids[2]
+    if stop not in free_run.token_ids[:2]:
+        r = engine.generate([GenerationRequest(prompt_token_ids=prompt, max_new_tokens=8, temperature=0.0,
+                                               ignore_eos=True, stop_token_ids=[stop])])[0]
+        assert r.token_ids == free_run.token_ids[:3] and r.finish_reason == "stop"
+    # eos from config.json (7) stops unless ignored; sampled runs are reproducible by seed and differ across seeds
+    a = engine.generate([GenerationRequest(prompt_token_ids=prompt, max_new_tokens=20, temperature=1.0, top_k=0,
+                                           top_p=1.0, seed=s, ignore_eos=True) for s in (1, 1, 2)])
+    assert a[0].token_ids == a[1].token_ids and a[0].token_ids != a[2].token_ids
+    assert a[0].text == " ".join(map(str, a[0].token_ids))
+    with pytest.raises(ValueError, match="only supports"):
+        engine.generate([GenerationRequest(prompt_token_ids=list(range(64)), max_new_tokens=1)])
+    with pytest.raises(ValueError, match="vocabulary"):
+        engine.generate([GenerationRequest(prompt_token_ids=[400], max_new_tokens=1)])
+    with pytest.raises(RuntimeError, match="tokenizer"):
+        engine.generate([GenerationRequest(prompt="hello", max_new_tokens=1)])
+
+
+def test_enqueue_request_and_run(tmp_path):
+    from gllm_b200 import GenerationRequest, GeneratorParams, LLMEngine
+
+    folder = write_tiny("A", str(tmp_path / "m"))
+    engine = LLMEngine(folder, GeneratorParams(block_size=4, max_batch_size=2, max_seq_len=32, model_dtype="float32"),
+                       device="cuda:0")
+    reqs = [GenerationRequest(prompt_token_ids=[1 + i, 2, 3], max_new_tokens=5, temperature=0.0, ignore_eos=True)
+            for i in range(5)]
+    expected = [r.token_ids for r in engine.generate(reqs)]
+
+    async def client():
+        not_running = await asyncio.gather(engine.enqueue_request(reqs[0]), return_exceptions=True)
+        assert isinstance(not_running[0], RuntimeError)
+        thread = threading.Thread(target=engine.run, daemon=True)
+        thread.start()
+        while not engine.alive:
+            await asyncio.sleep(0.01)
+        bad = GenerationRequest(prompt_token_ids=list(range(40)), max_new_tokens=1)
+        results = await asyncio.gather(*[engine.enqueue_request(r) for r in reqs], engine.enqueue_request(bad),
+                                       return_exceptions=True)
+        engine.stop()
+        thread.join(timeout=10)
+        return results
+
+    results = asyncio.run(client())
+    assert isinstance(results[-1], ValueError)                       # delivered on its own future
+    assert [r.token_ids for r in results[:-1]] == expected           # more requests than slots: they wait, none is refused
+
+
+def test_command_line(tmp_path):
+    folder = str(tmp_path / "m")
+    cfg_path = str(tmp_path / "cfg.json")
+    from tiny_models import TINY_B
+
+    with open(cfg_path, "w") as f:
+        json.dump(TINY_B, f)
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    subprocess.run([sys.executable, "-m", "gllm_b200", "make-random", "--config", cfg_path, "--out", folder, "--seed", "3"],
+                   check=True, env=env, cwd=ROOT)
+    out = subprocess.run(
+        [sys.executable, "-m", "gllm_b200", "generate", "--model", folder, "--prompt-ids", "5 17 3", "--prompt-ids",
+         "9,9,9,1", "--max-new-tokens", "4", "--temperature", "0", "--ignore-eos", "--max-seq-len", "64",
+         "--max-batch-size", "2", "--model-dtype", "float32"],
+        check=True, env=env, cwd=ROOT, capture_output=True, text=True,
+    )
+    lines = [json.loads(line) for line in out.stdout.strip().splitlines()]
+    assert len(lines) == 2 and all(len(line["token_ids"]) == 4 for line in lines)
+    cfg, weights = read_raw(folder)
+    plain_greedy_check(cfg, weights, [5, 17, 3], lines[0]["token_ids"], 1e-5)
