@@ -93,6 +93,10 @@ class StepRunner:
         if len(entries) > cache.max_batch_size:
             raise ValueError("more requests in a step than state slots")
 
+        # wanted rows keep the caller's order of entries; the flat batch itself puts
+        # multi-token portions first and single tokens after them
+        caller_order = {id(e): i for i, e in enumerate(entries)}
+        entries = sorted(entries, key=lambda e: (len(e.tokens) == 1, caller_order[id(e)]))
         appended = []
         slot_maps = {g.index: [] for g in cache.groups}
         try:
@@ -120,9 +124,10 @@ class StepRunner:
         cu_q = np.zeros(r + 1, dtype=np.int32)
         ctx_lens = np.empty(r, dtype=np.int32)
         slots = np.empty(r, dtype=np.int32)
-        rows = []
+        rows_of = {}
         q_lens = []
         off = 0
+        n_prefill = 0
         for i, e in enumerate(entries):
             rc = cache.requests[e.request_id]
             n = len(e.tokens)
@@ -134,11 +139,13 @@ class StepRunner:
             for w in e.want:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.request_id!r} wants place {w} of {n} tokens")
-                rows.append(off + w)
+            rows_of[caller_order[id(e)]] = [off + w for w in e.want]
             q_lens.append(n)
+            if n > 1:
+                n_prefill += n
             off += n
             cu_q[i + 1] = off
-        logit_rows = np.asarray(rows, dtype=np.int32)
+        logit_rows = np.asarray([r for i in sorted(rows_of) for r in rows_of[i]], dtype=np.int32)
 
         # pack everything into one pinned buffer, one copy to the device
         pinned = self._pinned[self._flip]
@@ -186,6 +193,7 @@ class StepRunner:
             context_lens_host=tuple(int(c) for c in ctx_lens),
             max_q_len=max(q_lens),
             max_seq_len=max(int(c) + q for c, q in zip(ctx_lens, q_lens)),
+            num_prefill_tokens=n_prefill,
             workspace=self.workspace,
         )
         return dev("tokens"), ctx, dev("rows")

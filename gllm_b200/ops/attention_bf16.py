@@ -1,12 +1,83 @@
-"""Tensor-core attention kernels of the bf16 path (prefill tiles and split-KV
-decode) over the paged cache."""
+"""Attention kernels of the bf16 path over the paged cache: split-KV decode
+for requests that bring one token, tiled prefill for the rest.
+
+The step function lays the flat batch out with all multi-token portions first
+and the single decoded tokens after them (``StepContext.num_prefill_tokens``),
+so each kernel works on one contiguous run of tokens.
+"""
 
 from __future__ import annotations
 
+from ctypes import c_float, c_int, c_int64, c_void_p
+
+import torch
+
+from gllm_b200.ops.build import load_module
+
+P = c_void_p
+# keys per split of the decode kernel; fixed, so the cut depends on positions only
+DECODE_CHUNK = 128
+_DECODE_HEAD_DIMS = (16, 32, 64, 128)
+
+_decode = None
+
+
+def _decode_fn():
+    global _decode
+    if _decode is None:
+        lib = load_module("attention_bf16")
+        f = lib.gllm_attention_decode_bf16
+        f.argtypes = [P, c_int64, P, c_int64, P, P, c_int, P, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,
+                      c_int, c_int, c_float, c_int, P, P]
+        f.restype = c_int
+        _decode = f
+    return _decode
+
 
 def supports(head_dim: int, block_size: int) -> bool:
-    return False
+    return head_dim in _DECODE_HEAD_DIMS and (block_size * head_dim) % 8 == 0
 
 
-def paged_attention_bf16(*args, **kwargs):
-    raise NotImplementedError
+def decode_scratch_elems(num_queries: int, num_heads: int, head_dim: int, max_seq_len: int) -> tuple[int, int, int]:
+    """(num_chunks, floats of partial outputs, floats of partial max/sum)."""
+    chunks = max(1, -(-max_seq_len // DECODE_CHUNK))
+    return chunks, num_queries * num_heads * chunks * head_dim, num_queries * num_heads * chunks * 2
+
+
+def decode_attention(q, q_stride, cache_layer, block_table, positions, token_row, num_heads, scale, window,
+                     max_seq_len, workspace, out):
+    """Split-KV attention of ``positions.numel()`` single query tokens."""
+    from gllm_b200 import ops
+
+    num_pages, _, hkv, block_size, d = cache_layer.shape
+    n = positions.numel()
+    chunks, n_o, n_ml = decode_scratch_elems(n, num_heads, d, max_seq_len)
+    if workspace is not None:
+        part_o = workspace.get("attention_decode_partial_out", n_o, torch.float32)
+        part_ml = workspace.get("attention_decode_partial_max_sum", n_ml, torch.float32)
+    else:
+        part_o = torch.empty(n_o, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(n_ml, dtype=torch.float32, device=q.device)
+    code = _decode_fn()(
+        q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), cache_layer.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), positions.data_ptr(), token_row.data_ptr(), None, n, part_o.data_ptr(),
+        part_ml.data_ptr(), num_heads, hkv, d, block_size, num_pages, DECODE_CHUNK, chunks, float(scale),
+        int(window), ops.status_word(q.device).data_ptr(), ops._stream(),
+    )
+    ops._check(code, "attention_decode_bf16")
+    ops.launch_count += 1  # two kernels: split and merge
+    return out
+
+
+def paged_attention_bf16(qkv, cache_layer, block_table, positions, token_row, num_heads, scale, window, batch, out):
+    from gllm_b200 import ops
+
+    n = qkv.shape[0]
+    n_pf = batch.num_prefill_tokens
+    if n_pf > 0:
+        ops.paged_attention_simt(qkv[:n_pf], qkv.shape[1], cache_layer, block_table, positions[:n_pf],
+                                 token_row[:n_pf], num_heads, scale, window, out[:n_pf])
+    if n_pf < n:
+        decode_attention(qkv[n_pf:], qkv.shape[1], cache_layer, block_table, positions[n_pf:], token_row[n_pf:],
+                         num_heads, scale, window, batch.max_seq_len, batch.workspace, out[n_pf:])
+    return out

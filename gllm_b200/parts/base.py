@@ -97,6 +97,8 @@ class StepContext:
     context_lens_host: tuple[int, ...] = ()
     max_q_len: int = 0
     max_seq_len: int = 0
+    # the flat batch holds all multi-token portions first, then the single tokens
+    num_prefill_tokens: int = 0
     # device scratch the attention kernels share (owned by the step function)
     workspace: Any = None
 

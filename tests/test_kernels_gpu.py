@@ -200,3 +200,55 @@ def test_attention_simt(ops, dtype, hq, hkv, d, bs, window):
         assert not got.isnan().any()
         torch.testing.assert_close(got, want, **(dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else tol(dtype)))
         off += nq
+
+
+@pytest.mark.parametrize("hq,hkv,d,bs,window", [
+    (4, 2, 16, 4, None), (3, 1, 32, 8, None), (5, 5, 16, 16, 24), (32, 8, 64, 16, None), (6, 3, 128, 32, 100),
+    (16, 1, 64, 16, None), (12, 2, 128, 16, 300), (7, 7, 64, 8, None),
+])
+def test_attention_decode_split_kv(ops, hq, hkv, d, bs, window):
+    """One query token per request over caches of 1 .. 1500 tokens: several chunks of 128 keys, a chunk
+    that holds a single key, windows that start inside a chunk; the far keys carry the weight."""
+    from gllm_b200.ops import attention_bf16
+
+    g = torch.Generator().manual_seed(6)
+    lens = [1, 37, 128, 129, 300, 1500, 64]
+    pool, table, ks, vs, qs, pos, rows = _paged_case(g, torch.bfloat16, lens, hq, hkv, d, bs, [1] * len(lens))
+    n = pos.numel()
+    qkv = torch.zeros(n, (hq + 2 * hkv) * d, dtype=torch.bfloat16)
+    qkv[:, : hq * d] = torch.cat(qs).reshape(n, hq * d)
+    scale = 1.0 / math.sqrt(d)
+    assert attention_bf16.supports(d, bs)
+    out = torch.full((n, hq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    attention_bf16.decode_attention(qkv.cuda(), qkv.shape[1], pool.cuda(), table.cuda(), pos.cuda(), rows.cuda(), hq,
+                                    scale, window or 0, max(lens), None, out)
+    ops.check_status()
+    for r in range(n):
+        want = _plain_attn(qs[r], ks[r], vs[r], pos[r:r + 1].long(), window, scale)
+        got = out[r].double().cpu().view(1, hq, d)
+        assert not got.isnan().any()
+        torch.testing.assert_close(got, want, **tol(torch.bfloat16))
+
+
+def test_attention_mixed_batch_uses_both_kernels(ops):
+    """Portions first, single tokens after, as the step function lays a batch out."""
+    from types import SimpleNamespace
+
+    g = torch.Generator().manual_seed(7)
+    hq, hkv, d, bs = 8, 2, 64, 16
+    lens, q_counts = [200, 90, 400, 33], [50, 2, 1, 1]
+    pool, table, ks, vs, qs, pos, rows = _paged_case(g, torch.bfloat16, lens, hq, hkv, d, bs, q_counts)
+    n = pos.numel()
+    qkv = torch.zeros(n, (hq + 2 * hkv) * d, dtype=torch.bfloat16)
+    qkv[:, : hq * d] = torch.cat(qs).reshape(n, hq * d)
+    from gllm_b200.engine.step import Workspace
+
+    batch = SimpleNamespace(num_prefill_tokens=52, max_seq_len=400, workspace=Workspace(torch.device("cuda")))
+    scale = 1.0 / math.sqrt(d)
+    out = ops.paged_attention(qkv.cuda(), pool.cuda(), table.cuda(), pos.cuda(), rows.cuda(), hq, scale, batch=batch)
+    ops.check_status()
+    off = 0
+    for r, nq in enumerate(q_counts):
+        want = _plain_attn(qs[r], ks[r], vs[r], pos[off:off + nq].long(), None, scale)
+        torch.testing.assert_close(out[off:off + nq].double().cpu().view(nq, hq, d), want, **tol(torch.bfloat16))
+        off += nq

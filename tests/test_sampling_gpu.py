@@ -54,12 +54,15 @@ def test_distribution_equals_the_reference_rules(temperature, top_k, top_p, voca
     for r in range(6):
         want, n = plain_sampling_distribution(logits[r].cpu(), temperature, top_k, top_p)
         got = out["probs"][r].double().cpu()
-        # an entry whose cumulative probability lands within rounding of top_p may fall on either side
         if int(out["num_candidates"][r]) != n:
+            # two cases are no fault: a cumulative probability within rounding of top_p, and equal
+            # logits on both sides of the cut (the kernel keeps or drops equal values together)
             z = logits[r].double().cpu() / temperature
             k = vocab if top_k == 0 else min(top_k, vocab)
-            p = torch.softmax(torch.topk(z, k).values, -1).cumsum(-1)
-            assert (p - top_p).abs().min() < 1e-5, (r, int(out["num_candidates"][r]), n)
+            top = torch.topk(z, min(k + 1, vocab)).values
+            p = torch.softmax(top[:k], -1).cumsum(-1)
+            tie = n < top.numel() and float(top[n - 1]) == float(top[n])
+            assert tie or float((p - top_p).abs().min()) < 1e-5, (r, int(out["num_candidates"][r]), n)
             continue
         torch.testing.assert_close(got, want, rtol=2e-4, atol=1e-7)
         assert int(out["tokens"][r]) in torch.nonzero(want).flatten().tolist()
@@ -105,3 +108,15 @@ def test_top_logprobs():
     out = ops.sample(logits, **_args(5, 1.0, 3, 1.0, nlp=5), max_logprobs=5)
     assert out["num_candidates"].tolist() == [3] * 5
     assert (out["top_ids"][:, 3:] == -1).all() and (out["top_ids"][:, :3] >= 0).all()
+
+
+def test_equal_logits_are_kept_or_dropped_together():
+    from gllm_b200 import ops
+
+    logits = torch.full((1, 64), -20.0)
+    logits[0, [3, 9, 11, 30]] = torch.tensor([4.0, 2.0, 2.0, 1.0])       # the 2nd and 3rd highest tie
+    out = ops.sample(logits.cuda(), **_args(1, 1.0, 2, 1.0), return_probs=True)
+    assert int(out["num_candidates"][0]) == 3                            # top_k = 2 keeps both of the tied values
+    # softmax .78 .105 .105 .04: top_p .9 is crossed inside the tie, so both tied values go
+    out = ops.sample(logits.cuda(), **_args(1, 1.0, 0, 0.9), return_probs=True)
+    assert int(out["num_candidates"][0]) == 1 and float(out["probs"][0, 3]) == 1.0
