@@ -116,15 +116,29 @@ class CacheManager:
                 self._states.append(None)
         for g in self.groups:
             r = g.requirement
+            # One page more than the allocator hands out: the *null page* (id num_blocks).
+            # Rows that pad a batch to a fixed size store there and read from there.
             if allocate_pools:
                 g.pool = torch.zeros(
-                    (len(g.owner_entries), self.num_blocks, 2, r.num_kv_heads, self.block_size, r.head_dim),
+                    (len(g.owner_entries), self.num_blocks + 1, 2, r.num_kv_heads, self.block_size, r.head_dim),
                     dtype=dtype, device=self.device,
                 )
+            # One row more than there are state slots: the *null row* (index max_batch_size),
+            # every entry of which is the null page.
             g.block_table = torch.full(
-                (self.max_batch_size, self.max_blocks_per_request), -1, dtype=torch.int32, device=self.device
+                (self.max_batch_size + 1, self.max_blocks_per_request), -1, dtype=torch.int32, device=self.device
             )
-            g.block_table_host = np.full((self.max_batch_size, self.max_blocks_per_request), -1, dtype=np.int32)
+            g.block_table[self.max_batch_size].fill_(self.num_blocks)
+            g.block_table_host = np.full((self.max_batch_size + 1, self.max_blocks_per_request), -1, dtype=np.int32)
+            g.block_table_host[self.max_batch_size] = self.num_blocks
+
+    @property
+    def null_page(self) -> int:
+        return self.num_blocks
+
+    @property
+    def null_row(self) -> int:
+        return self.max_batch_size
 
     # ------------------------------------------------------------- accounting
     def bytes_per_token(self) -> int:

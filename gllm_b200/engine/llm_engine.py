@@ -80,7 +80,8 @@ class LLMEngine(LLMEngineBase):
             dtype=self.model.dtype,
             device=dev,
         )
-        self.runner = StepRunner(self.model, self.cache, gen_params.max_num_batched_tokens)
+        self.runner = StepRunner(self.model, self.cache, gen_params.max_num_batched_tokens,
+                                 cuda_graphs=gen_params.cuda_graphs)
         self.scheduler = Scheduler(gen_params, self.cache)
         self.sampler = Sampler(dev)
         self.request_queue: queue.Queue = queue.Queue()
@@ -177,9 +178,13 @@ class LLMEngine(LLMEngineBase):
                 self.counters["decode_tokens"] += 1
             else:
                 self.counters["prefill_tokens"] += e.num_tokens
-        logits = self.runner.run(entries, check=False)
+        all_greedy = all(r.sampling.greedy and r.sampling.max_num_logprobs == 0 for r in sampling_rows)
+        logits = self.runner.run(entries, check=False, greedy=all_greedy)
         sampled = {}
-        if sampling_rows:
+        if sampling_rows and all_greedy:
+            for r, token in zip(sampling_rows, self.runner.last_argmax.tolist()):
+                sampled[r.id] = token
+        elif sampling_rows:
             out = self.sampler.forward(
                 logits,
                 [r.sampling for r in sampling_rows],

@@ -54,8 +54,12 @@ def _align4(n: int) -> int:
 class StepRunner:
     """Owns the staging buffers of the batch metadata and runs steps."""
 
-    def __init__(self, model, cache: CacheManager, max_tokens_per_step: int):
+    def __init__(self, model, cache: CacheManager, max_tokens_per_step: int, cuda_graphs: bool = True):
         self.model = model
+        self.cuda_graphs = bool(cuda_graphs) and torch.cuda.is_available()
+        self._graphs: dict = {}
+        self._graph_pool = None
+        self.graph_replays = 0
         self.cache = cache
         self.device = model.device
         self.dtype = model.dtype
@@ -73,9 +77,15 @@ class StepRunner:
         self.last_h2d_bytes = 0
 
     # ------------------------------------------------------------------ build
-    def build(self, entries: list[StepEntry]):
+    def build(self, entries: list[StepEntry], pad_to: int = 0, seq_bucket: int = 0):
         """Reserve pages, lay the flat batch out on the host and upload it.
-        Returns (tokens, StepContext, logit_rows)."""
+        Returns (tokens, StepContext, logit_rows).
+
+        ``pad_to`` (decode-only steps): pad the batch with rows that belong to
+        no request up to that many, so a captured graph sees fixed shapes; the
+        padding rows use the cache's null row and null page and want logits
+        like everybody else.  ``seq_bucket`` then stands in for the longest
+        sequence."""
         cache = self.cache
         if not entries:
             raise ValueError("a step needs at least one entry")
@@ -117,13 +127,16 @@ class StepRunner:
                     cache.rollback(rid, before)
             raise
 
-        r = len(entries)
-        tokens = np.empty(n_total, dtype=np.int32)
-        positions = np.empty(n_total, dtype=np.int32)
-        token_row = np.empty(n_total, dtype=np.int32)
+        real_r = len(entries)
+        pad = max(0, pad_to - real_r)
+        r = real_r + pad
+        n_total += pad
+        tokens = np.zeros(n_total, dtype=np.int32)
+        positions = np.zeros(n_total, dtype=np.int32)
+        token_row = np.full(n_total, cache.null_row, dtype=np.int32)
         cu_q = np.zeros(r + 1, dtype=np.int32)
-        ctx_lens = np.empty(r, dtype=np.int32)
-        slots = np.empty(r, dtype=np.int32)
+        ctx_lens = np.zeros(r, dtype=np.int32)
+        slots = np.full(r, cache.null_row, dtype=np.int32)
         rows_of = {}
         q_lens = []
         off = 0
@@ -145,7 +158,13 @@ class StepRunner:
                 n_prefill += n
             off += n
             cu_q[i + 1] = off
-        logit_rows = np.asarray([r for i in sorted(rows_of) for r in rows_of[i]], dtype=np.int32)
+        row_list = [x for i in sorted(rows_of) for x in rows_of[i]]
+        for k in range(pad):
+            q_lens.append(1)
+            cu_q[real_r + k + 1] = off + k + 1
+            row_list.append(off + k)
+        logit_rows = np.asarray(row_list, dtype=np.int32)
+        null_slots = np.full(pad, cache.null_page * cache.block_size, dtype=np.int32)
 
         # pack everything into one pinned buffer, one copy to the device
         pinned = self._pinned[self._flip]
@@ -169,7 +188,7 @@ class StepRunner:
         put("slots", slots)
         put("rows", logit_rows)
         for g in cache.groups:
-            put(f"slotmap{g.index}", np.concatenate(slot_maps[g.index]))
+            put(f"slotmap{g.index}", np.concatenate(slot_maps[g.index] + [null_slots]))
         self._meta[:cursor].copy_(pinned[:cursor], non_blocking=True)
         self.last_h2d_bytes = cursor * 4 + cache.flush_block_tables()
 
@@ -192,18 +211,78 @@ class StepRunner:
             q_lens_host=tuple(q_lens),
             context_lens_host=tuple(int(c) for c in ctx_lens),
             max_q_len=max(q_lens),
-            max_seq_len=max(int(c) + q for c, q in zip(ctx_lens, q_lens)),
+            max_seq_len=max(seq_bucket, max(int(c) + q for c, q in zip(ctx_lens, q_lens))),
             num_prefill_tokens=n_prefill,
             workspace=self.workspace,
         )
+        self._last_views = views
         return dev("tokens"), ctx, dev("rows")
 
     # -------------------------------------------------------------------- run
-    def run(self, entries: list[StepEntry], check: bool = True) -> torch.Tensor:
+    def _graph_key(self, entries: list[StepEntry]):
+        """(batch bucket, sequence bucket) when the step can run as a captured
+        graph: every entry brings one token and wants its logits."""
+        if not self.cuda_graphs or not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            return None
+        bucket = 1
+        while bucket < len(entries):
+            bucket *= 2
+        bucket = min(bucket, self.cache.max_batch_size)
+        if bucket < len(entries) or bucket > self.max_tokens:
+            return None
+        longest = 1
+        for e in entries:
+            rc = self.cache.requests.get(e.request_id)
+            longest = max(longest, (rc.num_tokens if rc else 0) + 1)
+        seq_bucket = 1024
+        while seq_bucket < longest:
+            seq_bucket *= 2
+        return bucket, min(seq_bucket, max(self.cache.max_seq_len, longest))
+
+    def run(self, entries: list[StepEntry], check: bool = True, greedy: bool = False) -> torch.Tensor:
         """Run one step; returns fp32 logits ``[wanted, vocab]`` on the device,
-        in the order of the entries and of their ``want`` lists."""
-        tokens, ctx, rows = self.build(entries)
-        logits = self.model.forward(tokens, ctx, self.mixer_caches, rows)
+        in the order of the entries and of their ``want`` lists.  With
+        ``greedy`` the argmax of every row is left in ``self.last_argmax``.
+
+        A step in which every request brings a single token runs as a CUDA
+        graph captured once per (batch bucket, sequence bucket): same kernels,
+        same buffers, one launch."""
+        wanted = sum(len(e.want) for e in entries)
+        key = self._graph_key(entries)
+        self.last_argmax = None
+        if key is None:
+            tokens, ctx, rows = self.build(entries)
+            logits = self.model.forward(tokens, ctx, self.mixer_caches, rows)
+            if greedy and wanted:
+                self.last_argmax = ops.argmax(logits)
+        else:
+            bucket, seq_bucket = key
+            tokens, ctx, rows = self.build(entries, pad_to=bucket, seq_bucket=seq_bucket)
+            record = self._graphs.get(key)
+            if record is None:
+                # first time: run it plainly (this is the step's result), then capture for later
+                logits = self.model.forward(tokens, ctx, self.mixer_caches, rows)
+                argmax = ops.argmax(logits)
+                torch.cuda.synchronize(self.device)
+                graph = torch.cuda.CUDAGraph()
+                if self._graph_pool is None:
+                    self._graph_pool = torch.cuda.graph_pool_handle()
+                launches_before = ops.launch_count
+                with torch.cuda.graph(graph, pool=self._graph_pool):
+                    g_logits = self.model.forward(tokens, ctx, self.mixer_caches, rows)
+                    g_argmax = ops.argmax(g_logits)
+                launches = ops.launch_count - launches_before
+                ops.launch_count = launches_before          # captured, not run
+                self._graphs[key] = (graph, g_logits, g_argmax, dict(self._last_views), launches)
+            else:
+                graph, logits, argmax, views, launches = record
+                if views != self._last_views:
+                    raise RuntimeError("the batch layout of a captured decode step changed")
+                graph.replay()
+                self.graph_replays += 1
+                ops.launch_count += launches
+            logits = logits[:wanted]
+            self.last_argmax = argmax[:wanted]
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1

@@ -57,7 +57,7 @@ def test_layers_with_equal_needs_share_a_group():
     c = m2.mixer_caches()
     assert c[1].group == 0 and not c[1].writes and c[0].writes
     assert c[1].pages.data_ptr() == c[0].pages.data_ptr()     # reads the other entry's pages
-    assert m2.groups[0].pool.shape == (1, 8, 2, 2, 4, 16)
+    assert m2.groups[0].pool.shape == (1, 8 + 1, 2, 2, 4, 16)    # + the null page
 
 
 def test_append_commit_free_and_slot_mapping():
@@ -75,7 +75,7 @@ def test_append_commit_free_and_slot_mapping():
     assert list(m.groups[0].block_table_host[rc.slot, :3]) == m.requests["a"].blocks[0]
     m.check_invariants()
     m.free_request("a")
-    assert m.num_free_pages() == 12 and (m.groups[0].block_table_host == -1).all()
+    assert m.num_free_pages() == 12 and (m.groups[0].block_table_host[:-1] == -1).all()
     with pytest.raises(CacheError):
         m.free_request("a")
 
