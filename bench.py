@@ -352,7 +352,15 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the full model (named in config)")
+    ap.add_argument("--kernel", default=None, help="time one kernel alone (see gllm_b200/kernel_bench.py)")
+    ap.add_argument("--shape", default="", help="with --kernel: overrides such as batch=8,context=2048")
     args = ap.parse_args()
+    if args.kernel:
+        from gllm_b200 import kernel_bench
+
+        overrides = {k: int(v) for k, v in (kv.split("=") for kv in args.shape.split(",") if kv)}
+        print(json.dumps(kernel_bench.run(args.kernel, load_peaks(), overrides)))
+        return 0
     if args.impl == "reference":
         print(json.dumps(run_reference(args)))
         return 0

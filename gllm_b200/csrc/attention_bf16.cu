@@ -95,41 +95,65 @@ decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride,
   // blocks of 32 keys aligned to absolute positions; warps take them round-robin
   const int first_block = (split * chunk) / 32;
   const int last_block = (c1 - 1) / 32;
+  constexpr int V_LOADS = 32 / KG;               // 16-byte value loads per lane and block of 32 keys
+  constexpr int V_BATCH = V_LOADS < 8 ? V_LOADS : 8;
   for (int blk = first_block + warp; blk <= last_block; blk += DEC_WARPS) {
     const int j0 = blk * 32;
     if (j0 + 31 < c0) continue;
-    // ---- scores: lane <-> key j0 + lane
+    // ---- every lane looks its own key's page up once; all loads of the block are issued before any is used
     const int j = j0 + lane;
     const bool valid = j >= c0 && j < c1;
+    int page = -1;
+    if (valid) {
+      page = bt[j / block_size];
+      if (page < 0 || page >= num_pages) {
+        atomicOr(status, GLLM_STATUS_PAGE_RANGE);
+        page = -1;
+      }
+    }
+    uint4 kraw[DG];
+    if (page >= 0) {
+      const uint4* kp = reinterpret_cast<const uint4*>(
+          cache + (int64_t)page * page_elems + (int64_t)kvh * head_elems + (int64_t)(j % block_size) * D);
+#pragma unroll
+      for (int c = 0; c < DG; ++c) kraw[c] = __ldg(kp + c);
+    }
+    uint4 vraw[V_BATCH];
+    auto load_values = [&](int first) {
+#pragma unroll
+      for (int i = 0; i < V_BATCH; ++i) {
+        const int jj = (first + i) * KG + kg;
+        const int pg = __shfl_sync(0xffffffffu, page, jj);
+        const int key = j0 + jj;
+        vraw[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (pg >= 0)
+          vraw[i] = __ldg(reinterpret_cast<const uint4*>(cache + (int64_t)pg * page_elems + v_off +
+                                                         (int64_t)kvh * head_elems +
+                                                         (int64_t)(key % block_size) * D) + dg);
+      }
+    };
+    load_values(0);
+    // ---- scores: lane <-> key j0 + lane
     float s[GT];
 #pragma unroll
     for (int g = 0; g < GT; ++g) s[g] = 0.f;
-    bool bad_page = false;
-    if (valid) {
-      const int page = bt[j / block_size];
-      if (page < 0 || page >= num_pages) {
-        bad_page = true;
-      } else {
-        const uint4* kp = reinterpret_cast<const uint4*>(
-            cache + (int64_t)page * page_elems + (int64_t)kvh * head_elems + (int64_t)(j % block_size) * D);
+    if (page >= 0) {
 #pragma unroll
-        for (int c = 0; c < DG; ++c) {
-          float kf[8];
-          unpack8(kp[c], kf);
+      for (int c = 0; c < DG; ++c) {
+        float kf[8];
+        unpack8(kraw[c], kf);
 #pragma unroll
-          for (int g = 0; g < GT; ++g) {
-            const float4 qa = *reinterpret_cast<const float4*>(&q_s[g][c * 8]);
-            const float4 qb = *reinterpret_cast<const float4*>(&q_s[g][c * 8 + 4]);
-            s[g] = fmaf(qa.x, kf[0], s[g]); s[g] = fmaf(qa.y, kf[1], s[g]);
-            s[g] = fmaf(qa.z, kf[2], s[g]); s[g] = fmaf(qa.w, kf[3], s[g]);
-            s[g] = fmaf(qb.x, kf[4], s[g]); s[g] = fmaf(qb.y, kf[5], s[g]);
-            s[g] = fmaf(qb.z, kf[6], s[g]); s[g] = fmaf(qb.w, kf[7], s[g]);
-          }
+        for (int g = 0; g < GT; ++g) {
+          const float4 qa = *reinterpret_cast<const float4*>(&q_s[g][c * 8]);
+          const float4 qb = *reinterpret_cast<const float4*>(&q_s[g][c * 8 + 4]);
+          s[g] = fmaf(qa.x, kf[0], s[g]); s[g] = fmaf(qa.y, kf[1], s[g]);
+          s[g] = fmaf(qa.z, kf[2], s[g]); s[g] = fmaf(qa.w, kf[3], s[g]);
+          s[g] = fmaf(qb.x, kf[4], s[g]); s[g] = fmaf(qb.y, kf[5], s[g]);
+          s[g] = fmaf(qb.z, kf[6], s[g]); s[g] = fmaf(qb.w, kf[7], s[g]);
         }
       }
     }
-    if (bad_page) atomicOr(status, GLLM_STATUS_PAGE_RANGE);
-    const bool use = valid && !bad_page;
+    const bool use = page >= 0;
     float corr[GT];
 #pragma unroll
     for (int g = 0; g < GT; ++g) {
@@ -147,22 +171,20 @@ decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride,
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[g][i] *= corr[g];
     // ---- values: each 16-byte load covers KG rows; lane (kg, dg) owns 8 dims of its rows
-#pragma unroll 2
-    for (int i = 0; i < 32 / KG; ++i) {
-      const int jj = i * KG + kg;
-      const int key = j0 + jj;
-      if (key < c0 || key >= c1) continue;
-      const int page = bt[key / block_size];
-      if (page < 0 || page >= num_pages) continue;
-      const uint4* vp = reinterpret_cast<const uint4*>(
-          cache + (int64_t)page * page_elems + v_off + (int64_t)kvh * head_elems + (int64_t)(key % block_size) * D);
-      float vf[8];
-      unpack8(vp[dg], vf);
 #pragma unroll
-      for (int g = 0; g < GT; ++g) {
-        const float p = p_s[warp][g][jj];
+    for (int first = 0; first < V_LOADS; first += V_BATCH) {
+      if (first > 0) load_values(first);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(p, vf[e], acc[g][e]);
+      for (int i = 0; i < V_BATCH; ++i) {
+        const int jj = (first + i) * KG + kg;
+        float vf[8];
+        unpack8(vraw[i], vf);
+#pragma unroll
+        for (int g = 0; g < GT; ++g) {
+          const float p = p_s[warp][g][jj];      // 0 for keys outside the chunk
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[g][e] = fmaf(p, vf[e], acc[g][e]);
+        }
       }
     }
     __syncwarp();

@@ -213,6 +213,7 @@ class StepRunner:
             max_q_len=max(q_lens),
             max_seq_len=max(seq_bucket, max(int(c) + q for c, q in zip(ctx_lens, q_lens))),
             num_prefill_tokens=n_prefill,
+            num_prefill_requests=sum(1 for n in q_lens if n > 1),
             workspace=self.workspace,
         )
         self._last_views = views

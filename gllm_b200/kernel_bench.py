@@ -1,0 +1,125 @@
+"""Single-kernel workloads: each builds synthetic inputs, runs one kernel of the
+engine a few times with an L2 flush between runs, and reports its time beside
+the bytes or flops it has to move.  ``python bench.py --kernel NAME`` runs one;
+the same command under ``ncu`` gives the profiles kept under ``profiles/``."""
+
+from __future__ import annotations
+
+import json
+import math
+
+import torch
+
+
+def _flush_l2(buf):
+    buf.zero_()
+
+
+def _time(fn, iters: int, flush) -> float:
+    """Median device time of ``fn`` in microseconds."""
+    times = []
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    for _ in range(iters):
+        _flush_l2(flush)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end) * 1e3)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def _paged_cache(batch, context, hkv, d, block_size, extra_tokens=0):
+    """A pool holding ``batch`` requests of ``context`` tokens on scattered pages."""
+    pages_per_req = -(-(context + extra_tokens) // block_size)
+    num_pages = batch * pages_per_req + 1
+    g = torch.Generator(device="cuda").manual_seed(0)
+    pool = torch.randn((num_pages, 2, hkv, block_size, d), generator=g, device="cuda", dtype=torch.float32)
+    pool = pool.to(torch.bfloat16)
+    perm = torch.randperm(num_pages - 1, generator=g, device="cuda").to(torch.int32)
+    table = perm[: batch * pages_per_req].view(batch, pages_per_req).contiguous()
+    return pool, table
+
+
+def attention_decode(batch=64, context=2048, hq=32, hkv=8, d=64, block_size=16, iters=5, peaks=None):
+    from gllm_b200.ops import attention_bf16
+
+    pool, table = _paged_cache(batch, context, hkv, d, block_size)
+    qkv = torch.randn(batch, (hq + 2 * hkv) * d, device="cuda").to(torch.bfloat16)
+    positions = torch.full((batch,), context - 1, dtype=torch.int32, device="cuda")
+    rows = torch.arange(batch, dtype=torch.int32, device="cuda")
+    out = torch.empty(batch, hq * d, dtype=torch.bfloat16, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    class _WS:
+        def __init__(self):
+            self.b = {}
+
+        def get(self, name, n, dt):
+            if name not in self.b:
+                self.b[name] = torch.empty(n, dtype=dt, device="cuda")
+            return self.b[name]
+
+    ws = _WS()
+    fn = lambda: attention_bf16.decode_attention(qkv, qkv.shape[1], pool, table, positions, rows, hq,
+                                                 1.0 / math.sqrt(d), 0, context, ws, out)
+    us = _time(fn, iters, flush)
+    nbytes = batch * context * 2 * hkv * d * 2
+    gbs = nbytes / us / 1e3
+    return {"kernel": "attention_decode (split + merge)", "us": round(us, 2), "bytes": nbytes,
+            "achieved_gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4),
+            "shape": dict(batch=batch, context=context, heads=hq, kv_heads=hkv, head_dim=d, block_size=block_size)}
+
+
+def attention_prefill(tokens=2048, context=0, hq=32, hkv=8, d=64, block_size=16, iters=5, peaks=None):
+    from gllm_b200.ops import attention_bf16
+
+    pool, table = _paged_cache(1, context + tokens, hkv, d, block_size)
+    qkv = torch.randn(tokens, (hq + 2 * hkv) * d, device="cuda").to(torch.bfloat16)
+    cu = torch.tensor([0, tokens], dtype=torch.int32, device="cuda")
+    ctx = torch.tensor([context], dtype=torch.int32, device="cuda")
+    slots = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.empty(tokens, hq * d, dtype=torch.bfloat16, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    fn = lambda: attention_bf16.prefill_attention(qkv, qkv.shape[1], pool, table, cu, ctx, slots, 1, tokens, hq,
+                                                  1.0 / math.sqrt(d), 0, out)
+    us = _time(fn, iters, flush)
+    flops = 4.0 * d * hq * (tokens * context + tokens * (tokens + 1) / 2)
+    tf = flops / us / 1e6
+    return {"kernel": "attention_prefill", "us": round(us, 2), "flops": flops, "achieved_tflops": round(tf, 1),
+            "frac_of_bf16_peak": round(tf / peaks["bf16_tflops"], 4),
+            "shape": dict(tokens=tokens, context=context, heads=hq, kv_heads=hkv, head_dim=d, block_size=block_size)}
+
+
+def linear(m=8, n=16384, k=2048, iters=5, peaks=None, out_fp32=False):
+    from gllm_b200 import ops
+
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
+    out = torch.empty(m, n, dtype=torch.float32 if out_fp32 else torch.bfloat16, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    fn = lambda: ops.linear(x, w, out_dtype=out.dtype, out=out)
+    us = _time(fn, iters, flush)
+    nbytes = (m * k + n * k) * 2 + out.numel() * out.element_size()
+    flops = 2.0 * m * n * k
+    gbs, tf = nbytes / us / 1e3, flops / us / 1e6
+    return {"kernel": "linear", "us": round(us, 2), "achieved_gbs": round(gbs, 1), "achieved_tflops": round(tf, 1),
+            "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4), "frac_of_bf16_peak": round(tf / peaks["bf16_tflops"], 4),
+            "shape": dict(m=m, n=n, k=k)}
+
+
+KERNELS = {
+    "attention_decode": attention_decode,
+    "attention_prefill": attention_prefill,
+    "linear": linear,
+}
+
+
+def run(name: str, peaks: dict, overrides: dict) -> dict:
+    if name not in KERNELS:
+        raise SystemExit(f"unknown kernel {name!r}; known: {sorted(KERNELS)}")
+    return KERNELS[name](peaks=peaks, **overrides)

@@ -19,7 +19,42 @@ P = c_void_p
 DECODE_CHUNK = 128
 _DECODE_HEAD_DIMS = (16, 32, 64, 128)
 
+_PREFILL_HEAD_DIMS = (32, 64, 128)
 _decode = None
+_prefill = None
+
+
+def _prefill_fn():
+    global _prefill
+    if _prefill is None:
+        lib = load_module("attention_prefill_bf16")
+        f = lib.gllm_attention_prefill_bf16
+        f.argtypes = [P, c_int64, P, c_int64, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                      c_float, c_int, P, P]
+        f.restype = c_int
+        _prefill = f
+    return _prefill
+
+
+def prefill_supports(head_dim: int, block_size: int) -> bool:
+    return head_dim in _PREFILL_HEAD_DIMS and (block_size * head_dim) % 8 == 0
+
+
+def prefill_attention(q, q_stride, cache_layer, block_table, cu_q, ctx_lens, slots, num_requests, max_q_len,
+                      num_heads, scale, window, out):
+    """Tensor-core attention of the first ``num_requests`` requests of the
+    flat batch (portions of prompts)."""
+    from gllm_b200 import ops
+
+    num_pages, _, hkv, block_size, d = cache_layer.shape
+    code = _prefill_fn()(
+        q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), cache_layer.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), cu_q.data_ptr(), ctx_lens.data_ptr(), slots.data_ptr(), num_requests, max_q_len,
+        num_heads, hkv, d, block_size, num_pages, float(scale), int(window),
+        ops.status_word(q.device).data_ptr(), ops._stream(),
+    )
+    ops._check(code, "attention_prefill_bf16")
+    return out
 
 
 def _decode_fn():
@@ -74,7 +109,12 @@ def paged_attention_bf16(qkv, cache_layer, block_table, positions, token_row, nu
 
     n = qkv.shape[0]
     n_pf = batch.num_prefill_tokens
-    if n_pf > 0:
+    d, block_size = cache_layer.shape[4], cache_layer.shape[3]
+    if n_pf > 0 and prefill_supports(d, block_size):
+        prefill_attention(qkv, qkv.shape[1], cache_layer, block_table, batch.cu_q, batch.context_lens,
+                          batch.state_slots, batch.num_prefill_requests, batch.max_q_len, num_heads, scale, window,
+                          out)
+    elif n_pf > 0:
         ops.paged_attention_simt(qkv[:n_pf], qkv.shape[1], cache_layer, block_table, positions[:n_pf],
                                  token_row[:n_pf], num_heads, scale, window, out[:n_pf])
     if n_pf < n:

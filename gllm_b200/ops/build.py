@@ -44,6 +44,7 @@ MODULES = {
     "sampling": "sampling.cu",
     "gemm_bf16": "gemm_bf16.cu",
     "attention_bf16": "attention_bf16.cu",
+    "attention_prefill_bf16": "attention_prefill_bf16.cu",
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

@@ -99,6 +99,7 @@ class StepContext:
     max_seq_len: int = 0
     # the flat batch holds all multi-token portions first, then the single tokens
     num_prefill_tokens: int = 0
+    num_prefill_requests: int = 0
     # device scratch the attention kernels share (owned by the step function)
     workspace: Any = None
 

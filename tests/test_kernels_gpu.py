@@ -243,7 +243,13 @@ def test_attention_mixed_batch_uses_both_kernels(ops):
     qkv[:, : hq * d] = torch.cat(qs).reshape(n, hq * d)
     from gllm_b200.engine.step import Workspace
 
-    batch = SimpleNamespace(num_prefill_tokens=52, max_seq_len=400, workspace=Workspace(torch.device("cuda")))
+    batch = SimpleNamespace(
+        num_prefill_tokens=52, num_prefill_requests=2, max_seq_len=400, max_q_len=50,
+        workspace=Workspace(torch.device("cuda")),
+        cu_q=torch.tensor([0, 50, 52, 53, 54], dtype=torch.int32).cuda(),
+        context_lens=torch.tensor([150, 88, 399, 32], dtype=torch.int32).cuda(),
+        state_slots=torch.tensor([1, 2, 3, 4], dtype=torch.int32).cuda(),
+    )
     scale = 1.0 / math.sqrt(d)
     out = ops.paged_attention(qkv.cuda(), pool.cuda(), table.cuda(), pos.cuda(), rows.cuda(), hq, scale, batch=batch)
     ops.check_status()
@@ -251,4 +257,37 @@ def test_attention_mixed_batch_uses_both_kernels(ops):
     for r, nq in enumerate(q_counts):
         want = _plain_attn(qs[r], ks[r], vs[r], pos[off:off + nq].long(), None, scale)
         torch.testing.assert_close(out[off:off + nq].double().cpu().view(nq, hq, d), want, **tol(torch.bfloat16))
+        off += nq
+
+
+@pytest.mark.parametrize("hq,hkv,d,bs,window", [
+    (4, 1, 64, 16, None), (3, 1, 32, 8, None), (32, 8, 64, 16, None), (6, 3, 128, 32, 100), (8, 8, 64, 4, 70),
+    (16, 2, 128, 16, None), (5, 5, 32, 16, 24), (64, 1, 64, 16, None),
+])
+def test_attention_prefill_tensor_cores(ops, hq, hkv, d, bs, window):
+    """Portions of prompts over a cache: a whole prompt, a portion after 250 cached tokens, two-token
+    portions, portions that end inside a page and inside a 64-key tile; the far keys carry the weight."""
+    from gllm_b200.ops import attention_bf16
+
+    g = torch.Generator().manual_seed(8)
+    lens, q_counts = [130, 300, 2, 64, 67, 451], [130, 50, 2, 2, 65, 200]
+    pool, table, ks, vs, qs, pos, rows = _paged_case(g, torch.bfloat16, lens, hq, hkv, d, bs, q_counts)
+    n = pos.numel()
+    qkv = torch.zeros(n, (hq + 2 * hkv) * d, dtype=torch.bfloat16)
+    qkv[:, : hq * d] = torch.cat(qs).reshape(n, hq * d)
+    scale = 1.0 / math.sqrt(d)
+    assert attention_bf16.prefill_supports(d, bs)
+    cu = torch.tensor([0] + list(torch.tensor(q_counts).cumsum(0)), dtype=torch.int32).cuda()
+    ctx = torch.tensor([a - b for a, b in zip(lens, q_counts)], dtype=torch.int32).cuda()
+    slots = torch.arange(1, len(lens) + 1, dtype=torch.int32).cuda()
+    out = torch.full((n, hq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    attention_bf16.prefill_attention(qkv.cuda(), qkv.shape[1], pool.cuda(), table.cuda(), cu, ctx, slots, len(lens),
+                                     max(q_counts), hq, scale, window or 0, out)
+    ops.check_status()
+    off = 0
+    for r, nq in enumerate(q_counts):
+        want = _plain_attn(qs[r], ks[r], vs[r], pos[off:off + nq].long(), window, scale)
+        got = out[off:off + nq].double().cpu().view(nq, hq, d)
+        assert not got.isnan().any(), r
+        torch.testing.assert_close(got, want, **tol(torch.bfloat16))
         off += nq

@@ -134,7 +134,7 @@ def compare(results, index, plain, tol_max, tol_mean=None):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_all_cuts(name, dtype, tmp_path):
     folder = write_tiny(name, str(tmp_path / "model"), sharp=(dtype == "float32"))
     cfg, weights = read_raw(folder, round_to_bf16=(dtype == "bfloat16"))

@@ -4,7 +4,8 @@ that write them as model folders with random weights in a temporary place.
 They differ in every size and option: layers, width, head counts and groups
 (GQA, MQA, MHA), head size, feed-forward width, vocabulary (384 and the odd
 311), rope base and scaling, eps, tied or untied head, stored dtype, norm
-weights, and (C) a bounded window on one layer.
+weights, and (C, D) a bounded window on one layer; D has the head size of 64
+that the tensor-core attention kernels are tuned for.
 """
 
 from __future__ import annotations
@@ -33,12 +34,19 @@ TINY_C = dict(
     torch_dtype="bfloat16", rope_theta=30000.0, vocab_size=311, tie_word_embeddings=True,
     sliding_window=24, layer_types=["full_attention", "sliding_attention", "full_attention"],
 )
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+TINY_D = dict(
+    architectures=["LlamaForCausalLM"], hidden_size=128, head_dim=64, intermediate_size=200, hidden_act="silu",
+    num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1, rms_norm_eps=1e-5, eos_token_id=[0],
+    torch_dtype="bfloat16", rope_theta=10000.0, vocab_size=500, tie_word_embeddings=True,
+    sliding_window=40, layer_types=["sliding_attention", "full_attention"],
+)
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 # how each one's random weights are drawn
 DRAW = {
     "A": dict(seed=11, std=0.05, norm_jitter=0.0, std_overrides={"q_proj": 0.3, "k_proj": 0.3}),
     "B": dict(seed=12, std=0.04, norm_jitter=0.1, std_overrides={"q_proj": 0.25, "k_proj": 0.25}),
     "C": dict(seed=13, std=0.05, norm_jitter=0.05, std_overrides={"q_proj": 0.3, "k_proj": 0.3}),
+    "D": dict(seed=14, std=0.04, norm_jitter=0.05, std_overrides={"q_proj": 0.2, "k_proj": 0.2}),
 }
 
 
