@@ -1,0 +1,424 @@
+// bf16 matrix product out[M, N] = X[M, K] * W[N, K]^T on the 5th-generation
+// tensor cores: tcgen05.mma with the accumulator in tensor memory, operands
+// brought into shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle),
+// fp32 accumulation.  It stands where the reference calls the library
+// (gllm/model/layers/linear.py:20, gllm/model/model.py:239).
+//
+// One CTA computes one 128 x BN accumulator tile D = A[128, K] * B[BN, K]^T:
+//   normal  (many tokens):  A = X (128 tokens),        B = W (BN = 256 weight rows)
+//   swapped (few tokens):   A = W (128 weight rows),   B = X (BN = tokens padded to 16/32/64)
+// so a decode step streams the weight through the 128-row operand and wastes
+// no tensor-core rows on padding.  Six warps: warp 0 issues the TMA loads,
+// warp 1 allocates tensor memory and issues the MMAs (one thread), warps 2-5
+// read the accumulator back with tcgen05.ld and store.  A ring of shared-memory
+// stages is handed back and forth with mbarriers; tcgen05.commit releases a
+// stage when the MMAs that read it are done.
+//
+// Narrow weights are cut along K into S splits (S from (N, K) only, never from
+// M); each CTA writes its fp32 tile to scratch and takes a ticket, and the CTA
+// that draws the last ticket of a tile sums the splits in ascending order, so
+// no CTA waits for another and a token's result does not depend on its batch.
+//
+// Every wait on an mbarrier is bounded: when it runs out, the kernel sets a
+// status bit, stops issuing work, lets its copies in flight land (bounded
+// again), frees its tensor memory and returns.
+//
+// No TMA load here uses cluster multicast; every CTA fetches its own tiles.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+constexpr int BM = 128;          // rows of the accumulator tile (MMA M)
+constexpr int BK = 64;           // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr int SMEM_BUDGET = 200 * 1024;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long global_timer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait: false (and a status bit) when the phase does not complete in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 1023u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer() - t0 > WAIT_LIMIT_NS) {
+        atomicOr(status, GLLM_STATUS_WAIT_TIMEOUT);
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle,
+// 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;                 // leading byte offset (unused with a swizzled K-major tile)
+  d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                 // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor of kind::f16: bf16 x bf16 -> fp32, both operands K-major.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <typename OutT> __device__ __forceinline__ OutT cast_out(float v);
+template <> __device__ __forceinline__ float cast_out<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 cast_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <int BN>
+struct Shape {
+  static constexpr int STAGE_A = BM * BK * 2;
+  static constexpr int STAGE_B = BN * BK * 2;
+  static constexpr int STAGE = STAGE_A + ((STAGE_B + 1023) / 1024) * 1024;   // keeps every tile 1024-aligned
+  static constexpr int STAGES = (SMEM_BUDGET / STAGE) > 8 ? 8 : (SMEM_BUDGET / STAGE);
+  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;                        // a power of two >= 32
+  static constexpr int SMEM = STAGES * STAGE + 1024;                         // + slack to align the base
+};
+
+// SWAPPED = false: A = X (tile rows are tokens), B = W (tile columns are weight rows).
+// SWAPPED = true : A = W (tile rows are weight rows), B = X (tile columns are tokens).
+template <int BN, bool SWAPPED, typename OutT>
+__global__ void __launch_bounds__(THREADS, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 OutT* __restrict__ out, int M, int N, int K, int64_t ldo, int splits, int kb_per_split,
+                 float* __restrict__ partial, int* __restrict__ tickets, int* __restrict__ status) {
+  using S = Shape<BN>;
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ __align__(8) uint64_t full_bar[S::STAGES], empty_bar[S::STAGES], tmem_full_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag, is_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t tiles = smem_addr(smem_dyn);
+  const uint32_t tile_base = (tiles + 1023u) & ~1023u;
+  const int a_row0 = blockIdx.x * BM;        // first row of A this CTA covers
+  const int b_row0 = blockIdx.y * BN;        // first row of B this CTA covers
+  const int split = blockIdx.z;
+  const int num_kb_total = (K + BK - 1) / BK;
+  const int kb_begin = split * kb_per_split;
+  const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
+  const int num_kb = max(0, kb_end - kb_begin);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S::STAGES; ++s) {
+      mbar_init(smem_addr(&full_bar[s]), 1);
+      mbar_init(smem_addr(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_addr(&tmem_full_bar), 1);
+    abort_flag = 0;
+    is_last = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)),
+                 "r"((uint32_t)S::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % S::STAGES;
+        const uint32_t round = (uint32_t)(i / S::STAGES);
+        if (!mbar_wait(smem_addr(&empty_bar[s]), (round & 1u) ^ 1u, status, &abort_flag)) break;
+        const uint32_t bar = smem_addr(&full_bar[s]);
+        mbar_expect_tx(bar, (uint32_t)(S::STAGE_A + S::STAGE_B));
+        const uint32_t dst = tile_base + (uint32_t)s * S::STAGE;
+        const int k = (kb_begin + i) * BK;
+        tma_load_2d(dst, &map_a, k, a_row0, bar);
+        tma_load_2d(dst + S::STAGE_A, &map_b, k, b_row0, bar);
+        issued = i + 1;
+      }
+      if (abort_flag) {
+        // let the copies already issued land before the CTA leaves (bounded)
+        for (int i = max(0, issued - S::STAGES); i < issued; ++i) {
+          const unsigned long long t0 = global_timer();
+          while (!mbar_try_wait(smem_addr(&full_bar[i % S::STAGES]), (uint32_t)(i / S::STAGES) & 1u)) {
+            if (global_timer() - t0 > WAIT_LIMIT_NS) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc(BM, BN);
+      bool ok = true;
+      for (int i = 0; i < num_kb && ok; ++i) {
+        const int s = i % S::STAGES;
+        ok = mbar_wait(smem_addr(&full_bar[s]), (uint32_t)(i / S::STAGES) & 1u, status, &abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = tile_base + (uint32_t)s * S::STAGE;
+        const uint32_t b_addr = a_addr + S::STAGE_A;
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          umma_bf16(tmem_base, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
+                    (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_addr(&empty_bar[s]));      // the stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(smem_addr(&tmem_full_bar));   // the accumulator is complete
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quarter = warp & 3;                   // the TMEM lanes this warp may read: 32*quarter ..
+    const int row = quarter * 32 + lane;            // row of the accumulator tile
+    bool ok = true;
+    if (num_kb > 0) ok = mbar_wait(smem_addr(&tmem_full_bar), 0u, status, &abort_flag);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      float* mine = partial + (int64_t)split * M * N;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float v[16];
+        if (num_kb > 0) {
+          tmem_ld16(taddr + (uint32_t)c, v);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        }
+        if (!SWAPPED) {
+          const int m = a_row0 + row, n0 = b_row0 + c;
+          if (m < M && n0 < N) {
+            if (splits > 1) {
+              for (int i = 0; i < 16 && n0 + i < N; ++i) mine[(int64_t)m * N + n0 + i] = v[i];
+            } else {
+              OutT* dst = out + (int64_t)m * ldo + n0;
+              if (n0 + 16 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+                if (sizeof(OutT) == 2) {
+                  uint4 p0, p1;
+                  __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&p0);
+                  __nv_bfloat162* h1 = reinterpret_cast<__nv_bfloat162*>(&p1);
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    h0[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                    h1[i] = __floats2bfloat162_rn(v[8 + 2 * i], v[8 + 2 * i + 1]);
+                  }
+                  reinterpret_cast<uint4*>(dst)[0] = p0;
+                  reinterpret_cast<uint4*>(dst)[1] = p1;
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 4; ++i)
+                    reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                }
+              } else {
+                for (int i = 0; i < 16 && n0 + i < N; ++i) dst[i] = cast_out<OutT>(v[i]);
+              }
+            }
+          }
+        } else {
+          const int n = a_row0 + row;               // weight row
+          if (n < N) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int m = b_row0 + c + i;         // token
+              if (m < M) {
+                if (splits > 1) mine[(int64_t)m * N + n] = v[i];
+                else out[(int64_t)m * ldo + n] = cast_out<OutT>(v[i]);
+              }
+            }
+          }
+        }
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS)
+                 : "memory");
+  }
+  if (splits == 1) return;
+
+  // ---- the CTA that draws the last ticket of this tile sums the splits in ascending order
+  __threadfence();
+  __syncthreads();
+  const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
+  if (threadIdx.x == 0) is_last = (atomicAdd(&tickets[tile_id], 1) == splits - 1);
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  const int m0 = SWAPPED ? b_row0 : a_row0, n0 = SWAPPED ? a_row0 : b_row0;
+  const int rows = min(SWAPPED ? BN : BM, M - m0), cols = min(SWAPPED ? BM : BN, N - n0);
+  for (int idx = threadIdx.x; idx < rows * cols; idx += THREADS) {
+    const int m = m0 + idx / cols, n = n0 + idx % cols;
+    float sum = 0.f;
+    for (int s = 0; s < splits; ++s) sum += __ldcg(partial + ((int64_t)s * M + m) * N + n);
+    out[(int64_t)m * ldo + n] = cast_out<OutT>(sum);
+  }
+  if (threadIdx.x == 0) tickets[tile_id] = 0;
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A [rows, cols] bf16 matrix with `ld` elements between rows; boxes of 64 columns x box_rows rows.
+bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int64_t ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, bool SWAPPED, typename OutT>
+int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int64_t ldx,
+                int64_t ldw, int64_t ldo, int splits, float* partial, int* tickets, int* status,
+                cudaStream_t stream) {
+  using S = Shape<BN>;
+  CUtensorMap map_a, map_b;
+  const bool ok = SWAPPED ? (make_map(&map_a, W, N, K, ldw, BM) && make_map(&map_b, X, M, K, ldx, BN))
+                          : (make_map(&map_a, X, M, K, ldx, BM) && make_map(&map_b, W, N, K, ldw, BN));
+  if (!ok) return (int)cudaErrorInvalidValue;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<BN, SWAPPED, OutT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const int a_rows = SWAPPED ? N : M, b_rows = SWAPPED ? M : N;
+  const int num_kb = (K + BK - 1) / BK;
+  const int kb_per_split = (num_kb + splits - 1) / splits;
+  dim3 grid((a_rows + BM - 1) / BM, (b_rows + BN - 1) / BN, splits);
+  umma_gemm_kernel<BN, SWAPPED, OutT><<<grid, THREADS, S::SMEM, stream>>>(map_a, map_b, out, M, N, K, ldo, splits,
+                                                                         kb_per_split, partial, tickets, status);
+  return gllm_launch_result();
+}
+
+template <typename OutT>
+int umma_dispatch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int64_t ldx,
+                  int64_t ldw, int64_t ldo, int splits, float* partial, int* tickets, int* status,
+                  cudaStream_t stream) {
+#define GLLM_UMMA(BN, SW) \
+  return umma_launch<BN, SW, OutT>(X, W, out, M, N, K, ldx, ldw, ldo, splits, partial, tickets, status, stream)
+  if (M <= 16) GLLM_UMMA(16, true);
+  if (M <= 32) GLLM_UMMA(32, true);
+  if (M <= 64) GLLM_UMMA(64, true);
+  GLLM_UMMA(256, false);
+#undef GLLM_UMMA
+}
+}  // namespace
+
+// Splits along K for an [N, K] weight and M tokens' orientation; from (N, K) and the
+// orientation only (few tokens: M <= 64), never from M itself.
+GLLM_API int gllm_gemm_bf16_splits(int few_tokens, int N, int K) {
+  if (!few_tokens) return 1;
+  const int tiles = (N + BM - 1) / BM;
+  const int num_kb = (K + BK - 1) / BK;
+  int s = 1;
+  while (s < 16 && tiles * s < 148 && num_kb / (2 * s) >= 4) s *= 2;
+  return s;
+}
+
+// Output tiles of the launch (the ticket array needs this many zeroed ints when splits > 1).
+GLLM_API int gllm_gemm_bf16_tiles(int M, int N) {
+  if (M <= 64) return (N + BM - 1) / BM;
+  return ((M + BM - 1) / BM) * ((N + 255) / 256);
+}
+
+// out_is_f32: 0 = bf16 output, 1 = fp32 output.  Needs K % 8 == 0 and 16-byte aligned rows of X and W.
+// partial: splits * M * N floats of scratch when splits > 1; tickets: zeroed ints (left at zero).
+GLLM_API int gllm_gemm_bf16(const __nv_bfloat16* X, const __nv_bfloat16* W, void* out, int out_is_f32, int M,
+                            int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int splits, float* partial,
+                            int* tickets, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || splits < 1 || splits > 16 ||
+      (reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
+    return (int)cudaErrorInvalidValue;
+  if (out_is_f32)
+    return umma_dispatch<float>(X, W, (float*)out, M, N, K, ldx, ldw, ldo, splits, partial, tickets, status, stream);
+  return umma_dispatch<__nv_bfloat16>(X, W, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, splits, partial, tickets,
+                                      status, stream);
+}

@@ -23,6 +23,8 @@ def _time(fn, iters: int, flush) -> float:
     torch.cuda.synchronize()
     for _ in range(iters):
         _flush_l2(flush)
+        # keep the GPU busy while the host queues the launches, so the events bracket device time only
+        torch.cuda._sleep(400_000)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         fn()

@@ -15,9 +15,7 @@ import torch
 from gllm_b200.ops.build import load_module
 
 P = c_void_p
-# keys per split of the decode kernel; fixed, so the cut depends on positions only
-DECODE_CHUNK = 128
-_DECODE_HEAD_DIMS = (16, 32, 64, 128)
+_DECODE_HEAD_DIMS = (32, 64, 128)
 
 _PREFILL_HEAD_DIMS = (32, 64, 128)
 _decode = None
@@ -62,11 +60,19 @@ def _decode_fn():
     if _decode is None:
         lib = load_module("attention_bf16")
         f = lib.gllm_attention_decode_bf16
-        f.argtypes = [P, c_int64, P, c_int64, P, P, c_int, P, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,
-                      c_int, c_int, c_float, c_int, P, P]
+        f.argtypes = [P, c_int64, P, c_int64, P, P, c_int, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,
+                      c_int, c_float, c_int, P, P]
         f.restype = c_int
-        _decode = f
+        lib.gllm_attention_decode_chunk.argtypes = [c_int]
+        lib.gllm_attention_decode_chunk.restype = c_int
+        _decode = (f, lib.gllm_attention_decode_chunk)
     return _decode
+
+
+def decode_chunk(head_dim: int) -> int:
+    """Keys per split of the decode kernel for this head size: a constant, so
+    the cut of a request's keys depends on positions only."""
+    return _decode_fn()[1](head_dim)
 
 
 def supports(head_dim: int, block_size: int) -> bool:
@@ -75,7 +81,7 @@ def supports(head_dim: int, block_size: int) -> bool:
 
 def decode_scratch_elems(num_queries: int, num_heads: int, head_dim: int, max_seq_len: int) -> tuple[int, int, int]:
     """(num_chunks, floats of partial outputs, floats of partial max/sum)."""
-    chunks = max(1, -(-max_seq_len // DECODE_CHUNK))
+    chunks = max(1, -(-max_seq_len // decode_chunk(head_dim)))
     return chunks, num_queries * num_heads * chunks * head_dim, num_queries * num_heads * chunks * 2
 
 
@@ -93,10 +99,10 @@ def decode_attention(q, q_stride, cache_layer, block_table, positions, token_row
     else:
         part_o = torch.empty(n_o, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(n_ml, dtype=torch.float32, device=q.device)
-    code = _decode_fn()(
+    code = _decode_fn()[0](
         q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), cache_layer.data_ptr(), block_table.data_ptr(),
-        block_table.stride(0), positions.data_ptr(), token_row.data_ptr(), None, n, part_o.data_ptr(),
-        part_ml.data_ptr(), num_heads, hkv, d, block_size, num_pages, DECODE_CHUNK, chunks, float(scale),
+        block_table.stride(0), positions.data_ptr(), token_row.data_ptr(), n, part_o.data_ptr(),
+        part_ml.data_ptr(), num_heads, hkv, d, block_size, num_pages, chunks, float(scale),
         int(window), ops.status_word(q.device).data_ptr(), ops._stream(),
     )
     ops._check(code, "attention_decode_bf16")

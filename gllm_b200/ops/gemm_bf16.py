@@ -1,22 +1,35 @@
 """bf16 matrix products ``x @ W.T`` with fp32 accumulation.
 
-Two backends stand behind ``linear_bf16``: the engine's own tcgen05 kernels
-(``csrc/gemm_bf16.cu``) and the library product (cuBLAS through
-``torch.matmul``), which is what the reference itself uses for every
-projection (gllm/model/layers/linear.py:20).  ``set_backend`` chooses.
+The engine's own kernel (``csrc/gemm_bf16.cu``: tcgen05.mma, accumulator in
+tensor memory, operands by TMA) runs every product whose rows are 16-byte
+aligned and whose inner size is a multiple of 8; decode steps (M <= 64) run it
+with the weight as the 128-row operand and split along K.  Anything else (odd
+inner sizes) goes to the library product (cuBLAS through ``torch.matmul``),
+which is what the reference uses for every projection
+(gllm/model/layers/linear.py:20).  ``set_backend("library")`` sends everything
+there, for comparisons.
 """
 
 from __future__ import annotations
 
+from ctypes import c_int, c_int64, c_void_p
+
 import torch
 
-_BACKEND = "library"
+from gllm_b200.ops.build import load_module
+
+P = c_void_p
+FEW_TOKENS = 64
+
+_BACKEND = "tcgen05"
+_umma = None
+_scratch: dict[int, dict[str, torch.Tensor]] = {}
 
 
 def set_backend(name: str) -> None:
     global _BACKEND
-    if name not in ("library", "tcgen05"):
-        raise ValueError("backend must be 'library' or 'tcgen05'")
+    if name not in ("tcgen05", "library"):
+        raise ValueError("backend must be 'tcgen05' or 'library'")
     _BACKEND = name
 
 
@@ -24,7 +37,57 @@ def get_backend() -> str:
     return _BACKEND
 
 
+def _umma_fns():
+    global _umma
+    if _umma is None:
+        lib = load_module("gemm_bf16")
+        f = lib.gllm_gemm_bf16
+        f.argtypes = [P, P, P, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, P, P, P, P]
+        f.restype = c_int
+        lib.gllm_gemm_bf16_splits.argtypes = [c_int, c_int, c_int]
+        lib.gllm_gemm_bf16_splits.restype = c_int
+        lib.gllm_gemm_bf16_tiles.argtypes = [c_int, c_int]
+        lib.gllm_gemm_bf16_tiles.restype = c_int
+        _umma = (f, lib.gllm_gemm_bf16_splits, lib.gllm_gemm_bf16_tiles)
+    return _umma
+
+
+def _device_scratch(device: torch.device, partial_floats: int, tickets: int):
+    """Per-device scratch of the split-K reduction: fp32 partial tiles and the
+    ticket counters (zeroed once; the kernel leaves them at zero)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    s = _scratch.setdefault(idx, {})
+    if "tickets" not in s or s["tickets"].numel() < tickets:
+        s["tickets"] = torch.zeros(max(tickets, 4096), dtype=torch.int32, device=device)
+    if "partial" not in s or s["partial"].numel() < partial_floats:
+        s["partial"] = torch.empty(max(partial_floats, 1 << 22), dtype=torch.float32, device=device)
+    return s["partial"], s["tickets"]
+
+
+def tensor_core_kernel_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    k = x.shape[1]
+    return (k % 8 == 0 and x.stride(1) == 1 and weight.stride(1) == 1 and x.stride(0) % 8 == 0
+            and weight.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    from gllm_b200 import ops
+
+    f, splits_of, tiles_of = _umma_fns()
+    m, k = x.shape
+    n = weight.shape[0]
+    splits = splits_of(int(m <= FEW_TOKENS), n, k)
+    partial, tickets = _device_scratch(x.device, splits * m * n if splits > 1 else 0, tiles_of(m, n))
+    code = f(x.data_ptr(), weight.data_ptr(), out.data_ptr(), int(out.dtype == torch.float32), m, n, k,
+             x.stride(0), weight.stride(0), out.stride(0), splits, partial.data_ptr(), tickets.data_ptr(),
+             ops.status_word(x.device).data_ptr(), ops._stream())
+    ops._check(code, "gemm_bf16")
+    return out
+
+
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    if _BACKEND == "tcgen05" and tensor_core_kernel_takes(x, weight):
+        return linear_tcgen05(x, weight, out)
     if out.dtype == torch.bfloat16:
         torch.matmul(x, weight.t(), out=out)
     else:

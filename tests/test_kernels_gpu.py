@@ -203,16 +203,16 @@ def test_attention_simt(ops, dtype, hq, hkv, d, bs, window):
 
 
 @pytest.mark.parametrize("hq,hkv,d,bs,window", [
-    (4, 2, 16, 4, None), (3, 1, 32, 8, None), (5, 5, 16, 16, 24), (32, 8, 64, 16, None), (6, 3, 128, 32, 100),
-    (16, 1, 64, 16, None), (12, 2, 128, 16, 300), (7, 7, 64, 8, None),
+    (4, 2, 32, 4, None), (3, 1, 32, 8, None), (5, 5, 32, 16, 24), (32, 8, 64, 16, None), (6, 3, 128, 32, 100),
+    (16, 1, 64, 16, None), (12, 2, 128, 16, 300), (7, 7, 64, 8, None), (40, 2, 64, 16, None),
 ])
 def test_attention_decode_split_kv(ops, hq, hkv, d, bs, window):
-    """One query token per request over caches of 1 .. 1500 tokens: several chunks of 128 keys, a chunk
+    """One query token per request over caches of 1 .. 1500 tokens: several chunks of keys (128 or 256 by head size), a chunk
     that holds a single key, windows that start inside a chunk; the far keys carry the weight."""
     from gllm_b200.ops import attention_bf16
 
     g = torch.Generator().manual_seed(6)
-    lens = [1, 37, 128, 129, 300, 1500, 64]
+    lens = [1, 37, 128, 129, 300, 1500, 64, 256, 257]
     pool, table, ks, vs, qs, pos, rows = _paged_case(g, torch.bfloat16, lens, hq, hkv, d, bs, [1] * len(lens))
     n = pos.numel()
     qkv = torch.zeros(n, (hq + 2 * hkv) * d, dtype=torch.bfloat16)
@@ -291,3 +291,40 @@ def test_attention_prefill_tensor_cores(ops, hq, hkv, d, bs, window):
         assert not got.isnan().any(), r
         torch.testing.assert_close(got, want, **tol(torch.bfloat16))
         off += nq
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 311, 72), (8, 3072, 2048), (7, 96, 160), (13, 2048, 8192), (33, 1000, 520),
+                                   (64, 16384, 2048), (50, 130, 104), (3, 128256, 256), (65, 520, 200),
+                                   (128, 256, 64), (300, 777, 1000), (2048, 3072, 2048), (1000, 16384, 2048)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_bf16_tensor_memory(ops, m, n, k, out_dtype):
+    """The tcgen05 product in both orientations: few tokens (the weight is the 128-row operand, split
+    along K with the last-ticket reduction: 3072x2048, 2048x8192) and many tokens; tails in M, N and K;
+    twice in a row (the tickets return to zero)."""
+    from gllm_b200.ops import gemm_bf16
+
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).cuda()
+    assert gemm_bf16.get_backend() == "tcgen05" and gemm_bf16.tensor_core_kernel_takes(x, w)
+    want = x.double() @ w.double().T
+    for _ in range(2):
+        got = ops.linear(x, w, out_dtype=out_dtype)
+        ops.check_status()
+        assert got.dtype == out_dtype
+        if out_dtype == torch.float32:
+            torch.testing.assert_close(got.double(), want, rtol=1e-4, atol=1e-4)
+        else:
+            torch.testing.assert_close(got.double(), want, rtol=1e-2, atol=1e-2)
+    if m <= 64:
+        # a token's result does not depend on the rest of the batch: bitwise
+        alone = ops.linear(x[m // 2:m // 2 + 1].contiguous(), w, out_dtype=out_dtype)
+        assert torch.equal(alone[0], got[m // 2])
+
+
+def test_gemm_bf16_odd_inner_size_goes_to_the_library(ops):
+    g = torch.Generator().manual_seed(10)
+    x = torch.randn(5, 100, generator=g).to(torch.bfloat16).cuda()
+    w = torch.randn(37, 100, generator=g).to(torch.bfloat16).cuda()
+    got = ops.linear(x, w)
+    torch.testing.assert_close(got.double(), x.double() @ w.double().T, rtol=2e-2, atol=2e-2)
