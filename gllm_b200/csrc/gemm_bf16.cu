@@ -4,7 +4,8 @@
 // fp32 accumulation.  It stands where the reference calls the library
 // (gllm/model/layers/linear.py:20, gllm/model/model.py:239).
 //
-// One CTA computes one 128 x BN accumulator tile D = A[128, K] * B[BN, K]^T:
+// The kernel is persistent: one CTA per SM walks over work items, each a
+// 128 x BN accumulator tile D = A[128, K] * B[BN, K]^T (times a range of K):
 //   normal  (many tokens):  A = X (128 tokens),        B = W (BN = 256 weight rows)
 //   swapped (few tokens):   A = W (128 weight rows),   B = X (BN = tokens padded to 16/32/64)
 // so a decode step streams the weight through the 128-row operand and wastes
@@ -12,12 +13,15 @@
 // warp 1 allocates tensor memory and issues the MMAs (one thread), warps 2-5
 // read the accumulator back with tcgen05.ld and store.  A ring of shared-memory
 // stages is handed back and forth with mbarriers; tcgen05.commit releases a
-// stage when the MMAs that read it are done.
+// stage when the MMAs that read it are done.  Tensor memory holds two
+// accumulators, so the loads and MMAs of the next item run while the epilogue
+// warps drain the previous one.
 //
-// Narrow weights are cut along K into S splits (S from (N, K) only, never from
-// M); each CTA writes its fp32 tile to scratch and takes a ticket, and the CTA
-// that draws the last ticket of a tile sums the splits in ascending order, so
-// no CTA waits for another and a token's result does not depend on its batch.
+// With few tokens a weight is cut along K into S splits (S from (N, K) and the
+// bucket M falls in: <= 16, <= 32, <= 64); each item writes its fp32 tile to
+// scratch and takes a ticket, and the one that draws the last ticket of a tile
+// sums the splits in ascending order, so no CTA waits for another and, within a
+// bucket, a token's result does not depend on its batch.
 //
 // Every wait on an mbarrier is bounded: when it runs out, the kernel sets a
 // status bit, stops issuing work, lets its copies in flight land (bounded
@@ -134,9 +138,31 @@ struct Shape {
   static constexpr int STAGE_B = BN * BK * 2;
   static constexpr int STAGE = STAGE_A + ((STAGE_B + 1023) / 1024) * 1024;   // keeps every tile 1024-aligned
   static constexpr int STAGES = (SMEM_BUDGET / STAGE) > 8 ? 8 : (SMEM_BUDGET / STAGE);
-  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;                        // a power of two >= 32
+  static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;                // two accumulators; a power of two >= 32
   static constexpr int SMEM = STAGES * STAGE + 1024;                         // + slack to align the base
 };
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+struct Item {
+  int a_row0, b_row0, split, tile_id;
+};
+// Work item w of a launch.  Normal: neighbouring CTAs share a weight tile.  Swapped:
+// neighbouring CTAs take the K ranges of the same weight rows.
+template <int BN, bool SWAPPED>
+__device__ __forceinline__ Item item_of(int w, int tiles_a, int splits) {
+  Item it;
+  const int t = w / splits;
+  it.split = w - t * splits;
+  const int tb = t / tiles_a, ta = t - tb * tiles_a;
+  it.a_row0 = ta * BM;
+  it.b_row0 = tb * BN;
+  it.tile_id = t;
+  return it;
+}
 
 // SWAPPED = false: A = X (tile rows are tokens), B = W (tile columns are weight rows).
 // SWAPPED = true : A = W (tile rows are weight rows), B = X (tile columns are tokens).
@@ -144,30 +170,27 @@ template <int BN, bool SWAPPED, typename OutT>
 __global__ void __launch_bounds__(THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  OutT* __restrict__ out, int M, int N, int K, int64_t ldo, int splits, int kb_per_split,
-                 float* __restrict__ partial, int* __restrict__ tickets, int* __restrict__ status) {
+                 int tiles_a, int num_items, float* __restrict__ partial, int* __restrict__ tickets,
+                 int* __restrict__ status) {
   using S = Shape<BN>;
   extern __shared__ unsigned char smem_dyn[];
-  __shared__ __align__(8) uint64_t full_bar[S::STAGES], empty_bar[S::STAGES], tmem_full_bar;
+  __shared__ __align__(8) uint64_t full_bar[S::STAGES], empty_bar[S::STAGES], tmem_full_bar[2], tmem_empty_bar[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag, is_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t tiles = smem_addr(smem_dyn);
-  const uint32_t tile_base = (tiles + 1023u) & ~1023u;
-  const int a_row0 = blockIdx.x * BM;        // first row of A this CTA covers
-  const int b_row0 = blockIdx.y * BN;        // first row of B this CTA covers
-  const int split = blockIdx.z;
+  const uint32_t tile_base = (smem_addr(smem_dyn) + 1023u) & ~1023u;
   const int num_kb_total = (K + BK - 1) / BK;
-  const int kb_begin = split * kb_per_split;
-  const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
-  const int num_kb = max(0, kb_end - kb_begin);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S::STAGES; ++s) {
       mbar_init(smem_addr(&full_bar[s]), 1);
       mbar_init(smem_addr(&empty_bar[s]), 1);
     }
-    mbar_init(smem_addr(&tmem_full_bar), 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_addr(&tmem_full_bar[b]), 1);
+      mbar_init(smem_addr(&tmem_empty_bar[b]), 4);      // one arrival per epilogue warp
+    }
     abort_flag = 0;
     is_last = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -186,24 +209,29 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      int issued = 0;
-      for (int i = 0; i < num_kb; ++i) {
-        const int s = i % S::STAGES;
-        const uint32_t round = (uint32_t)(i / S::STAGES);
-        if (!mbar_wait(smem_addr(&empty_bar[s]), (round & 1u) ^ 1u, status, &abort_flag)) break;
-        const uint32_t bar = smem_addr(&full_bar[s]);
-        mbar_expect_tx(bar, (uint32_t)(S::STAGE_A + S::STAGE_B));
-        const uint32_t dst = tile_base + (uint32_t)s * S::STAGE;
-        const int k = (kb_begin + i) * BK;
-        tma_load_2d(dst, &map_a, k, a_row0, bar);
-        tma_load_2d(dst + S::STAGE_A, &map_b, k, b_row0, bar);
-        issued = i + 1;
+      uint32_t it = 0;                                   // k-blocks issued so far, over all items
+      bool ok = true;
+      for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
+        const Item item = item_of<BN, SWAPPED>(w, tiles_a, splits);
+        const int kb_begin = item.split * kb_per_split;
+        const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+          const uint32_t s = it % S::STAGES, round = it / S::STAGES;
+          ok = mbar_wait(smem_addr(&empty_bar[s]), (round & 1u) ^ 1u, status, &abort_flag);
+          if (!ok) break;
+          const uint32_t bar = smem_addr(&full_bar[s]);
+          mbar_expect_tx(bar, (uint32_t)(S::STAGE_A + S::STAGE_B));
+          const uint32_t dst = tile_base + s * S::STAGE;
+          tma_load_2d(dst, &map_a, kb * BK, item.a_row0, bar);
+          tma_load_2d(dst + S::STAGE_A, &map_b, kb * BK, item.b_row0, bar);
+        }
       }
       if (abort_flag) {
         // let the copies already issued land before the CTA leaves (bounded)
-        for (int i = max(0, issued - S::STAGES); i < issued; ++i) {
+        const uint32_t first = it > (uint32_t)S::STAGES ? it - S::STAGES : 0u;
+        for (uint32_t i = first; i < it; ++i) {
           const unsigned long long t0 = global_timer();
-          while (!mbar_try_wait(smem_addr(&full_bar[i % S::STAGES]), (uint32_t)(i / S::STAGES) & 1u)) {
+          while (!mbar_try_wait(smem_addr(&full_bar[i % S::STAGES]), (i / S::STAGES) & 1u)) {
             if (global_timer() - t0 > WAIT_LIMIT_NS) break;
           }
         }
@@ -213,44 +241,69 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(BM, BN);
+      uint32_t it = 0, n_used = 0;                       // k-blocks consumed; accumulators handed over
       bool ok = true;
-      for (int i = 0; i < num_kb && ok; ++i) {
-        const int s = i % S::STAGES;
-        ok = mbar_wait(smem_addr(&full_bar[s]), (uint32_t)(i / S::STAGES) & 1u, status, &abort_flag);
+      for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
+        const Item item = item_of<BN, SWAPPED>(w, tiles_a, splits);
+        const int kb_begin = item.split * kb_per_split;
+        const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
+        if (kb_end <= kb_begin) continue;                // an empty K range: the epilogue writes zeros
+        const uint32_t acc = n_used & 1u;
+        // the epilogue must have drained this accumulator (two uses ago)
+        ok = mbar_wait(smem_addr(&tmem_empty_bar[acc]), ((n_used >> 1) & 1u) ^ 1u, status, &abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_addr = tile_base + (uint32_t)s * S::STAGE;
-        const uint32_t b_addr = a_addr + S::STAGE_A;
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+          const uint32_t s = it % S::STAGES;
+          ok = mbar_wait(smem_addr(&full_bar[s]), (it / S::STAGES) & 1u, status, &abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = tile_base + s * S::STAGE;
+          const uint32_t b_addr = a_addr + S::STAGE_A;
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          umma_bf16(tmem_base, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
-                    (i > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            umma_bf16(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
+                      (kb > kb_begin || k > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_addr(&empty_bar[s]));         // the stage is free once these MMAs have read it
         }
-        umma_commit(smem_addr(&empty_bar[s]));      // the stage is free once these MMAs have read it
+        if (ok) umma_commit(smem_addr(&tmem_full_bar[acc]));   // the accumulator is complete
+        ++n_used;
       }
-      if (ok) umma_commit(smem_addr(&tmem_full_bar));   // the accumulator is complete
     }
   } else {
     // ---------------------------------------------------------------- epilogue
-    const int quarter = warp & 3;                   // the TMEM lanes this warp may read: 32*quarter ..
-    const int row = quarter * 32 + lane;            // row of the accumulator tile
-    bool ok = true;
-    if (num_kb > 0) ok = mbar_wait(smem_addr(&tmem_full_bar), 0u, status, &abort_flag);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (ok) {
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-      float* mine = partial + (int64_t)split * M * N;
+    const int quarter = warp & 3;                        // the TMEM lanes this warp may read: 32*quarter ..
+    const int row = quarter * 32 + lane;                 // row of the accumulator tile
+    const int ep_thread = (warp - 2) * 32 + lane;        // 0 .. 127
+    uint32_t n_used = 0;
+    for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
+      const Item item = item_of<BN, SWAPPED>(w, tiles_a, splits);
+      const int kb_begin = item.split * kb_per_split;
+      const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
+      const bool has_k = kb_end > kb_begin;
+      const uint32_t acc = n_used & 1u;
+      if (has_k) {
+        mbar_wait(smem_addr(&tmem_full_bar[acc]), (n_used >> 1) & 1u, status, &abort_flag);
+        // the four warps leave together: one that gave up has set abort_flag before this barrier
+        epilogue_sync();
+        if (abort_flag) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      }
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+      float* mine = partial + (int64_t)item.split * M * N;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 16) {
         float v[16];
-        if (num_kb > 0) {
+        if (has_k) {
           tmem_ld16(taddr + (uint32_t)c, v);
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0.f;
         }
         if (!SWAPPED) {
-          const int m = a_row0 + row, n0 = b_row0 + c;
+          const int m = item.a_row0 + row, n0 = item.b_row0 + c;
           if (m < M && n0 < N) {
             if (splits > 1) {
               for (int i = 0; i < 16 && n0 + i < N; ++i) mine[(int64_t)m * N + n0 + i] = v[i];
@@ -279,11 +332,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
           }
         } else {
-          const int n = a_row0 + row;               // weight row
+          const int n = item.a_row0 + row;               // weight row
           if (n < N) {
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-              const int m = b_row0 + c + i;         // token
+              const int m = item.b_row0 + c + i;         // token
               if (m < M) {
                 if (splits > 1) mine[(int64_t)m * N + n] = v[i];
                 else out[(int64_t)m * ldo + n] = cast_out<OutT>(v[i]);
@@ -291,6 +344,33 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
           }
         }
+      }
+      if (has_k) {
+        // this warp is done reading the accumulator: hand it back to the MMA warp
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_addr(&tmem_empty_bar[acc]));
+        ++n_used;
+      }
+      if (splits > 1) {
+        // the CTA that draws the last ticket of this tile sums the splits in ascending order
+        __threadfence();
+        epilogue_sync();
+        if (ep_thread == 0) is_last = (atomicAdd(&tickets[item.tile_id], 1) == splits - 1);
+        epilogue_sync();
+        if (is_last) {
+          __threadfence();
+          const int m0 = SWAPPED ? item.b_row0 : item.a_row0, n0 = SWAPPED ? item.a_row0 : item.b_row0;
+          const int rows = min(SWAPPED ? BN : BM, M - m0), cols = min(SWAPPED ? BM : BN, N - n0);
+          for (int idx = ep_thread; idx < rows * cols; idx += 128) {
+            const int m = m0 + idx / cols, n = n0 + idx % cols;
+            float sum = 0.f;
+            for (int s = 0; s < splits; ++s) sum += __ldcg(partial + ((int64_t)s * M + m) * N + n);
+            out[(int64_t)m * ldo + n] = cast_out<OutT>(sum);
+          }
+          if (ep_thread == 0) tickets[item.tile_id] = 0;
+        }
+        epilogue_sync();                                 // is_last is rewritten for the next item
       }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -301,25 +381,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS)
                  : "memory");
   }
-  if (splits == 1) return;
-
-  // ---- the CTA that draws the last ticket of this tile sums the splits in ascending order
-  __threadfence();
-  __syncthreads();
-  const int tile_id = blockIdx.y * gridDim.x + blockIdx.x;
-  if (threadIdx.x == 0) is_last = (atomicAdd(&tickets[tile_id], 1) == splits - 1);
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  const int m0 = SWAPPED ? b_row0 : a_row0, n0 = SWAPPED ? a_row0 : b_row0;
-  const int rows = min(SWAPPED ? BN : BM, M - m0), cols = min(SWAPPED ? BM : BN, N - n0);
-  for (int idx = threadIdx.x; idx < rows * cols; idx += THREADS) {
-    const int m = m0 + idx / cols, n = n0 + idx % cols;
-    float sum = 0.f;
-    for (int s = 0; s < splits; ++s) sum += __ldcg(partial + ((int64_t)s * M + m) * N + n);
-    out[(int64_t)m * ldo + n] = cast_out<OutT>(sum);
-  }
-  if (threadIdx.x == 0) tickets[tile_id] = 0;
 }
 
 // ------------------------------------------------------------------ host side
@@ -352,6 +413,16 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int64_t ld
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
 template <int BN, bool SWAPPED, typename OutT>
 int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int64_t ldx,
                 int64_t ldw, int64_t ldo, int splits, float* partial, int* tickets, int* status,
@@ -371,9 +442,11 @@ int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M
   const int a_rows = SWAPPED ? N : M, b_rows = SWAPPED ? M : N;
   const int num_kb = (K + BK - 1) / BK;
   const int kb_per_split = (num_kb + splits - 1) / splits;
-  dim3 grid((a_rows + BM - 1) / BM, (b_rows + BN - 1) / BN, splits);
-  umma_gemm_kernel<BN, SWAPPED, OutT><<<grid, THREADS, S::SMEM, stream>>>(map_a, map_b, out, M, N, K, ldo, splits,
-                                                                         kb_per_split, partial, tickets, status);
+  const int tiles_a = (a_rows + BM - 1) / BM, tiles_b = (b_rows + BN - 1) / BN;
+  const int num_items = tiles_a * tiles_b * splits;
+  const int grid = num_items < sm_count() ? num_items : sm_count();
+  umma_gemm_kernel<BN, SWAPPED, OutT><<<grid, THREADS, S::SMEM, stream>>>(
+      map_a, map_b, out, M, N, K, ldo, splits, kb_per_split, tiles_a, num_items, partial, tickets, status);
   return gllm_launch_result();
 }
 
@@ -391,14 +464,16 @@ int umma_dispatch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int
 }
 }  // namespace
 
-// Splits along K for an [N, K] weight and M tokens' orientation; from (N, K) and the
-// orientation only (few tokens: M <= 64), never from M itself.
-GLLM_API int gllm_gemm_bf16_splits(int few_tokens, int N, int K) {
-  if (!few_tokens) return 1;
+// Splits along K for M tokens and an [N, K] weight.  It depends on (N, K) and on the bucket
+// M falls in (<= 16, <= 32, <= 64, more), never on M itself: enough items to keep every SM
+// streaming, as long as the fp32 partial tiles stay a small part of the weight's bytes.
+GLLM_API int gllm_gemm_bf16_splits(int M, int N, int K) {
+  if (M > 64) return 1;
+  const int bucket = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   const int tiles = (N + BM - 1) / BM;
   const int num_kb = (K + BK - 1) / BK;
   int s = 1;
-  while (s < 16 && tiles * s < 148 && num_kb / (2 * s) >= 4) s *= 2;
+  while (s < 16 && tiles * s < 2 * 148 && 2 * s <= K / (16 * bucket) && num_kb / (2 * s) >= 2) s *= 2;
   return s;
 }
 

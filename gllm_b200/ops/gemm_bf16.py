@@ -76,7 +76,7 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
     f, splits_of, tiles_of = _umma_fns()
     m, k = x.shape
     n = weight.shape[0]
-    splits = splits_of(int(m <= FEW_TOKENS), n, k)
+    splits = splits_of(m, n, k)
     partial, tickets = _device_scratch(x.device, splits * m * n if splits > 1 else 0, tiles_of(m, n))
     code = f(x.data_ptr(), weight.data_ptr(), out.data_ptr(), int(out.dtype == torch.float32), m, n, k,
              x.stride(0), weight.stride(0), out.stride(0), splits, partial.data_ptr(), tickets.data_ptr(),

@@ -316,10 +316,13 @@ def test_gemm_bf16_tensor_memory(ops, m, n, k, out_dtype):
             torch.testing.assert_close(got.double(), want, rtol=1e-4, atol=1e-4)
         else:
             torch.testing.assert_close(got.double(), want, rtol=1e-2, atol=1e-2)
-    if m <= 64:
-        # a token's result does not depend on the rest of the batch: bitwise
-        alone = ops.linear(x[m // 2:m // 2 + 1].contiguous(), w, out_dtype=out_dtype)
+    # a token's result does not depend on the rest of the batch: bitwise among batches of up to 16
+    # tokens (one kernel variant, one cut of K), to rounding beyond
+    alone = ops.linear(x[m // 2:m // 2 + 1].contiguous(), w, out_dtype=out_dtype)
+    if m <= 16:
         assert torch.equal(alone[0], got[m // 2])
+    else:
+        torch.testing.assert_close(alone[0].double(), got[m // 2].double(), rtol=1e-2, atol=1e-2)
 
 
 def test_gemm_bf16_odd_inner_size_goes_to_the_library(ops):
