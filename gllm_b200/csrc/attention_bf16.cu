@@ -47,6 +47,8 @@ decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride,
   unsigned char* q_sm = smem_raw + W * 2 * S::TILE_BYTES;
   __shared__ float red_m[W][ROWS], red_l[W][ROWS];
 
+  pdl_trigger();
+  pdl_wait();
   const int split = blockIdx.x;
   const int group = hq / hkv;
   const int head_tiles = (group + ROWS - 1) / ROWS;
@@ -241,6 +243,8 @@ decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride,
 template <int D>
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, int64_t out_stride, int hq, int num_chunks) {
+  pdl_trigger();
+  pdl_wait();
   const int n = blockIdx.y, h = blockIdx.x, d = threadIdx.x;
   const float* ml = part_ml + ((int64_t)n * hq + h) * num_chunks * 2;
   const float* po = part_o + ((int64_t)n * hq + h) * num_chunks * D;
@@ -271,13 +275,12 @@ int decode_launch(const __nv_bfloat16* q, int64_t q_stride, __nv_bfloat16* out, 
     if (e != cudaSuccess) return (int)e;
   }
   dim3 grid(num_chunks, hkv * head_tiles, num_queries);
-  decode_split_kernel<D><<<grid, S::W * 32, S::SMEM, stream>>>(
-      q, q_stride, cache, block_table, bt_stride, positions, token_row, part_o, part_ml, hq, hkv, block_size,
-      num_pages, num_chunks, scale * 1.4426950408889634f, window, status);
-  int e = gllm_launch_result();
+  int e = gllm_launch(decode_split_kernel<D>, grid, dim3(S::W * 32), (size_t)S::SMEM, stream, q, q_stride, cache,
+                      block_table, bt_stride, positions, token_row, part_o, part_ml, hq, hkv, block_size, num_pages,
+                      num_chunks, scale * 1.4426950408889634f, window, status);
   if (e) return e;
-  decode_merge_kernel<D><<<dim3(hq, num_queries), D, 0, stream>>>(part_o, part_ml, out, out_stride, hq, num_chunks);
-  return gllm_launch_result();
+  return gllm_launch(decode_merge_kernel<D>, dim3(hq, num_queries), dim3(D), 0, stream, part_o, part_ml, out,
+                     out_stride, hq, num_chunks);
 }
 }  // namespace
 

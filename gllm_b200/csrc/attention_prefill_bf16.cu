@@ -33,6 +33,8 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, __nv_bfloa
   unsigned char* q_sm = smem_raw;                       // [BM][D]
   unsigned char* kv_sm = smem_raw + BM * D * 2;         // [2 stages][K | V][BN][D]
 
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.z;
   const int group = hq / hkv;
   const int tiles_per_kv = group / gp;                  // CTAs that share a kv head
@@ -251,10 +253,9 @@ int prefill_launch(const __nv_bfloat16* q, int64_t q_stride, __nv_bfloat16* out,
   }
   dim3 grid((max_q_len + qt - 1) / qt, hkv * (group / gp), num_requests);
   const float scale_log2 = scale * 1.4426950408889634f;
-  prefill_kernel<D><<<grid, PF_THREADS, smem, stream>>>(q, q_stride, out, out_stride, cache, block_table, bt_stride,
-                                                       cu_q, ctx_lens, slots, hq, hkv, gp, block_size, num_pages,
-                                                       scale_log2, window, status);
-  return gllm_launch_result();
+  return gllm_launch(prefill_kernel<D>, grid, dim3(PF_THREADS), smem, stream, q, q_stride, out, out_stride, cache,
+                     block_table, bt_stride, cu_q, ctx_lens, slots, hq, hkv, gp, block_size, num_pages, scale_log2,
+                     window, status);
 }
 }  // namespace
 

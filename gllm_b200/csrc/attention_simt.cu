@@ -30,6 +30,8 @@ attention_simt_kernel(const T* __restrict__ q, int64_t q_stride, T* __restrict__
                       int hkv, int d, int block_size, int num_pages, float scale, int window,
                       int* __restrict__ status) {
   __shared__ float q_s[WARPS][MAX_D];
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t item = (int64_t)blockIdx.x * WARPS + warp;
   if (item >= (int64_t)n_tokens * hq) return;
@@ -109,10 +111,9 @@ int attention_simt_launch(const T* q, int64_t q_stride, T* out, int64_t out_stri
   const int64_t items = (int64_t)n_tokens * hq;
   const int64_t blocks = (items + WARPS - 1) / WARPS;
   if (blocks > 0x7fffffffLL) return (int)cudaErrorInvalidValue;
-  attention_simt_kernel<T><<<(unsigned)blocks, WARPS * 32, 0, stream>>>(
-      q, q_stride, out, out_stride, cache, block_table, bt_stride, positions, token_row, n_tokens, hq, hkv, d,
-      block_size, num_pages, scale, window, status);
-  return gllm_launch_result();
+  return gllm_launch(attention_simt_kernel<T>, dim3((unsigned)blocks), dim3(WARPS * 32), 0, stream, q, q_stride, out,
+                     out_stride, cache, block_table, bt_stride, positions, token_row, n_tokens, hq, hkv, d,
+                     block_size, num_pages, scale, window, status);
 }
 }  // namespace
 

@@ -55,4 +55,52 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return total;
 }
 
-static inline int gllm_launch_result() { return (int)cudaGetLastError(); }
+// Sum of up to 16 unsummed splits of a product, in ascending order; all loads are issued
+// before the first add so that they overlap.
+__device__ __forceinline__ float sum_parts16(const float* __restrict__ p, int n_parts, int64_t stride) {
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = i < n_parts ? __ldcg(p + (int64_t)i * stride) : 0.f;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) s += v[i];
+  return s;
+}
+
+// ---- programmatic dependent launch
+// Every kernel of the engine is launched so that it may be scheduled while the kernel before it
+// on the stream is still draining (its blocks become resident and run their set-up).  The rule
+// that keeps this safe: a kernel calls pdl_wait() before its first access to global memory, which
+// returns only when every earlier kernel has completed and its writes are visible; and it calls
+// pdl_trigger() at once, which lets the kernel after it be scheduled early in turn.  Both are
+// no-ops for a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#include <stdlib.h>
+static inline bool gllm_pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("GLLM_B200_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on != 0;
+}
+
+// Launches `kernel` on `stream` with programmatic stream serialization allowed (see above);
+// returns the cudaError_t as an int.
+template <typename... KArgs, typename... Args>
+static inline int gllm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = gllm_pdl_enabled() ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -15,6 +15,8 @@ template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                  float* __restrict__ resid, int n_tokens, int hidden, int vocab,
                                  int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
   const int n = blockIdx.x;
   if (n >= n_tokens) return;
   const int tok = tokens[n];
@@ -30,8 +32,8 @@ static int embedding_launch(const int* tokens, const T* table, float* resid, int
                             int vocab, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
-  embedding_kernel<T><<<n_tokens, threads, 0, stream>>>(tokens, table, resid, n_tokens, hidden, vocab, status);
-  return gllm_launch_result();
+  return gllm_launch(embedding_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, tokens, table, resid, n_tokens,
+                     hidden, vocab, status);
 }
 
 GLLM_API int gllm_embedding_f32(const int* tokens, const float* table, float* resid, int n_tokens,
@@ -51,24 +53,35 @@ GLLM_API int gllm_embedding_bf16(const int* tokens, const __nv_bfloat16* table, 
 // y = x / sqrt(mean + eps) * w as gllm/model/layers/norm.py:20-22, with the
 // statistic in fp32 whatever T is.  One block per row; the row lives in
 // shared memory between the two passes, so it is read from HBM once.
+// The branch may come as `n_parts` fp32 partial sums (a product cut along K whose splits
+// were left unsummed, laid out [part][row][hidden]): they are added in ascending order.
 template <typename T>
-__global__ void add_rmsnorm_kernel(const T* __restrict__ branch, float* __restrict__ resid,
+__global__ void add_rmsnorm_kernel(const T* __restrict__ branch, const float* __restrict__ parts, int n_parts,
+                                   int64_t part_stride, float* __restrict__ resid,
                                    const float* __restrict__ weight, T* __restrict__ out,
                                    const int* __restrict__ rows, int n_rows, int hidden, float eps,
                                    int unit_offset) {
   extern __shared__ float row_buf[];  // hidden floats + 32 scratch
   float* scratch = row_buf + hidden;
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x;
   if (i >= n_rows) return;
   const size_t r = rows ? (size_t)rows[i] : (size_t)i;
   float* res = resid + r * hidden;
   const T* br = branch ? branch + r * hidden : nullptr;
+  const float* pr = parts ? parts + r * hidden : nullptr;
   float ss = 0.f;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float x = res[c];
-    if (br) x += to_float(br[c]);
+    if (pr) {
+      const float b = sum_parts16(pr + c, n_parts, part_stride);
+      x += to_float(from_float<T>(b));           // rounded as the product itself would have rounded it
+    } else if (br) {
+      x += to_float(br[c]);
+    }
     row_buf[c] = x;
-    if (br && !rows) res[c] = x;
+    if ((br || pr) && !rows) res[c] = x;
     ss += x * x;
   }
   const float total = block_sum(ss, scratch);
@@ -81,9 +94,11 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ branch, float* __restri
 }
 
 template <typename T>
-static int add_rmsnorm_launch(const T* branch, float* resid, const float* weight, T* out, const int* rows,
-                              int n_rows, int hidden, float eps, int unit_offset, cudaStream_t stream) {
+static int add_rmsnorm_launch(const T* branch, const float* parts, int n_parts, int64_t part_stride, float* resid,
+                              const float* weight, T* out, const int* rows, int n_rows, int hidden, float eps,
+                              int unit_offset, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  if (n_parts > 16) return (int)cudaErrorInvalidValue;
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   size_t smem = (size_t)(hidden + 32) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
@@ -91,21 +106,50 @@ static int add_rmsnorm_launch(const T* branch, float* resid, const float* weight
     cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  add_rmsnorm_kernel<T><<<n_rows, threads, smem, stream>>>(branch, resid, weight, out, rows, n_rows, hidden, eps,
-                                                         unit_offset);
-  return gllm_launch_result();
+  return gllm_launch(add_rmsnorm_kernel<T>, dim3(n_rows), dim3(threads), smem, stream, branch, parts, n_parts,
+                     part_stride, resid, weight, out, rows, n_rows, hidden, eps, unit_offset);
 }
 
-GLLM_API int gllm_add_rmsnorm_f32(const float* branch, float* resid, const float* weight, float* out,
-                                  const int* rows, int n_rows, int hidden, float eps, int unit_offset,
-                                  cudaStream_t stream) {
-  return add_rmsnorm_launch<float>(branch, resid, weight, out, rows, n_rows, hidden, eps, unit_offset, stream);
+GLLM_API int gllm_add_rmsnorm_f32(const float* branch, const float* parts, int n_parts, int64_t part_stride,
+                                  float* resid, const float* weight, float* out, const int* rows, int n_rows,
+                                  int hidden, float eps, int unit_offset, cudaStream_t stream) {
+  return add_rmsnorm_launch<float>(branch, parts, n_parts, part_stride, resid, weight, out, rows, n_rows, hidden,
+                                   eps, unit_offset, stream);
 }
-GLLM_API int gllm_add_rmsnorm_bf16(const __nv_bfloat16* branch, float* resid, const float* weight,
-                                   __nv_bfloat16* out, const int* rows, int n_rows, int hidden, float eps,
-                                   int unit_offset, cudaStream_t stream) {
-  return add_rmsnorm_launch<__nv_bfloat16>(branch, resid, weight, out, rows, n_rows, hidden, eps, unit_offset,
-                                           stream);
+GLLM_API int gllm_add_rmsnorm_bf16(const __nv_bfloat16* branch, const float* parts, int n_parts,
+                                   int64_t part_stride, float* resid, const float* weight, __nv_bfloat16* out,
+                                   const int* rows, int n_rows, int hidden, float eps, int unit_offset,
+                                   cudaStream_t stream) {
+  return add_rmsnorm_launch<__nv_bfloat16>(branch, parts, n_parts, part_stride, resid, weight, out, rows, n_rows,
+                                           hidden, eps, unit_offset, stream);
+}
+
+// ------------------------------------------------- sum of unsummed splits
+// out[i] = parts[0][i] + parts[1][i] + ... in ascending order, rounded to T.
+template <typename T>
+__global__ void sum_parts_kernel(const float* __restrict__ parts, int n_parts, int64_t part_stride,
+                                 T* __restrict__ out, int64_t n) {
+  pdl_trigger();
+  pdl_wait();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    out[i] = from_float<T>(sum_parts16(parts + i, n_parts, part_stride));
+  }
+}
+template <typename T>
+static int sum_parts_launch(const float* parts, int n_parts, int64_t part_stride, T* out, int64_t n,
+                            cudaStream_t stream) {
+  if (n <= 0) return 0;
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  return gllm_launch(sum_parts_kernel<T>, dim3(blocks), dim3(256), 0, stream, parts, n_parts, part_stride, out, n);
+}
+GLLM_API int gllm_sum_parts_f32(const float* parts, int n_parts, int64_t part_stride, float* out, int64_t n,
+                                cudaStream_t stream) {
+  return sum_parts_launch<float>(parts, n_parts, part_stride, out, n, stream);
+}
+GLLM_API int gllm_sum_parts_bf16(const float* parts, int n_parts, int64_t part_stride, __nv_bfloat16* out,
+                                 int64_t n, cudaStream_t stream) {
+  return sum_parts_launch<__nv_bfloat16>(parts, n_parts, part_stride, out, n, stream);
 }
 
 // ------------------------------------------------------------------ SiLU · up
@@ -113,6 +157,8 @@ GLLM_API int gllm_add_rmsnorm_bf16(const __nv_bfloat16* branch, float* resid, co
 // out = silu(gate) * up, silu(z) = z / (1 + exp(-z))  (gllm/model/layers/mlp.py:44-47)
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_rows, int inter) {
+  pdl_trigger();
+  pdl_wait();
   const size_t total = (size_t)n_rows * inter;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
@@ -130,8 +176,7 @@ static int silu_mul_launch(const T* gate_up, T* out, int n_rows, int inter, cuda
   const size_t total = (size_t)n_rows * inter;
   int blocks = (int)((total + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  silu_mul_kernel<T><<<blocks, 256, 0, stream>>>(gate_up, out, n_rows, inter);
-  return gllm_launch_result();
+  return gllm_launch(silu_mul_kernel<T>, dim3(blocks), dim3(256), 0, stream, gate_up, out, n_rows, inter);
 }
 GLLM_API int gllm_silu_mul_f32(const float* gate_up, float* out, int n_rows, int inter, cudaStream_t stream) {
   return silu_mul_launch<float>(gate_up, out, n_rows, inter, stream);
@@ -151,15 +196,27 @@ GLLM_API int gllm_silu_mul_bf16(const __nv_bfloat16* gate_up, __nv_bfloat16* out
 // cached, gllm/model/layers/attention.py:156-161).
 // Cache layer layout: [page][k|v][kv_head][block_size][d].
 // inv_freq == nullptr: no rotation.  slot_mapping == nullptr or slot < 0: no store.
+// qkv may arrive as `n_parts` unsummed fp32 splits of the projection ([part][token][width]):
+// the kernel first sums them in ascending order into qkv (rounded to T, as the product would have).
 template <typename T>
-__global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+__global__ void rope_store_kernel(T* __restrict__ qkv, const float* __restrict__ parts, int n_parts,
+                                  int64_t part_stride, const int* __restrict__ positions,
                                   const float* __restrict__ inv_freq, const int* __restrict__ slot_mapping,
                                   T* __restrict__ cache, int n_tokens, int hq, int hkv, int d, int rotary_dim,
                                   int interleaved, int block_size, int num_pages, int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
   const int n = blockIdx.x;
   if (n >= n_tokens) return;
   T* row = qkv + (size_t)n * (hq + 2 * hkv) * d;
   const int half = rotary_dim / 2;
+  if (parts) {
+    const int width = (hq + 2 * hkv) * d;
+    const float* src = parts + (size_t)n * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+      row[c] = from_float<T>(sum_parts16(src + c, n_parts, part_stride));
+    __syncthreads();
+  }
   if (inv_freq) {
     const float pos = (float)positions[n];
     // one (head, pair) per thread-iteration over q and k heads
@@ -198,29 +255,33 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
 }
 
 template <typename T>
-static int rope_store_launch(T* qkv, const int* positions, const float* inv_freq, const int* slot_mapping,
+static int rope_store_launch(T* qkv, const float* parts, int n_parts, int64_t part_stride, const int* positions,
+                             const float* inv_freq, const int* slot_mapping,
                              T* cache, int n_tokens, int hq, int hkv, int d, int rotary_dim, int interleaved,
                              int block_size, int num_pages, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
+  if (rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || n_parts > 16) return (int)cudaErrorInvalidValue;
   int work = max((hq + hkv) * (rotary_dim / 2), hkv * d);
   int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
-  rope_store_kernel<T><<<n_tokens, threads, 0, stream>>>(qkv, positions, inv_freq, slot_mapping, cache, n_tokens,
-                                                        hq, hkv, d, rotary_dim, interleaved, block_size,
-                                                        num_pages, status);
-  return gllm_launch_result();
+  return gllm_launch(rope_store_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, qkv, parts, n_parts,
+                     part_stride, positions, inv_freq, slot_mapping, cache, n_tokens, hq, hkv, d, rotary_dim,
+                     interleaved, block_size, num_pages, status);
 }
-GLLM_API int gllm_rope_store_f32(float* qkv, const int* positions, const float* inv_freq, const int* slot_mapping,
+GLLM_API int gllm_rope_store_f32(float* qkv, const float* parts, int n_parts, int64_t part_stride,
+                                 const int* positions, const float* inv_freq, const int* slot_mapping,
                                  float* cache, int n_tokens, int hq, int hkv, int d, int rotary_dim,
                                  int interleaved, int block_size, int num_pages, int* status,
                                  cudaStream_t stream) {
-  return rope_store_launch<float>(qkv, positions, inv_freq, slot_mapping, cache, n_tokens, hq, hkv, d, rotary_dim,
-                                  interleaved, block_size, num_pages, status, stream);
+  return rope_store_launch<float>(qkv, parts, n_parts, part_stride, positions, inv_freq, slot_mapping, cache,
+                                  n_tokens, hq, hkv, d, rotary_dim, interleaved, block_size, num_pages, status,
+                                  stream);
 }
-GLLM_API int gllm_rope_store_bf16(__nv_bfloat16* qkv, const int* positions, const float* inv_freq,
-                                  const int* slot_mapping, __nv_bfloat16* cache, int n_tokens, int hq, int hkv,
-                                  int d, int rotary_dim, int interleaved, int block_size, int num_pages,
-                                  int* status, cudaStream_t stream) {
-  return rope_store_launch<__nv_bfloat16>(qkv, positions, inv_freq, slot_mapping, cache, n_tokens, hq, hkv, d,
-                                          rotary_dim, interleaved, block_size, num_pages, status, stream);
+GLLM_API int gllm_rope_store_bf16(__nv_bfloat16* qkv, const float* parts, int n_parts, int64_t part_stride,
+                                  const int* positions, const float* inv_freq, const int* slot_mapping,
+                                  __nv_bfloat16* cache, int n_tokens, int hq, int hkv, int d, int rotary_dim,
+                                  int interleaved, int block_size, int num_pages, int* status,
+                                  cudaStream_t stream) {
+  return rope_store_launch<__nv_bfloat16>(qkv, parts, n_parts, part_stride, positions, inv_freq, slot_mapping,
+                                          cache, n_tokens, hq, hkv, d, rotary_dim, interleaved, block_size,
+                                          num_pages, status, stream);
 }

@@ -171,13 +171,14 @@ __global__ void __launch_bounds__(THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  OutT* __restrict__ out, int M, int N, int K, int64_t ldo, int splits, int kb_per_split,
                  int tiles_a, int num_items, float* __restrict__ partial, int* __restrict__ tickets,
-                 int* __restrict__ status) {
+                 int reduce_in_kernel, int* __restrict__ status) {
   using S = Shape<BN>;
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[S::STAGES], empty_bar[S::STAGES], tmem_full_bar[2], tmem_empty_bar[2];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag, is_last;
 
+  pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t tile_base = (smem_addr(smem_dyn) + 1023u) & ~1023u;
   const int num_kb_total = (K + BK - 1) / BK;
@@ -205,6 +206,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
+  // set-up is done (barriers, tensor memory); everything below touches global memory
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -352,7 +355,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (lane == 0) mbar_arrive(smem_addr(&tmem_empty_bar[acc]));
         ++n_used;
       }
-      if (splits > 1) {
+      if (splits > 1 && reduce_in_kernel) {
         // the CTA that draws the last ticket of this tile sums the splits in ascending order
         __threadfence();
         epilogue_sync();
@@ -364,9 +367,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const int rows = min(SWAPPED ? BN : BM, M - m0), cols = min(SWAPPED ? BM : BN, N - n0);
           for (int idx = ep_thread; idx < rows * cols; idx += 128) {
             const int m = m0 + idx / cols, n = n0 + idx % cols;
-            float sum = 0.f;
-            for (int s = 0; s < splits; ++s) sum += __ldcg(partial + ((int64_t)s * M + m) * N + n);
-            out[(int64_t)m * ldo + n] = cast_out<OutT>(sum);
+            out[(int64_t)m * ldo + n] = cast_out<OutT>(sum_parts16(partial + (int64_t)m * N + n, splits, (int64_t)M * N));
           }
           if (ep_thread == 0) tickets[item.tile_id] = 0;
         }
@@ -425,7 +426,7 @@ int sm_count() {
 
 template <int BN, bool SWAPPED, typename OutT>
 int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int64_t ldx,
-                int64_t ldw, int64_t ldo, int splits, float* partial, int* tickets, int* status,
+                int64_t ldw, int64_t ldo, int splits, float* partial, int* tickets, int reduce_in_kernel, int* status,
                 cudaStream_t stream) {
   using S = Shape<BN>;
   CUtensorMap map_a, map_b;
@@ -445,17 +446,18 @@ int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M
   const int tiles_a = (a_rows + BM - 1) / BM, tiles_b = (b_rows + BN - 1) / BN;
   const int num_items = tiles_a * tiles_b * splits;
   const int grid = num_items < sm_count() ? num_items : sm_count();
-  umma_gemm_kernel<BN, SWAPPED, OutT><<<grid, THREADS, S::SMEM, stream>>>(
-      map_a, map_b, out, M, N, K, ldo, splits, kb_per_split, tiles_a, num_items, partial, tickets, status);
-  return gllm_launch_result();
+  return gllm_launch(umma_gemm_kernel<BN, SWAPPED, OutT>, dim3(grid), dim3(THREADS), (size_t)S::SMEM, stream, map_a,
+                     map_b, out, M, N, K, ldo, splits, kb_per_split, tiles_a, num_items, partial, tickets,
+                     reduce_in_kernel, status);
 }
 
 template <typename OutT>
 int umma_dispatch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int64_t ldx,
-                  int64_t ldw, int64_t ldo, int splits, float* partial, int* tickets, int* status,
+                  int64_t ldw, int64_t ldo, int splits, float* partial, int* tickets, int reduce_in_kernel, int* status,
                   cudaStream_t stream) {
 #define GLLM_UMMA(BN, SW) \
-  return umma_launch<BN, SW, OutT>(X, W, out, M, N, K, ldx, ldw, ldo, splits, partial, tickets, status, stream)
+  return umma_launch<BN, SW, OutT>(X, W, out, M, N, K, ldx, ldw, ldo, splits, partial, tickets, reduce_in_kernel, \
+                                   status, stream)
   if (M <= 16) GLLM_UMMA(16, true);
   if (M <= 32) GLLM_UMMA(32, true);
   if (M <= 64) GLLM_UMMA(64, true);
@@ -473,7 +475,8 @@ GLLM_API int gllm_gemm_bf16_splits(int M, int N, int K) {
   const int tiles = (N + BM - 1) / BM;
   const int num_kb = (K + BK - 1) / BK;
   int s = 1;
-  while (s < 16 && tiles * s < 2 * 148 && 2 * s <= K / (16 * bucket) && num_kb / (2 * s) >= 2) s *= 2;
+  if (tiles >= 96) return 1;                    // wide enough to keep most SMs streaming without a cut
+  while (s < 16 && tiles * s < 148 && 2 * s <= K / (8 * bucket) && num_kb / (2 * s) >= 2) s *= 2;
   return s;
 }
 
@@ -484,16 +487,20 @@ GLLM_API int gllm_gemm_bf16_tiles(int M, int N) {
 }
 
 // out_is_f32: 0 = bf16 output, 1 = fp32 output.  Needs K % 8 == 0 and 16-byte aligned rows of X and W.
-// partial: splits * M * N floats of scratch when splits > 1; tickets: zeroed ints (left at zero).
+// partial: splits * M * N floats of scratch when splits > 1, laid out [split][M][N].
+// reduce_in_kernel != 0: the kernel sums the splits itself into `out` (tickets: zeroed ints, left at
+// zero).  reduce_in_kernel == 0 with splits > 1: `out` is not written; the caller's next kernel sums
+// partial[0..splits) in ascending order.
 GLLM_API int gllm_gemm_bf16(const __nv_bfloat16* X, const __nv_bfloat16* W, void* out, int out_is_f32, int M,
                             int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int splits, float* partial,
-                            int* tickets, int* status, cudaStream_t stream) {
+                            int* tickets, int reduce_in_kernel, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || splits < 1 || splits > 16 ||
       (reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
     return (int)cudaErrorInvalidValue;
   if (out_is_f32)
-    return umma_dispatch<float>(X, W, (float*)out, M, N, K, ldx, ldw, ldo, splits, partial, tickets, status, stream);
+    return umma_dispatch<float>(X, W, (float*)out, M, N, K, ldx, ldw, ldo, splits, partial, tickets, reduce_in_kernel,
+                                status, stream);
   return umma_dispatch<__nv_bfloat16>(X, W, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, splits, partial, tickets,
-                                      status, stream);
+                                      reduce_in_kernel, status, stream);
 }

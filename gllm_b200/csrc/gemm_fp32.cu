@@ -16,6 +16,8 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float*
                 int K, int64_t lda, int64_t ldb, int64_t ldc) {
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
+  pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int tx = tid % 16, ty = tid / 16;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -70,6 +72,5 @@ GLLM_API int gllm_gemm_f32(const float* A, const float* B, float* C, int M, int 
   if (K <= 0) return (int)cudaErrorInvalidValue;
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return (int)cudaErrorInvalidValue;
-  gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, B, C, M, N, K, lda, ldb, ldc);
-  return gllm_launch_result();
+  return gllm_launch(gemm_f32_kernel, grid, dim3(256), 0, stream, A, B, C, M, N, K, lda, ldb, ldc);
 }

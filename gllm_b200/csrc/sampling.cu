@@ -195,6 +195,8 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int V, const
               int* __restrict__ out_token, float* __restrict__ out_logprob, int* __restrict__ out_ncand,
               float* __restrict__ out_top_lp, int* __restrict__ out_top_id, float* __restrict__ probs_out) {
   __shared__ Smem s;
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const float* x = logits + (int64_t)row * row_stride;
   const int tid = threadIdx.x;
@@ -348,6 +350,8 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int V, const
 __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, int64_t row_stride, int V, int* __restrict__ out_token) {
   __shared__ Smem s;
+  pdl_trigger();
+  pdl_wait();
   const float* x = logits + (int64_t)blockIdx.x * row_stride;
   float vmax = -INFINITY;
   int imax = 0x7fffffff;
@@ -368,16 +372,14 @@ GLLM_API int gllm_sample(const float* logits, int64_t row_stride, int rows, int 
                          cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (V <= 0) return (int)cudaErrorInvalidValue;
-  sample_kernel<<<rows, THREADS, 0, stream>>>(logits, row_stride, V, temperature, top_k, top_p, seed, counter,
-                                             n_logprobs, lp_stride, out_token, out_logprob, out_ncand,
-                                             out_top_lp, out_top_id, probs_out);
-  return gllm_launch_result();
+  return gllm_launch(sample_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, row_stride, V, temperature, top_k,
+                     top_p, seed, counter, n_logprobs, lp_stride, out_token, out_logprob, out_ncand, out_top_lp,
+                     out_top_id, probs_out);
 }
 
 GLLM_API int gllm_argmax(const float* logits, int64_t row_stride, int rows, int V, int* out_token,
                          cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (V <= 0) return (int)cudaErrorInvalidValue;
-  argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, row_stride, V, out_token);
-  return gllm_launch_result();
+  return gllm_launch(argmax_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, row_stride, V, out_token);
 }

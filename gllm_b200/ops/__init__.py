@@ -32,15 +32,19 @@ __all__ = [
     "check_status",
     "sample",
     "argmax",
+    "SplitSum",
+    "as_tensor",
 ]
 
 P = c_void_p
 _SIGNATURES = {
     "elementwise": {
         "gllm_embedding_{t}": [P, P, P, c_int, c_int, c_int, P, P],
-        "gllm_add_rmsnorm_{t}": [P, P, P, P, P, c_int, c_int, c_float, c_int, P],
+        "gllm_add_rmsnorm_{t}": [P, P, c_int, c_int64, P, P, P, P, c_int, c_int, c_float, c_int, P],
+        "gllm_sum_parts_{t}": [P, c_int, c_int64, P, c_int64, P],
         "gllm_silu_mul_{t}": [P, P, c_int, c_int, P],
-        "gllm_rope_store_{t}": [P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
+        "gllm_rope_store_{t}": [P, P, c_int, c_int64, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                c_int, P, P],
     },
     "gemm_fp32": {
         "gllm_gemm_f32": [P, P, P, c_int, c_int, c_int, c_int64, c_int64, c_int64, P],
@@ -159,6 +163,46 @@ def check_status(device=None) -> None:
         raise RuntimeError("a kernel reported: " + "; ".join(reasons))
 
 
+# ------------------------------------------------------------ unsummed splits
+class SplitSum:
+    """The result of a product that was cut along K and whose ``splits`` fp32
+    partial results ``parts [splits, rows, cols]`` were left unsummed: the
+    kernel that consumes it (``add_rmsnorm``, ``rope_store``) adds them in
+    ascending order, which saves a reduction pass.  ``parts`` lives in shared
+    scratch: consume a SplitSum before the next product runs."""
+
+    def __init__(self, parts: torch.Tensor, dtype: torch.dtype):
+        self.parts = parts
+        self.dtype = dtype
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+    @property
+    def device(self):
+        return self.parts.device
+
+    def tensor(self) -> torch.Tensor:
+        """The summed result as an ordinary tensor of ``dtype``."""
+        out = torch.empty(tuple(self.shape), dtype=self.dtype, device=self.parts.device)
+        f = _fn("elementwise", f"gllm_sum_parts_{_suffix(self.dtype)}")
+        _check(f(self.parts.data_ptr(), self.parts.shape[0], self.parts.stride(0), out.data_ptr(), out.numel(),
+                 _stream()), "sum_parts")
+        return out
+
+
+def as_tensor(x):
+    """``x`` itself, or the summed tensor of a SplitSum."""
+    return x.tensor() if isinstance(x, SplitSum) else x
+
+
+def _parts_args(x):
+    if isinstance(x, SplitSum):
+        return x.parts.data_ptr(), x.parts.shape[0], x.parts.stride(0)
+    return None, 0, 0
+
+
 # ---------------------------------------------------------------- embedding
 def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """fp32 residual rows ``table[tokens]`` (gllm/model/model.py:175-182)."""
@@ -195,7 +239,12 @@ def add_rmsnorm(
     hidden = resid.shape[-1]
     if weight.numel() != hidden:
         raise ValueError(f"norm weight has {weight.numel()} elements, rows have {hidden}")
-    if branch is not None:
+    parts_ptr, n_parts, part_stride = _parts_args(branch)
+    if isinstance(branch, SplitSum):
+        if tuple(branch.shape) != tuple(resid.shape) or branch.dtype != out_dtype:
+            raise ValueError("branch and resid differ in shape or dtype")
+        branch = None
+    elif branch is not None:
         _cuda(branch, "branch", out_dtype)
         if branch.shape != resid.shape:
             raise ValueError("branch and resid differ in shape")
@@ -209,8 +258,8 @@ def add_rmsnorm(
     else:
         _cuda(out, "out", out_dtype)
     f = _fn("elementwise", f"gllm_add_rmsnorm_{_suffix(out_dtype)}")
-    _check(f(_ptr(branch), resid.data_ptr(), weight.data_ptr(), out.data_ptr(), _ptr(rows), n_rows, hidden,
-             float(eps), int(unit_offset), _stream()), "add_rmsnorm")
+    _check(f(_ptr(branch), parts_ptr, n_parts, part_stride, resid.data_ptr(), weight.data_ptr(), out.data_ptr(),
+             _ptr(rows), n_rows, hidden, float(eps), int(unit_offset), _stream()), "add_rmsnorm")
     return out
 
 
@@ -241,11 +290,16 @@ def rope_store(
     head_dim: int,
     rotary_dim: int,
     interleaved: bool = False,
-) -> None:
-    """Rotate q and k of ``qkv`` in place and store k, v into the cache.
+) -> torch.Tensor:
+    """Rotate q and k of ``qkv`` in place and store k, v into the cache;
+    returns ``qkv`` (a SplitSum is summed into a new tensor first, in the same
+    kernel).
 
     ``cache_layer`` is ``[pages, 2, kv_heads, block_size, head_dim]``.
     """
+    parts_ptr, n_parts, part_stride = _parts_args(qkv)
+    if isinstance(qkv, SplitSum):
+        qkv = torch.empty(tuple(qkv.shape), dtype=qkv.dtype, device=qkv.device)
     _cuda(qkv, "qkv")
     _cuda(positions, "positions", torch.int32)
     n = qkv.shape[0]
@@ -263,19 +317,21 @@ def rope_store(
         if two != 2 or hkv != num_kv_heads or d != head_dim:
             raise ValueError("cache layer shape does not match the mixer's heads")
     f = _fn("elementwise", f"gllm_rope_store_{_suffix(qkv.dtype)}")
-    _check(f(qkv.data_ptr(), positions.data_ptr(), _ptr(inv_freq), _ptr(slot_mapping),
-             _ptr(cache_layer) if slot_mapping is not None else None, n, num_heads, num_kv_heads, head_dim,
-             rotary_dim, int(interleaved), block_size, num_pages, status_word(qkv.device).data_ptr(), _stream()),
-           "rope_store")
+    _check(f(qkv.data_ptr(), parts_ptr, n_parts, part_stride, positions.data_ptr(), _ptr(inv_freq),
+             _ptr(slot_mapping), _ptr(cache_layer) if slot_mapping is not None else None, n, num_heads,
+             num_kv_heads, head_dim, rotary_dim, int(interleaved), block_size, num_pages,
+             status_word(qkv.device).data_ptr(), _stream()), "rope_store")
+    return qkv
 
 
 # ------------------------------------------------------------------- linear
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
-           out: torch.Tensor | None = None) -> torch.Tensor:
+           out: torch.Tensor | None = None, split_ok: bool = False):
     """``x @ weight.T`` with ``weight`` stored ``[out, in]``
     (gllm/model/layers/linear.py:20).  fp32 inputs run the FFMA kernel (no
     tensor-core mode); bf16 inputs run the tensor-core kernels with fp32
-    accumulation."""
+    accumulation.  With ``split_ok`` the result may be a SplitSum (for callers
+    that hand it to ``add_rmsnorm`` or ``rope_store``)."""
     _cuda(x, "x")
     _cuda(weight, "weight", x.dtype)
     m, k = x.shape
@@ -283,6 +339,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     if k != k2:
         raise ValueError(f"x has {k} columns, weight has {k2}")
     out_dtype = out_dtype or x.dtype
+    if x.dtype == torch.bfloat16 and split_ok and out is None:
+        from gllm_b200.ops import gemm_bf16
+
+        split = gemm_bf16.linear_split(x, weight, out_dtype)
+        if split is not None:
+            return split
     if out is None:
         out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     else:

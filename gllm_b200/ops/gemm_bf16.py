@@ -42,7 +42,7 @@ def _umma_fns():
     if _umma is None:
         lib = load_module("gemm_bf16")
         f = lib.gllm_gemm_bf16
-        f.argtypes = [P, P, P, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, P, P, P, P]
+        f.argtypes = [P, P, P, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, P, P, c_int, P, P]
         f.restype = c_int
         lib.gllm_gemm_bf16_splits.argtypes = [c_int, c_int, c_int]
         lib.gllm_gemm_bf16_splits.restype = c_int
@@ -53,15 +53,18 @@ def _umma_fns():
 
 
 def _device_scratch(device: torch.device, partial_floats: int, tickets: int):
-    """Per-device scratch of the split-K reduction: fp32 partial tiles and the
-    ticket counters (zeroed once; the kernel leaves them at zero)."""
+    """Per-device scratch of the split-K reduction: fp32 partial tiles (two
+    buffers used in turn, so an unsummed result survives the next product) and
+    the ticket counters (zeroed once; the kernel leaves them at zero)."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    s = _scratch.setdefault(idx, {})
+    s = _scratch.setdefault(idx, {"turn": 0})
     if "tickets" not in s or s["tickets"].numel() < tickets:
         s["tickets"] = torch.zeros(max(tickets, 4096), dtype=torch.int32, device=device)
-    if "partial" not in s or s["partial"].numel() < partial_floats:
-        s["partial"] = torch.empty(max(partial_floats, 1 << 22), dtype=torch.float32, device=device)
-    return s["partial"], s["tickets"]
+    s["turn"] ^= 1
+    name = f"partial{s['turn']}"
+    if name not in s or s[name].numel() < partial_floats:
+        s[name] = torch.empty(max(partial_floats, 1 << 22), dtype=torch.float32, device=device)
+    return s[name], s["tickets"]
 
 
 def tensor_core_kernel_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -79,10 +82,31 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
     splits = splits_of(m, n, k)
     partial, tickets = _device_scratch(x.device, splits * m * n if splits > 1 else 0, tiles_of(m, n))
     code = f(x.data_ptr(), weight.data_ptr(), out.data_ptr(), int(out.dtype == torch.float32), m, n, k,
-             x.stride(0), weight.stride(0), out.stride(0), splits, partial.data_ptr(), tickets.data_ptr(),
+             x.stride(0), weight.stride(0), out.stride(0), splits, partial.data_ptr(), tickets.data_ptr(), 1,
              ops.status_word(x.device).data_ptr(), ops._stream())
     ops._check(code, "gemm_bf16")
     return out
+
+
+def linear_split(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype):
+    """The product as a SplitSum when the kernel would cut it along K; None
+    when it would not (or does not take these operands)."""
+    from gllm_b200 import ops
+
+    if _BACKEND != "tcgen05" or not tensor_core_kernel_takes(x, weight):
+        return None
+    f, splits_of, tiles_of = _umma_fns()
+    m, k = x.shape
+    n = weight.shape[0]
+    splits = splits_of(m, n, k)
+    if splits <= 1:
+        return None
+    partial, tickets = _device_scratch(x.device, splits * m * n, 0)
+    code = f(x.data_ptr(), weight.data_ptr(), None, int(out_dtype == torch.float32), m, n, k, x.stride(0),
+             weight.stride(0), n, splits, partial.data_ptr(), tickets.data_ptr(), 0,
+             ops.status_word(x.device).data_ptr(), ops._stream())
+    ops._check(code, "gemm_bf16")
+    return ops.SplitSum(partial[: splits * m * n].view(splits, m, n), out_dtype)
 
 
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

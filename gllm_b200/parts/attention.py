@@ -69,13 +69,14 @@ class Attention(Mixer):
             self.position.load(get, dtype, device)
 
     def forward(self, x, ctx, cache):
-        qkv = ops.linear(x, self.w_qkv)
+        qkv = ops.linear(x, self.w_qkv, split_ok=True)
         view = ctx.groups[cache.group]
         rotary = self.position.rotary() if self.position is not None else None
         if self.position is not None and rotary is None:
+            qkv = ops.as_tensor(qkv)
             self.position.apply(qkv, ctx, self.num_heads, self.num_kv_heads, self.head_dim)
         inv_freq, rotary_dim, interleaved = rotary if rotary is not None else (None, 0, False)
-        ops.rope_store(
+        qkv = ops.rope_store(
             qkv, ctx.positions, inv_freq,
             view.slot_mapping if cache.writes else None,
             cache.pages, self.num_heads, self.num_kv_heads, self.head_dim, rotary_dim, interleaved,
@@ -84,4 +85,4 @@ class Attention(Mixer):
             qkv, cache.pages, view.block_table, ctx.positions, ctx.token_row, self.num_heads, self.scale,
             window=self.window, batch=ctx,
         )
-        return ops.linear(attn, self.w_o)
+        return ops.linear(attn, self.w_o, split_ok=True)

@@ -131,10 +131,13 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, branch: torch.Tensor | None, resid: torch.Tensor, dtype: torch.dtype,
+    def forward(self, branch, resid: torch.Tensor, dtype: torch.dtype,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
         """``resid += branch`` in place (fp32), return norm(resid) in ``dtype``.
-        With ``rows``: only those rows, ``resid`` untouched."""
+        With ``rows``: only those rows, ``resid`` untouched.  ``branch`` is a
+        tensor, None, or a ``gllm_b200.ops.SplitSum`` (a mixer's or
+        feed-forward's last product left unsummed); a norm that cannot take
+        the latter calls ``ops.as_tensor`` on it."""
         raise NotImplementedError
 
 

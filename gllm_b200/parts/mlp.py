@@ -33,4 +33,4 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, ctx):
         gate_up = ops.linear(x, self.w_gate_up)
-        return ops.linear(ops.silu_mul(gate_up), self.w_down)
+        return ops.linear(ops.silu_mul(gate_up), self.w_down, split_ok=True)

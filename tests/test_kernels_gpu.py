@@ -331,3 +331,37 @@ def test_gemm_bf16_odd_inner_size_goes_to_the_library(ops):
     w = torch.randn(37, 100, generator=g).to(torch.bfloat16).cuda()
     got = ops.linear(x, w)
     torch.testing.assert_close(got.double(), x.double() @ w.double().T, rtol=2e-2, atol=2e-2)
+
+
+def test_unsummed_splits_are_summed_by_their_consumers(ops):
+    """A product cut along K may hand its fp32 partial results to add_rmsnorm or rope_store; both
+    give exactly what they give for the summed product."""
+    g = torch.Generator().manual_seed(11)
+    m, k = 8, 2048
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(2048, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).cuda()
+    summed = ops.linear(x, w)
+    split = ops.linear(x, w, split_ok=True)
+    assert isinstance(split, ops.SplitSum) and split.parts.shape[0] > 1 and tuple(split.shape) == (m, 2048)
+    assert torch.equal(split.tensor(), summed)
+    resid = torch.randn(m, 2048, generator=g).cuda()
+    wn = torch.ones(2048).cuda()
+    r1, r2 = resid.clone(), resid.clone()
+    a = ops.add_rmsnorm(summed, r1, wn, 1e-5, torch.bfloat16)
+    split = ops.linear(x, w, split_ok=True)
+    b = ops.add_rmsnorm(split, r2, wn, 1e-5, torch.bfloat16)
+    assert torch.equal(a, b) and torch.equal(r1, r2)
+    rows = torch.tensor([5, 1], dtype=torch.int32).cuda()
+    split = ops.linear(x, w, split_ok=True)
+    assert torch.equal(ops.add_rmsnorm(split, resid.clone(), wn, 1e-5, torch.bfloat16, rows=rows),
+                       ops.add_rmsnorm(summed, resid.clone(), wn, 1e-5, torch.bfloat16, rows=rows))
+    # rotary + store: 24 query heads and 4 kv heads of 64 make a width of 2048
+    hq, hkv, d, bs = 24, 4, 64, 16
+    positions = torch.arange(100, 100 + m, dtype=torch.int32).cuda()
+    inv_freq = (10000.0 ** (-torch.arange(d // 2).double() * 2 / d)).float().cuda()
+    slots = torch.arange(m, dtype=torch.int32).cuda()
+    c1 = torch.zeros(2, 2, hkv, bs, d, dtype=torch.bfloat16).cuda()
+    c2 = torch.zeros_like(c1)
+    q1 = ops.rope_store(summed.clone(), positions, inv_freq, slots, c1, hq, hkv, d, d)
+    q2 = ops.rope_store(ops.linear(x, w, split_ok=True), positions, inv_freq, slots, c2, hq, hkv, d, d)
+    assert torch.equal(q1, q2) and torch.equal(c1, c2)
