@@ -320,3 +320,44 @@ GLLM_API int gllm_attention_decode_bf16(const __nv_bfloat16* q, int64_t q_stride
   }
 #undef GLLM_DEC_D
 }
+
+// ---------------------------------------------------------------------------
+// The same attention for callers that cannot allocate (see attention_decode_noalloc.h).
+#include "attention_decode_noalloc.h"
+
+namespace {
+// Scratch for the per-chunk partial results, part of the library's device image.
+static __device__ __align__(256) float g_decode_noalloc_scratch[GLLM_DECODE_NOALLOC_MAX_FLOATS];
+constexpr int NOALLOC_MAX_DEVICES = 64;
+// Device address of the array on each device, looked up on the first call there.  In host
+// code the array's name is only a handle for the runtime, not an address a kernel can use.
+float* g_decode_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+}  // namespace
+
+GLLM_API int gllm_attention_decode_bf16_noalloc(const __nv_bfloat16* q, int64_t q_stride, __nv_bfloat16* out,
+                                                int64_t out_stride, const __nv_bfloat16* cache,
+                                                const int* block_table, int bt_stride, const int* positions,
+                                                const int* token_row, int num_queries, int hq, int hkv, int d,
+                                                int block_size, int num_pages, int num_chunks, float scale,
+                                                int window, int* status, cudaStream_t stream) {
+  if (num_queries <= 0) return 0;
+  if (hq <= 0 || d <= 0 || num_chunks <= 0) return (int)cudaErrorInvalidValue;
+  const int64_t o_floats = (int64_t)num_queries * hq * num_chunks * d;
+  const int64_t ml_floats = (int64_t)num_queries * hq * num_chunks * 2;
+  if (o_floats + ml_floats > (int64_t)GLLM_DECODE_NOALLOC_MAX_FLOATS) return (int)cudaErrorInvalidValue;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return (int)cudaErrorInvalidDevice;
+  if (!g_decode_noalloc_ptr[dev]) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_decode_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_decode_noalloc_ptr[dev] = p;
+  }
+  float* part_o = g_decode_noalloc_ptr[dev];
+  float* part_ml = part_o + o_floats;
+  return gllm_attention_decode_bf16(q, q_stride, out, out_stride, cache, block_table, bt_stride, positions,
+                                    token_row, num_queries, part_o, part_ml, hq, hkv, d, block_size, num_pages,
+                                    num_chunks, scale, window, status, stream);
+}
