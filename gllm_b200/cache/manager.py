@@ -109,8 +109,9 @@ class CacheManager:
             self._entry_writes.append(True)
             self._state_reqs.append(state)
             if state is not None and allocate_pools:
+                # one row more than there are slots: the null row, for rows that pad a batch
                 self._states.append(
-                    torch.zeros((self.max_batch_size, *state.shape), dtype=state.dtype, device=self.device)
+                    torch.zeros((self.max_batch_size + 1, *state.shape), dtype=state.dtype, device=self.device)
                 )
             else:
                 self._states.append(None)

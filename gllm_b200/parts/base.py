@@ -111,7 +111,7 @@ class MixerCache:
     group: int | None = None              # key into StepContext.groups
     pages: torch.Tensor | None = None     # [pages, 2, kv_heads, block_size, head_dim]
     writes: bool = True                   # False: attends over another entry's pages
-    state: torch.Tensor | None = None     # [max_batch_size, *StateRequirement.shape]
+    state: torch.Tensor | None = None     # [max_batch_size + 1, *StateRequirement.shape]; last row: padding rows
 
 
 # ------------------------------------------------------------------ part bases

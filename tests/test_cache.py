@@ -123,7 +123,7 @@ def test_state_slots_are_zeroed_and_stay_put():
     reqs = [(None, StateRequirement((3,), torch.float32), None), (KVPageRequirement(1, 16), None, None)]
     m = CacheManager(reqs, 4, 8, 2, 32, torch.float32, "cpu")
     caches = m.mixer_caches()
-    assert caches[0].state.shape == (2, 3) and caches[0].pages is None and caches[1].state is None
+    assert caches[0].state.shape == (2 + 1, 3) and caches[0].pages is None and caches[1].state is None
     a = m.add_request("a")
     caches[0].state[a.slot] = 7
     b = m.add_request("b")
