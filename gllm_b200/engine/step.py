@@ -258,12 +258,13 @@ class StepRunner:
                 self.last_argmax = ops.argmax(logits)
         else:
             bucket, seq_bucket = key
+            key = (bucket, seq_bucket, bool(greedy))
             tokens, ctx, rows = self.build(entries, pad_to=bucket, seq_bucket=seq_bucket)
             record = self._graphs.get(key)
             if record is None:
                 # first time: run it plainly (this is the step's result), then capture for later
                 logits = self.model.forward(tokens, ctx, self.mixer_caches, rows)
-                argmax = ops.argmax(logits)
+                argmax = ops.argmax(logits) if greedy else None
                 torch.cuda.synchronize(self.device)
                 graph = torch.cuda.CUDAGraph()
                 if self._graph_pool is None:
@@ -271,7 +272,7 @@ class StepRunner:
                 launches_before = ops.launch_count
                 with torch.cuda.graph(graph, pool=self._graph_pool):
                     g_logits = self.model.forward(tokens, ctx, self.mixer_caches, rows)
-                    g_argmax = ops.argmax(g_logits)
+                    g_argmax = ops.argmax(g_logits) if greedy else None
                 launches = ops.launch_count - launches_before
                 ops.launch_count = launches_before          # captured, not run
                 self._graphs[key] = (graph, g_logits, g_argmax, dict(self._last_views), launches)
@@ -283,7 +284,7 @@ class StepRunner:
                 self.graph_replays += 1
                 ops.launch_count += launches
             logits = logits[:wanted]
-            self.last_argmax = argmax[:wanted]
+            self.last_argmax = argmax[:wanted] if argmax is not None else None
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
