@@ -172,7 +172,7 @@ decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride,
     for (int nt = 0; nt < TILE / 8; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const float p = exp2f(s[nt][e] - m[e >> 1]);
+        const float p = fast_exp2(s[nt][e] - m[e >> 1]);
         s[nt][e] = p;
         l[e >> 1] += p;
       }
@@ -226,7 +226,7 @@ decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride,
     float acc = 0.f, ll = 0.f;
 #pragma unroll
     for (int w = 0; w < W; ++w) {
-      const float f = red_m[w][row] == -INFINITY ? 0.f : exp2f(red_m[w][row] - mm);
+      const float f = red_m[w][row] == -INFINITY ? 0.f : fast_exp2(red_m[w][row] - mm);
       acc += all_o[((size_t)w * ROWS + row) * D + d] * f;
       ll += red_l[w][row] * f;
     }
@@ -254,7 +254,7 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
   for (int s = 0; s < num_chunks; ++s) {
     const float ms = ml[2 * s];
     if (ms == -INFINITY) continue;
-    const float f = exp2f(ms - mm);
+    const float f = fast_exp2(ms - mm);
     o += po[(int64_t)s * D + d] * f;
     l += ml[2 * s + 1] * f;
   }

@@ -154,47 +154,52 @@ prefill_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, __nv_bfloa
         mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
       }
     }
-    // ---- mask, scale, online softmax (rows g8 and g8 + 8 of the warp's 16)
+    // ---- mask, online softmax (rows g8 and g8 + 8 of the warp's 16).  The maximum is kept in raw
+    // score units; the scale enters through the exponent's FMA: p = 2^(s*c - m*c), c = scale*log2(e)
     const bool need_mask = (kv0 + BN - 1 > pos_first) || (window > 0) || (t_count < qt);
     float mx[2] = {-INFINITY, -INFINITY};
+    if (need_mask) {
+#pragma unroll
+      for (int nt = 0; nt < BN / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1;
+          const int key = kv0 + nt * 8 + 2 * t4 + (e & 1);
+          const bool hidden = !row_ok[i] || key > qpos[i] || (window > 0 && key <= qpos[i] - window);
+          if (hidden) s[nt][e] = -INFINITY;
+        }
+    }
 #pragma unroll
     for (int nt = 0; nt < BN / 8; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = e >> 1;
-        float v = s[nt][e] * scale_log2;
-        if (need_mask) {
-          const int key = kv0 + nt * 8 + 2 * t4 + (e & 1);
-          const bool hidden = !row_ok[i] || key > qpos[i] || (window > 0 && key <= qpos[i] - window);
-          if (hidden) v = -INFINITY;
-        }
-        s[nt][e] = v;
-        mx[i] = fmaxf(mx[i], v);
-      }
-    float corr[2], m_use[2];
+      for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+    float corr[2], neg_mc[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
       mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
       const float m_new = fmaxf(m[i], mx[i]);
-      m_use[i] = m_new == -INFINITY ? 0.f : m_new;
-      corr[i] = m[i] == -INFINITY ? 0.f : exp2f(m[i] - m_use[i]);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      corr[i] = m[i] == -INFINITY ? 0.f : fast_exp2((m[i] - m_use) * scale_log2);
+      neg_mc[i] = -m_use * scale_log2;
       m[i] = m_new;
-      l[i] *= corr[i];
     }
 #pragma unroll
     for (int nt = 0; nt < BN / 8; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int i = e >> 1;
-        const float p = exp2f(s[nt][e] - m_use[i]);
+        const float p = fast_exp2(fmaf(s[nt][e], scale_log2, neg_mc[i]));
         s[nt][e] = p;
-        l[i] += p;
+        l[i] = (e & 1) || nt ? l[i] + p : fmaf(l[i], corr[i], p);
       }
+    // the output only needs rescaling when some row's maximum moved (rare after the first tiles)
+    if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {
 #pragma unroll
-    for (int nd = 0; nd < D / 8; ++nd) {
-      o[nd][0] *= corr[0]; o[nd][1] *= corr[0];
-      o[nd][2] *= corr[1]; o[nd][3] *= corr[1];
+      for (int nd = 0; nd < D / 8; ++nd) {
+        o[nd][0] *= corr[0]; o[nd][1] *= corr[0];
+        o[nd][2] *= corr[1]; o[nd][3] *= corr[1];
+      }
     }
     // ---- O += P V
 #pragma unroll

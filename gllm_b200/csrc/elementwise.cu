@@ -8,6 +8,42 @@
 // stream, norm weights, norm statistics and rotation angles are always fp32.
 #include "common.cuh"
 
+// ------------------------------------------------- 8 elements at a time
+// Vec8<T>: eight consecutive elements of an activation row as fp32, moved with 16-byte
+// (bf16) or 2 x 16-byte (fp32) accesses.  The wide kernels below need rows whose length is a
+// multiple of 8 and 16-byte aligned pointers; otherwise the plain kernels run.
+template <typename T> struct Vec8;
+template <> struct Vec8<float> {
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* v) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+  }
+};
+template <> struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = raw;
+  }
+};
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 // ---------------------------------------------------------------- embedding
 // resid[n, :] = table[tokens[n], :] (upcast to fp32).  A token outside the
 // vocabulary sets a status bit and yields zeros: no fault, the host raises.
@@ -28,10 +64,36 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __rest
 }
 
 template <typename T>
+__global__ void embedding_wide_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                                      float* __restrict__ resid, int n_tokens, int hidden, int vocab,
+                                      int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
+  const int n = blockIdx.x;
+  const int tok = tokens[n];
+  const bool ok = tok >= 0 && tok < vocab;
+  if (!ok && threadIdx.x == 0) atomicOr(status, GLLM_STATUS_TOKEN_RANGE);
+  const T* row = table + (size_t)(ok ? tok : 0) * hidden;
+  float* dst = resid + (size_t)n * hidden;
+  for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+    float v[8];
+    Vec8<T>::load(row + c, v);
+    if (!ok) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.f;
+    }
+    Vec8<float>::store(dst + c, v);
+  }
+}
+
+template <typename T>
 static int embedding_launch(const int* tokens, const T* table, float* resid, int n_tokens, int hidden,
                             int vocab, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
+  if (hidden % 8 == 0 && aligned16(table) && aligned16(resid))
+    return gllm_launch(embedding_wide_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, tokens, table, resid,
+                       n_tokens, hidden, vocab, status);
   return gllm_launch(embedding_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, tokens, table, resid, n_tokens,
                      hidden, vocab, status);
 }
@@ -93,12 +155,68 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ branch, const float* __
   }
 }
 
+// The same with 8 columns per access and the row kept in registers (up to MAXC chunks of 8 per thread).
+template <typename T, int MAXC>
+__global__ void add_rmsnorm_wide_kernel(const T* __restrict__ branch, const float* __restrict__ parts, int n_parts,
+                                        int64_t part_stride, float* __restrict__ resid,
+                                        const float* __restrict__ weight, T* __restrict__ out,
+                                        const int* __restrict__ rows, int n_rows, int hidden, float eps,
+                                        int unit_offset) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x;
+  const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+  float* res = resid + r * hidden;
+  float x[MAXC][8], w[MAXC][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < MAXC; ++k) {
+    const int c = (threadIdx.x + k * blockDim.x) * 8;
+    if (c >= hidden) break;
+    Vec8<float>::load(res + c, x[k]);
+    Vec8<float>::load(weight + c, w[k]);
+    if (parts) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        x[k][e] += to_float(from_float<T>(sum_parts16(parts + r * hidden + c + e, n_parts, part_stride)));
+    } else if (branch) {
+      float b[8];
+      Vec8<T>::load(branch + r * hidden + c, b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[k][e] += b[e];
+    }
+    if ((branch || parts) && !rows) Vec8<float>::store(res + c, x[k]);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += x[k][e] * x[k][e];
+  }
+  const float total = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  T* o = out + (size_t)i * hidden;
+#pragma unroll
+  for (int k = 0; k < MAXC; ++k) {
+    const int c = (threadIdx.x + k * blockDim.x) * 8;
+    if (c >= hidden) break;
+    float y[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = x[k][e] * inv * (unit_offset ? 1.0f + w[k][e] : w[k][e]);
+    Vec8<T>::store(o + c, y);
+  }
+}
+
 template <typename T>
 static int add_rmsnorm_launch(const T* branch, const float* parts, int n_parts, int64_t part_stride, float* resid,
                               const float* weight, T* out, const int* rows, int n_rows, int hidden, float eps,
                               int unit_offset, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (n_parts > 16) return (int)cudaErrorInvalidValue;
+  if (hidden % 8 == 0 && aligned16(resid) && aligned16(weight) && aligned16(out) && (!branch || aligned16(branch))) {
+    const int chunks = hidden / 8;
+    const int wide_threads = chunks >= 256 ? 256 : (chunks >= 128 ? 128 : (chunks >= 64 ? 64 : 32));
+    if (chunks <= wide_threads * 4)
+      return gllm_launch(add_rmsnorm_wide_kernel<T, 4>, dim3(n_rows), dim3(wide_threads), 0, stream, branch, parts,
+                         n_parts, part_stride, resid, weight, out, rows, n_rows, hidden, eps, unit_offset);
+  }
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   size_t smem = (size_t)(hidden + 32) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
@@ -171,8 +289,33 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 }
 
 template <typename T>
+__global__ void silu_mul_wide_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_rows, int inter) {
+  pdl_trigger();
+  pdl_wait();
+  const int per_row = inter / 8;
+  const size_t total = (size_t)n_rows * per_row;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = idx / per_row;
+    const int c = (int)(idx - r * per_row) * 8;
+    float g[8], u[8], y[8];
+    Vec8<T>::load(gate_up + r * 2 * inter + c, g);
+    Vec8<T>::load(gate_up + r * 2 * inter + inter + c, u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) y[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
+    Vec8<T>::store(out + r * inter + c, y);
+  }
+}
+
+template <typename T>
 static int silu_mul_launch(const T* gate_up, T* out, int n_rows, int inter, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  if (inter % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
+    const size_t chunks = (size_t)n_rows * (inter / 8);
+    int wide_blocks = (int)((chunks + 255) / 256);
+    if (wide_blocks > 148 * 16) wide_blocks = 148 * 16;
+    return gllm_launch(silu_mul_wide_kernel<T>, dim3(wide_blocks), dim3(256), 0, stream, gate_up, out, n_rows, inter);
+  }
   const size_t total = (size_t)n_rows * inter;
   int blocks = (int)((total + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
@@ -254,6 +397,97 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const float* __restrict__
   }
 }
 
+// The same for the common case (pairs are the two halves, rotary_dim and head size multiples
+// of 16): one thread owns 8 consecutive pairs, takes sine and cosine once and reuses them for
+// every head, moves 16 bytes at a time and writes the rotated k and the v straight to the cache.
+template <typename T>
+__global__ void rope_store_wide_kernel(T* __restrict__ qkv, const float* __restrict__ parts, int n_parts,
+                                       int64_t part_stride, const int* __restrict__ positions,
+                                       const float* __restrict__ inv_freq, const int* __restrict__ slot_mapping,
+                                       T* __restrict__ cache, int n_tokens, int hq, int hkv, int d, int rotary_dim,
+                                       int block_size, int num_pages, int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
+  const int n = blockIdx.x;
+  const int width = (hq + 2 * hkv) * d;
+  T* row = qkv + (size_t)n * width;
+  const float* prow = parts ? parts + (size_t)n * width : nullptr;
+  const int half = rotary_dim / 2;
+  // where this token's k and v go
+  int64_t cache_base = -1;
+  if (slot_mapping) {
+    const int slot = slot_mapping[n];
+    if (slot >= 0) {
+      const int page = slot / block_size, off = slot - page * block_size;
+      if (page >= num_pages) {
+        if (threadIdx.x == 0) atomicOr(status, GLLM_STATUS_PAGE_RANGE);
+      } else {
+        cache_base = ((int64_t)page * 2 * hkv * block_size + off) * d;
+      }
+    }
+  }
+  const int64_t head_stride = (int64_t)block_size * d, v_plane = (int64_t)hkv * block_size * d;
+  auto load8 = [&](int col, float* v) {
+    if (prow) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = to_float(from_float<T>(sum_parts16(prow + col + e, n_parts, part_stride)));
+    } else {
+      Vec8<T>::load(row + col, v);
+    }
+  };
+  // rotated part of q and k heads: (head, chunk of 8 pairs)
+  const int chunks = inv_freq ? half / 8 : 0;
+  if (chunks > 0) {
+    const int my_chunk = threadIdx.x % chunks;
+    const float pos = (float)positions[n];
+    float sn[8], cs[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sincosf(pos * inv_freq[my_chunk * 8 + e], &sn[e], &cs[e]);
+    for (int h = threadIdx.x / chunks; h < hq + hkv; h += blockDim.x / chunks) {
+      const int c0 = h * d + my_chunk * 8, c1 = c0 + half;
+      float a[8], b[8], ra[8], rb[8];
+      load8(c0, a);
+      load8(c1, b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        ra[e] = a[e] * cs[e] - b[e] * sn[e];
+        rb[e] = a[e] * sn[e] + b[e] * cs[e];
+      }
+      Vec8<T>::store(row + c0, ra);
+      Vec8<T>::store(row + c1, rb);
+      if (h >= hq && cache_base >= 0) {
+        T* kdst = cache + cache_base + (int64_t)(h - hq) * head_stride;
+        Vec8<T>::store(kdst + my_chunk * 8, ra);
+        Vec8<T>::store(kdst + half + my_chunk * 8, rb);
+      }
+    }
+  }
+  // everything that is not rotated: the tail of q and k heads past rotary_dim, and v
+  const int rot = chunks > 0 ? rotary_dim : 0;
+  const int tail_chunks = (d - rot) / 8;
+  const int v_chunks = d / 8;
+  const int plain_items = (hq + hkv) * tail_chunks + hkv * v_chunks;
+  for (int item = threadIdx.x; item < plain_items; item += blockDim.x) {
+    int h, col_in_head;
+    if (item < (hq + hkv) * tail_chunks) {
+      h = item / tail_chunks;
+      col_in_head = rot + (item - h * tail_chunks) * 8;
+    } else {
+      const int j = item - (hq + hkv) * tail_chunks;
+      h = hq + hkv + j / v_chunks;
+      col_in_head = (j % v_chunks) * 8;
+    }
+    float v[8];
+    load8(h * d + col_in_head, v);
+    if (prow) Vec8<T>::store(row + h * d + col_in_head, v);
+    if (h >= hq && cache_base >= 0) {
+      const bool is_v = h >= hq + hkv;
+      const int kvh = is_v ? h - hq - hkv : h - hq;
+      Vec8<T>::store(cache + cache_base + (is_v ? v_plane : 0) + (int64_t)kvh * head_stride + col_in_head, v);
+    }
+  }
+}
+
 template <typename T>
 static int rope_store_launch(T* qkv, const float* parts, int n_parts, int64_t part_stride, const int* positions,
                              const float* inv_freq, const int* slot_mapping,
@@ -261,6 +495,13 @@ static int rope_store_launch(T* qkv, const float* parts, int n_parts, int64_t pa
                              int block_size, int num_pages, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || n_parts > 16) return (int)cudaErrorInvalidValue;
+  const int eff_rot = inv_freq ? rotary_dim : 0;
+  if (!interleaved && d % 8 == 0 && eff_rot % 16 == 0 && aligned16(qkv) && (!slot_mapping || aligned16(cache)) &&
+      (eff_rot == 0 || 128 % (eff_rot / 16) == 0)) {
+    return gllm_launch(rope_store_wide_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, qkv, parts, n_parts,
+                       part_stride, positions, inv_freq, slot_mapping, cache, n_tokens, hq, hkv, d, rotary_dim,
+                       block_size, num_pages, status);
+  }
   int work = max((hq + hkv) * (rotary_dim / 2), hkv * d);
   int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
   return gllm_launch(rope_store_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, qkv, parts, n_parts,
