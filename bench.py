@@ -231,6 +231,7 @@ def time_prefill(engine, tokens: int, repeats: int, warmup: int):
         engine.step()
         end.record()
         torch.cuda.synchronize()
+        engine.step()          # greedy steps are pipelined: this call reads the timed step's token
         assert st.is_finished, "the prefill step did not finish the one-token request"
         if it >= warmup:
             times.append(start.elapsed_time(end))

@@ -47,15 +47,19 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 // ---------------------------------------------------------------- embedding
 // resid[n, :] = table[tokens[n], :] (upcast to fp32).  A token outside the
 // vocabulary sets a status bit and yields zeros: no fault, the host raises.
+// A negative token id means "the token last sampled for this request": it is read from
+// sampled[token_row[n]], which the previous step's argmax left on the device.
 template <typename T>
-__global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+__global__ void embedding_kernel(const int* __restrict__ tokens, const int* __restrict__ sampled,
+                                 const int* __restrict__ token_row, const T* __restrict__ table,
                                  float* __restrict__ resid, int n_tokens, int hidden, int vocab,
                                  int* __restrict__ status) {
   pdl_trigger();
   pdl_wait();
   const int n = blockIdx.x;
   if (n >= n_tokens) return;
-  const int tok = tokens[n];
+  int tok = tokens[n];
+  if (tok < 0 && sampled) tok = sampled[token_row[n]];
   const bool ok = tok >= 0 && tok < vocab;
   if (!ok && threadIdx.x == 0) atomicOr(status, GLLM_STATUS_TOKEN_RANGE);
   const T* row = table + (size_t)(ok ? tok : 0) * hidden;
@@ -64,13 +68,15 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __rest
 }
 
 template <typename T>
-__global__ void embedding_wide_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+__global__ void embedding_wide_kernel(const int* __restrict__ tokens, const int* __restrict__ sampled,
+                                      const int* __restrict__ token_row, const T* __restrict__ table,
                                       float* __restrict__ resid, int n_tokens, int hidden, int vocab,
                                       int* __restrict__ status) {
   pdl_trigger();
   pdl_wait();
   const int n = blockIdx.x;
-  const int tok = tokens[n];
+  int tok = tokens[n];
+  if (tok < 0 && sampled) tok = sampled[token_row[n]];
   const bool ok = tok >= 0 && tok < vocab;
   if (!ok && threadIdx.x == 0) atomicOr(status, GLLM_STATUS_TOKEN_RANGE);
   const T* row = table + (size_t)(ok ? tok : 0) * hidden;
@@ -87,24 +93,28 @@ __global__ void embedding_wide_kernel(const int* __restrict__ tokens, const T* _
 }
 
 template <typename T>
-static int embedding_launch(const int* tokens, const T* table, float* resid, int n_tokens, int hidden,
-                            int vocab, int* status, cudaStream_t stream) {
+static int embedding_launch(const int* tokens, const int* sampled, const int* token_row, const T* table,
+                            float* resid, int n_tokens, int hidden, int vocab, int* status,
+                            cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
   if (hidden % 8 == 0 && aligned16(table) && aligned16(resid))
-    return gllm_launch(embedding_wide_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, tokens, table, resid,
-                       n_tokens, hidden, vocab, status);
-  return gllm_launch(embedding_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, tokens, table, resid, n_tokens,
-                     hidden, vocab, status);
+    return gllm_launch(embedding_wide_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, tokens, sampled,
+                       token_row, table, resid, n_tokens, hidden, vocab, status);
+  return gllm_launch(embedding_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, tokens, sampled, token_row,
+                     table, resid, n_tokens, hidden, vocab, status);
 }
 
-GLLM_API int gllm_embedding_f32(const int* tokens, const float* table, float* resid, int n_tokens,
-                                int hidden, int vocab, int* status, cudaStream_t stream) {
-  return embedding_launch<float>(tokens, table, resid, n_tokens, hidden, vocab, status, stream);
+GLLM_API int gllm_embedding_f32(const int* tokens, const int* sampled, const int* token_row, const float* table,
+                                float* resid, int n_tokens, int hidden, int vocab, int* status,
+                                cudaStream_t stream) {
+  return embedding_launch<float>(tokens, sampled, token_row, table, resid, n_tokens, hidden, vocab, status, stream);
 }
-GLLM_API int gllm_embedding_bf16(const int* tokens, const __nv_bfloat16* table, float* resid, int n_tokens,
-                                 int hidden, int vocab, int* status, cudaStream_t stream) {
-  return embedding_launch<__nv_bfloat16>(tokens, table, resid, n_tokens, hidden, vocab, status, stream);
+GLLM_API int gllm_embedding_bf16(const int* tokens, const int* sampled, const int* token_row,
+                                 const __nv_bfloat16* table, float* resid, int n_tokens, int hidden, int vocab,
+                                 int* status, cudaStream_t stream) {
+  return embedding_launch<__nv_bfloat16>(tokens, sampled, token_row, table, resid, n_tokens, hidden, vocab, status,
+                                         stream);
 }
 
 // ------------------------------------------------------ add + RMSNorm (fused)
@@ -210,7 +220,9 @@ static int add_rmsnorm_launch(const T* branch, const float* parts, int n_parts, 
                               int unit_offset, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (n_parts > 16) return (int)cudaErrorInvalidValue;
-  if (hidden % 8 == 0 && aligned16(resid) && aligned16(weight) && aligned16(out) && (!branch || aligned16(branch))) {
+  // unsummed splits: many loads per column, so spread a row over as many threads as there are columns
+  if (!parts && hidden % 8 == 0 && aligned16(resid) && aligned16(weight) && aligned16(out) &&
+      (!branch || aligned16(branch))) {
     const int chunks = hidden / 8;
     const int wide_threads = chunks >= 256 ? 256 : (chunks >= 128 ? 128 : (chunks >= 64 ? 64 : 32));
     if (chunks <= wide_threads * 4)
@@ -218,6 +230,7 @@ static int add_rmsnorm_launch(const T* branch, const float* parts, int n_parts, 
                          n_parts, part_stride, resid, weight, out, rows, n_rows, hidden, eps, unit_offset);
   }
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  if (parts) threads = hidden >= 1024 ? 1024 : threads;
   size_t smem = (size_t)(hidden + 32) * sizeof(float);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   if (smem > 48 * 1024) {
@@ -496,7 +509,8 @@ static int rope_store_launch(T* qkv, const float* parts, int n_parts, int64_t pa
   if (n_tokens <= 0) return 0;
   if (rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || n_parts > 16) return (int)cudaErrorInvalidValue;
   const int eff_rot = inv_freq ? rotary_dim : 0;
-  if (!interleaved && d % 8 == 0 && eff_rot % 16 == 0 && aligned16(qkv) && (!slot_mapping || aligned16(cache)) &&
+  if (!parts && !interleaved && d % 8 == 0 && eff_rot % 16 == 0 && aligned16(qkv) &&
+      (!slot_mapping || aligned16(cache)) &&
       (eff_rot == 0 || 128 % (eff_rot / 16) == 0)) {
     return gllm_launch(rope_store_wide_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, qkv, parts, n_parts,
                        part_stride, positions, inv_freq, slot_mapping, cache, n_tokens, hq, hkv, d, rotary_dim,
@@ -504,6 +518,7 @@ static int rope_store_launch(T* qkv, const float* parts, int n_parts, int64_t pa
   }
   int work = max((hq + hkv) * (rotary_dim / 2), hkv * d);
   int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);
+  if (parts && (hq + 2 * hkv) * d >= 1024) threads = 1024;   // unsummed splits: one column per thread and turn
   return gllm_launch(rope_store_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, qkv, parts, n_parts,
                      part_stride, positions, inv_freq, slot_mapping, cache, n_tokens, hq, hkv, d, rotary_dim,
                      interleaved, block_size, num_pages, status);

@@ -348,7 +348,8 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int V, const
 }
 
 __global__ void __launch_bounds__(THREADS)
-argmax_kernel(const float* __restrict__ logits, int64_t row_stride, int V, int* __restrict__ out_token) {
+argmax_kernel(const float* __restrict__ logits, int64_t row_stride, int V, int* __restrict__ out_token,
+              const int* __restrict__ out_index) {
   __shared__ Smem s;
   pdl_trigger();
   pdl_wait();
@@ -361,7 +362,7 @@ argmax_kernel(const float* __restrict__ logits, int64_t row_stride, int V, int* 
   }
   int arg;
   block_max_arg(vmax, imax, &arg, s);
-  if (threadIdx.x == 0) out_token[blockIdx.x] = arg;
+  if (threadIdx.x == 0) out_token[out_index ? out_index[blockIdx.x] : blockIdx.x] = arg;
 }
 }  // namespace
 
@@ -377,9 +378,11 @@ GLLM_API int gllm_sample(const float* logits, int64_t row_stride, int rows, int 
                      out_top_id, probs_out);
 }
 
+// out_index (optional): row r's result goes to out_token[out_index[r]] instead of out_token[r].
 GLLM_API int gllm_argmax(const float* logits, int64_t row_stride, int rows, int V, int* out_token,
-                         cudaStream_t stream) {
+                         const int* out_index, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (V <= 0) return (int)cudaErrorInvalidValue;
-  return gllm_launch(argmax_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, row_stride, V, out_token);
+  return gllm_launch(argmax_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, row_stride, V, out_token,
+                     out_index);
 }

@@ -93,6 +93,8 @@ class LLMEngine(LLMEngineBase):
 
             self.tokenizer = Tokenizer.from_file(tok_path)
         self.counters = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "preemptions": 0}
+        # the greedy step whose tokens the host has not read yet
+        self._pending = None
 
     # ------------------------------------------------------------- properties
     @property
@@ -161,12 +163,38 @@ class LLMEngine(LLMEngineBase):
         )
 
     # ---------------------------------------------------------------- one step
+    def _resolve_pending(self) -> list[RequestState]:
+        """Read the tokens of the step that is still in flight and account them."""
+        if self._pending is None:
+            return []
+        sched, rows, slots, (host, event) = self._pending
+        self._pending = None
+        event.synchronize()
+        values = host.tolist()
+        status = values[self.runner.sampled.numel()]
+        if status:
+            ops.status_word(self.device).zero_()
+            reasons = [text for bit, text in ops.STATUS_BITS.items() if status & bit] or [f"status {status}"]
+            raise RuntimeError("a kernel reported: " + "; ".join(reasons))
+        sampled = {r.id: values[slots[r.id]] for r in rows}
+        return self.scheduler.resolve(sched, sampled)
+
     def step(self) -> list[RequestState]:
-        """Schedule, run and sample one step; returns the requests it finished."""
+        """Schedule, run and sample one step; returns the requests that finished.
+
+        Greedy decoding is pipelined: the sampled tokens stay on the device, where the next step
+        reads them, so that step is scheduled and queued before the host has seen them; the host
+        reads a step's tokens while the next one runs and may therefore report a request's end one
+        call late (a request that met a stop token has then run one step too many, whose token is
+        dropped).  Whenever the next schedule could depend on the tokens (somebody waits, a portion
+        of a prompt runs, pages are short, sampling is not greedy) the step in flight is read first."""
+        finished: list[RequestState] = []
+        if self._pending is not None and not self.scheduler.can_run_ahead():
+            finished += self._resolve_pending()
         sched: ScheduledStep = self.scheduler.schedule()
         self.counters["preemptions"] = self.scheduler.num_preemptions
         if not sched.entries:
-            return []
+            return finished + self._resolve_pending()
         entries = []
         sampling_rows = []
         for e in sched.entries:
@@ -180,11 +208,22 @@ class LLMEngine(LLMEngineBase):
                 self.counters["prefill_tokens"] += e.num_tokens
         all_greedy = all(r.sampling.greedy and r.sampling.max_num_logprobs == 0 for r in sampling_rows)
         logits = self.runner.run(entries, check=False, greedy=all_greedy)
+        self.scheduler.advance(sched)
+        self.counters["steps"] += 1
+        previous, self._pending = self._pending, None
+        if all_greedy:
+            slots = {r.id: self.cache.requests[r.id].slot for r in sampling_rows}
+            self._pending = (sched, sampling_rows, slots, self.runner.snapshot())
+            if previous is not None:
+                self._pending, current = previous, self._pending
+                finished += self._resolve_pending()
+                self._pending = current
+            return finished
+        if previous is not None:
+            self._pending = previous
+            finished += self._resolve_pending()
         sampled = {}
-        if sampling_rows and all_greedy:
-            for r, token in zip(sampling_rows, self.runner.last_argmax.tolist()):
-                sampled[r.id] = token
-        elif sampling_rows:
+        if sampling_rows:
             out = self.sampler.forward(
                 logits,
                 [r.sampling for r in sampling_rows],
@@ -197,8 +236,7 @@ class LLMEngine(LLMEngineBase):
                     r.generated_logprobs.append(TokenLogProbs(vals, ids))
                     r.generated_token_logprobs.append(out.token_logprobs[i])
         ops.check_status(self.device)
-        self.counters["steps"] += 1
-        return self.scheduler.update(sched, sampled)
+        return finished + self.scheduler.resolve(sched, sampled)
 
     # --------------------------------------------------------------- generate
     def generate(self, reqs: list[GenerationRequest]) -> list[GenerationResult]:
@@ -207,11 +245,9 @@ class LLMEngine(LLMEngineBase):
         states = [self._make_state(r) for r in reqs]
         for s in states:
             self.scheduler.add(s)
-        remaining = len(states)
-        while remaining:
-            finished = self.step()
-            remaining -= sum(1 for f in finished if any(f is s for s in states))
-            if not finished and not self.scheduler.has_work:
+        while not all(s.is_finished for s in states):
+            self.step()
+            if not self.scheduler.has_work and self._pending is None:
                 break
         return [self._create_result(s) for s in states]
 
@@ -263,8 +299,8 @@ class LLMEngine(LLMEngineBase):
         self.alive = True
         try:
             while self.alive:
-                self._drain_queue(blocking=not self.scheduler.has_work)
-                if not self.scheduler.has_work:
+                self._drain_queue(blocking=not self.scheduler.has_work and self._pending is None)
+                if not self.scheduler.has_work and self._pending is None:
                     continue
                 for state in self.step():
                     if state.future is not None:

@@ -72,6 +72,8 @@ class RequestState:
     # tokens (prompt + generated) whose keys and values are in the cache
     num_computed: int = 0
     num_preemptions: int = 0
+    # tokens sampled on the device whose values the host has not read yet
+    num_inflight: int = 0
     finish_reason: str = ""
     future: Any = None
     arrival: int = 0
@@ -82,11 +84,17 @@ class RequestState:
 
     @property
     def num_tokens(self) -> int:
-        return len(self.prompt_token_ids) + len(self.generated_token_ids)
+        return len(self.prompt_token_ids) + len(self.generated_token_ids) + self.num_inflight
 
     def token_slice(self, start: int, n: int) -> list[int]:
         """Tokens ``start .. start+n-1`` of prompt + generated."""
         p, end = len(self.prompt_token_ids), start + n
+        known = p + len(self.generated_token_ids)
+        if end > known:
+            # the last token is still on the device: -1 stands for "the token last sampled for me"
+            if end - known != 1 or self.num_inflight != 1:
+                raise ValueError("only the very last token of a request may be in flight")
+            return self.token_slice(start, n - 1) + [-1] if n > 1 else [-1]
         if end <= p:
             return self.prompt_token_ids[start:end]
         if start >= p:

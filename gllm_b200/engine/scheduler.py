@@ -142,6 +142,8 @@ class Scheduler:
         for req in order:
             if req.status is not RequestStatus.RUNNING:
                 continue  # preempted a moment ago
+            if len(req.generated_token_ids) + req.num_inflight >= req.max_new_tokens:
+                continue  # its last token is in flight: nothing more to run
             pending = req.num_tokens - req.num_computed
             n = min(pending, self.params.prefill_chunk, budget)
             if n <= 0:
@@ -187,15 +189,39 @@ class Scheduler:
         return step
 
     # ------------------------------------------------------------ after a step
-    def update(self, step: ScheduledStep, sampled: dict) -> list[RequestState]:
-        """Account the step.  ``sampled[request.id]`` is the new token of every
-        entry that samples.  Returns the requests that finished; their pages
-        and slots are already free."""
+    def can_run_ahead(self) -> bool:
+        """True when the next step can be scheduled before the previous step's tokens are known:
+        nobody waits, everybody decodes, and every request finds room for one more token, so the
+        schedule holds no admission and no preemption."""
+        if self.waiting or not self.running:
+            return False
+        need = {g.index: 0 for g in self.cache.groups}
+        for req in self.running:
+            if req.num_tokens - req.num_computed != 1 or req.id not in self.cache.requests:
+                return False
+            for g, n in self.cache.pages_needed(req.id, 1).items():
+                need[g] += n
+        return all(self.cache.groups[g].allocator.num_free >= n for g, n in need.items())
+
+    def advance(self, step: ScheduledStep) -> None:
+        """The step has been queued on the device: count its tokens as computed and the tokens
+        it will sample as in flight."""
+        for e in step.entries:
+            e.request.num_computed += e.num_tokens
+            if e.samples:
+                e.request.num_inflight += 1
+
+    def resolve(self, step: ScheduledStep, sampled: dict) -> list[RequestState]:
+        """The host has read the step's tokens: ``sampled[request.id]`` for every entry that
+        sampled.  Returns the requests that finished; their pages and slots are already free.
+        A request that ended meanwhile (a stop token one step earlier, an abort) ignores its token."""
         finished = []
         for e in step.entries:
             req = e.request
-            req.num_computed += e.num_tokens
             if not e.samples:
+                continue
+            req.num_inflight -= 1
+            if req.status is not RequestStatus.RUNNING:
                 continue
             token = sampled[req.id]
             req.generated_token_ids.append(token)
@@ -210,3 +236,8 @@ class Scheduler:
                 self.running.remove(req)
                 finished.append(req)
         return finished
+
+    def update(self, step: ScheduledStep, sampled: dict) -> list[RequestState]:
+        """``advance`` and ``resolve`` in one go (the step's tokens are known already)."""
+        self.advance(step)
+        return self.resolve(step, sampled)

@@ -65,7 +65,7 @@ class StepRunner:
         self.dtype = model.dtype
         self.max_tokens = int(max_tokens_per_step)
         n_groups = len(cache.groups)
-        cap = _align4(self.max_tokens) * (4 + n_groups) + 4 * _align4(cache.max_batch_size + 1) + 64
+        cap = _align4(self.max_tokens) * (5 + n_groups) + 4 * _align4(cache.max_batch_size + 1) + 64
         self._capacity = cap
         self._pinned = [torch.empty(cap, dtype=torch.int32).pin_memory() if torch.cuda.is_available()
                         else torch.empty(cap, dtype=torch.int32) for _ in range(2)]
@@ -73,6 +73,16 @@ class StepRunner:
         self._meta = torch.empty(cap, dtype=torch.int32, device=self.device)
         self.workspace = Workspace(self.device)
         self.mixer_caches = cache.mixer_caches()
+        # The token last sampled (argmax) for every state slot stays on the device: the next step's
+        # embedding reads it from here when the host passes a token id < 0.
+        self.sampled = torch.zeros(cache.max_batch_size + 1, dtype=torch.int32, device=self.device)
+        self._snapshots = [
+            (torch.zeros(cache.max_batch_size + 2, dtype=torch.int32).pin_memory() if torch.cuda.is_available()
+             else torch.zeros(cache.max_batch_size + 2, dtype=torch.int32))
+            for _ in range(4)
+        ]
+        self._snapshot_turn = 0
+        self.last_argmax = None
         self.steps_run = 0
         self.last_h2d_bytes = 0
 
@@ -187,6 +197,9 @@ class StepRunner:
         put("ctx_lens", ctx_lens)
         put("slots", slots)
         put("rows", logit_rows)
+        # state slot of the request that owns each wanted row (padding rows: the null row)
+        row_owner = token_row[logit_rows] if logit_rows.size else np.zeros(0, dtype=np.int32)
+        put("row_slots", row_owner)
         for g in cache.groups:
             put(f"slotmap{g.index}", np.concatenate(slot_maps[g.index] + [null_slots]))
         self._meta[:cursor].copy_(pinned[:cursor], non_blocking=True)
@@ -215,7 +228,9 @@ class StepRunner:
             num_prefill_tokens=n_prefill,
             num_prefill_requests=sum(1 for n in q_lens if n > 1),
             workspace=self.workspace,
+            sampled=self.sampled,
         )
+        self._row_slots = dev("row_slots")
         self._last_views = views
         return dev("tokens"), ctx, dev("rows")
 
@@ -243,7 +258,8 @@ class StepRunner:
     def run(self, entries: list[StepEntry], check: bool = True, greedy: bool = False) -> torch.Tensor:
         """Run one step; returns fp32 logits ``[wanted, vocab]`` on the device,
         in the order of the entries and of their ``want`` lists.  With
-        ``greedy`` the argmax of every row is left in ``self.last_argmax``.
+        ``greedy`` the argmax of every wanted row is written to
+        ``self.sampled[state slot of the row's request]`` (see ``snapshot``).
 
         A step in which every request brings a single token runs as a CUDA
         graph captured once per (batch bucket, sequence bucket): same kernels,
@@ -255,7 +271,7 @@ class StepRunner:
             tokens, ctx, rows = self.build(entries)
             logits = self.model.forward(tokens, ctx, self.mixer_caches, rows)
             if greedy and wanted:
-                self.last_argmax = ops.argmax(logits)
+                ops.argmax(logits, out=self.sampled, scatter_index=self._row_slots)
         else:
             bucket, seq_bucket = key
             key = (bucket, seq_bucket, bool(greedy))
@@ -264,7 +280,8 @@ class StepRunner:
             if record is None:
                 # first time: run it plainly (this is the step's result), then capture for later
                 logits = self.model.forward(tokens, ctx, self.mixer_caches, rows)
-                argmax = ops.argmax(logits) if greedy else None
+                if greedy:
+                    ops.argmax(logits, out=self.sampled, scatter_index=self._row_slots)
                 torch.cuda.synchronize(self.device)
                 graph = torch.cuda.CUDAGraph()
                 if self._graph_pool is None:
@@ -272,25 +289,38 @@ class StepRunner:
                 launches_before = ops.launch_count
                 with torch.cuda.graph(graph, pool=self._graph_pool):
                     g_logits = self.model.forward(tokens, ctx, self.mixer_caches, rows)
-                    g_argmax = ops.argmax(g_logits) if greedy else None
+                    if greedy:
+                        ops.argmax(g_logits, out=self.sampled, scatter_index=self._row_slots)
                 launches = ops.launch_count - launches_before
                 ops.launch_count = launches_before          # captured, not run
-                self._graphs[key] = (graph, g_logits, g_argmax, dict(self._last_views), launches)
+                self._graphs[key] = (graph, g_logits, dict(self._last_views), launches)
             else:
-                graph, logits, argmax, views, launches = record
+                graph, logits, views, launches = record
                 if views != self._last_views:
                     raise RuntimeError("the batch layout of a captured decode step changed")
                 graph.replay()
                 self.graph_replays += 1
                 ops.launch_count += launches
             logits = logits[:wanted]
-            self.last_argmax = argmax[:wanted] if argmax is not None else None
         for e in entries:
             self.cache.commit(e.request_id, len(e.tokens))
         self.steps_run += 1
         if check:
             ops.check_status(self.device)
         return logits
+
+    def snapshot(self):
+        """Queue a copy of the sampled tokens (by state slot) and of the kernels' status word to
+        pinned host memory; returns ``(host tensor, event)``.  After ``event.synchronize()`` the
+        tensor holds ``sampled[0 .. max_batch_size]`` followed by the status word."""
+        host = self._snapshots[self._snapshot_turn]
+        self._snapshot_turn = (self._snapshot_turn + 1) % len(self._snapshots)
+        n = self.sampled.numel()
+        host[:n].copy_(self.sampled, non_blocking=True)
+        host[n:n + 1].copy_(ops.status_word(self.device), non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return host, event
 
     def finish(self, request_id) -> None:
         """The request is over: its pages and its slot are given back."""

@@ -99,7 +99,7 @@ class DecoderModel:
         logits_out: torch.Tensor | None = None,
     ) -> torch.Tensor:
         """Logits ``[len(logit_rows), vocab]`` fp32 of the flat batch ``tokens``."""
-        resid = ops.embedding(tokens, self.embedding)
+        resid = ops.embedding(tokens, self.embedding, sampled=ctx.sampled, token_row=ctx.token_row)
         branch = None
         for entry_idx, entry in enumerate(self.spec.plan):
             branch, resid = self.layers[entry.layer].forward(branch, resid, ctx, caches[entry_idx])

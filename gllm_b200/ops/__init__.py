@@ -39,7 +39,7 @@ __all__ = [
 P = c_void_p
 _SIGNATURES = {
     "elementwise": {
-        "gllm_embedding_{t}": [P, P, P, c_int, c_int, c_int, P, P],
+        "gllm_embedding_{t}": [P, P, P, P, P, c_int, c_int, c_int, P, P],
         "gllm_add_rmsnorm_{t}": [P, P, c_int, c_int64, P, P, P, P, c_int, c_int, c_float, c_int, P],
         "gllm_sum_parts_{t}": [P, c_int, c_int64, P, c_int64, P],
         "gllm_silu_mul_{t}": [P, P, c_int, c_int, P],
@@ -51,7 +51,7 @@ _SIGNATURES = {
     },
     "sampling": {
         "gllm_sample": [P, c_int64, c_int, c_int, P, P, P, P, P, P, c_int, P, P, P, P, P, P, P],
-        "gllm_argmax": [P, c_int64, c_int, c_int, P, P],
+        "gllm_argmax": [P, c_int64, c_int, c_int, P, P, P],
     },
     "attention_simt": {
         "gllm_attention_simt_{t}": [P, c_int64, P, c_int64, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,
@@ -204,9 +204,18 @@ def _parts_args(x):
 
 
 # ---------------------------------------------------------------- embedding
-def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """fp32 residual rows ``table[tokens]`` (gllm/model/model.py:175-182)."""
+def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None,
+              sampled: torch.Tensor | None = None, token_row: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 residual rows ``table[tokens]`` (gllm/model/model.py:175-182).
+
+    With ``sampled`` and ``token_row``: a negative token id stands for
+    ``sampled[token_row[i]]``, the token the previous step's argmax left on the
+    device for that request, so a decode step can be queued before the host
+    has seen the previous step's tokens."""
     _cuda(tokens, "tokens", torch.int32)
+    if sampled is not None:
+        _cuda(sampled, "sampled", torch.int32)
+        _cuda(token_row, "token_row", torch.int32)
     _cuda(table, "table")
     n, (vocab, hidden) = tokens.numel(), table.shape
     if out is None:
@@ -214,8 +223,8 @@ def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor | Non
     else:
         _cuda(out, "out", torch.float32)
     f = _fn("elementwise", f"gllm_embedding_{_suffix(table.dtype)}")
-    _check(f(tokens.data_ptr(), table.data_ptr(), out.data_ptr(), n, hidden, vocab,
-             status_word(table.device).data_ptr(), _stream()), "embedding")
+    _check(f(tokens.data_ptr(), _ptr(sampled), _ptr(token_row) if sampled is not None else None, table.data_ptr(),
+             out.data_ptr(), n, hidden, vocab, status_word(table.device).data_ptr(), _stream()), "embedding")
     return out
 
 
@@ -436,16 +445,23 @@ def paged_attention(
 MAX_LOGPROBS = 32
 
 
-def argmax(logits: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Index of the largest logit of every row (lowest index on ties), int32."""
+def argmax(logits: torch.Tensor, out: torch.Tensor | None = None,
+           scatter_index: torch.Tensor | None = None) -> torch.Tensor:
+    """Index of the largest logit of every row (lowest index on ties), int32.
+    With ``scatter_index`` row ``r``'s result is written to ``out[scatter_index[r]]``."""
     _cuda(logits, "logits", torch.float32, contiguous=False)
     rows, vocab = logits.shape
     if logits.stride(1) != 1:
         raise ValueError("logit rows must be contiguous")
     if out is None:
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    if scatter_index is not None:
+        _cuda(scatter_index, "scatter_index", torch.int32)
+        if scatter_index.numel() < rows:
+            raise ValueError("scatter_index needs one entry per row")
     f = _fn("sampling", "gllm_argmax")
-    _check(f(logits.data_ptr(), logits.stride(0), rows, vocab, out.data_ptr(), _stream()), "argmax")
+    _check(f(logits.data_ptr(), logits.stride(0), rows, vocab, out.data_ptr(), _ptr(scatter_index), _stream()),
+           "argmax")
     return out
 
 

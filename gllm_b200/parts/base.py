@@ -102,6 +102,9 @@ class StepContext:
     num_prefill_requests: int = 0
     # device scratch the attention kernels share (owned by the step function)
     workspace: Any = None
+    # [max_batch_size + 1] int32: the token last sampled for each state slot (a token id < 0 in the
+    # batch stands for it)
+    sampled: Any = None
 
 
 @dataclass

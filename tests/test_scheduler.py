@@ -159,3 +159,50 @@ def test_token_slice():
     assert r.token_slice(3, 4) == [13, 14, 100, 101]
     assert r.token_slice(6, 2) == [101, 102]
     assert r.token_slice(7, 1) == [102]
+
+
+def test_running_ahead_reads_tokens_one_step_late():
+    """Greedy decoding is pipelined: a step is scheduled while the tokens of the step before are
+    still on the device.  Length limits are honoured exactly; a stop token is seen one step late
+    and the token of the step too many is dropped."""
+    params, cache, sched = setup(num_blocks=32, budget=64, chunk=64)
+    a, b = request("a", 6, max_new=3), request("b", 4, max_new=10, stop=(7,))
+    sched.add(a)
+    sched.add(b)
+    assert not sched.can_run_ahead()                      # somebody waits
+    pending = None
+    tokens_for = {"a": iter([5, 5, 5, 5, 5]), "b": iter([1, 7, 9, 9, 9])}   # b meets its stop token second
+    steps = 0
+    while sched.has_work:
+        if pending is not None and not sched.can_run_ahead():
+            sched.resolve(*pending)
+            pending = None
+        step = sched.schedule()
+        if not step.entries:
+            if pending is not None:
+                sched.resolve(*pending)
+                pending = None
+            continue
+        for e in step.entries:
+            if e.request.id not in cache.requests:
+                cache.add_request(e.request.id)
+            toks = e.request.token_slice(e.start, e.num_tokens)
+            assert len(toks) == e.num_tokens
+            if e.start >= 6 or (e.request is b and e.start >= 4):
+                assert toks == [-1] or e.request.num_inflight == 0   # the device supplies the token in flight
+            cache.append(e.request.id, e.num_tokens)
+            cache.commit(e.request.id, e.num_tokens)
+        sched.advance(step)
+        sampled = {e.request.id: next(tokens_for[e.request.id]) for e in step.entries if e.samples}
+        previous, pending = pending, (step, sampled)
+        if previous is not None:
+            sched.resolve(*previous)
+        steps += 1
+        assert steps < 50
+    if pending is not None:
+        sched.resolve(*pending)
+    assert a.generated_token_ids == [5, 5, 5] and a.finish_reason == "length"       # never a fourth step for a
+    assert b.generated_token_ids == [1, 7] and b.finish_reason == "stop"            # the 9 of the extra step is dropped
+    assert a.num_inflight == 0 and b.num_inflight == 0
+    assert cache.num_free_pages() == 32 and cache.slots.num_free == 4
+    cache.check_invariants()
