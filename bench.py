@@ -207,7 +207,7 @@ def time_decode(engine, batch: int, context: int, steps: int, warmup: int):
     torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1000 / steps
     h2d = engine.runner.last_h2d_bytes
-    d2h = batch * 4 + 4
+    d2h = engine.runner.sampled.numel() * 4 + 4      # the sampled-token snapshot and the status word
     drain(engine, states)
     return dev_ms, wall_ms, launches, h2d, d2h
 

@@ -4,10 +4,10 @@
 // softmax(QK^T/sqrt(D) + bias)V (gllm/model/layers/attention.py:165-173,
 // gllm/ops/attention/reference_attention.py:40-48).
 //
-// A request's keys are cut into chunks of W*64 positions aligned to multiples
+// A request's keys are cut into chunks of W*32 positions aligned to multiples
 // of the chunk (the cut depends on absolute positions only, never on the batch
 // or on how the prompt was fed).  One CTA owns one (chunk, kv head, request):
-// each of its W warps copies 64 keys and 64 values of the chunk into shared
+// each of its W warps copies 32 keys and 32 values of the chunk into shared
 // memory with cp.async (16-byte pieces, everything in flight at once; decode
 // is bound by this traffic) and runs Q K^T and P V for all query heads of the
 // kv head on the tensor cores (mma.sync m16n8k16, the heads are the 16 rows of
@@ -19,12 +19,12 @@
 #include "mma_utils.cuh"
 
 namespace {
-constexpr int TILE = 64;     // keys per warp
+constexpr int TILE = 32;     // keys per warp
 constexpr int ROWS = 16;     // query heads per CTA (rows of the MMA tile)
 
 template <int D>
 struct DecodeShape {
-  static constexpr int W = D <= 64 ? 4 : 2;   // warps per CTA
+  static constexpr int W = D <= 64 ? 8 : 4;   // warps per CTA
   static constexpr int CHUNK = W * TILE;
   static constexpr int TILE_BYTES = TILE * D * 2;
   // per warp K and V tiles, then the Q tile
@@ -78,12 +78,12 @@ decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride,
   // ---- this warp's 64 keys and values: all copies are issued before anything waits
   const int k0 = split * S::CHUNK + warp * TILE;
   const bool warp_has_keys = k0 < c1 && k0 + TILE > c0;
-  // Every lane first resolves two of the 64 rows (page lookup, offset in the page) and leaves
+  // Every lane first resolves its share of the tile's rows (page lookup, offset in the page) and leaves
   // the rows' element offsets in shared memory, so the copy loop below has no dependent loads.
   __shared__ int64_t row_base[W][TILE];
   if (warp_has_keys) {
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
+    for (int half = 0; half < TILE / 32; ++half) {
       const int row = lane + 32 * half;
       const int key = k0 + row;
       int64_t base = -1;
