@@ -284,25 +284,30 @@ GLLM_API int gllm_sum_parts_bf16(const float* parts, int n_parts, int64_t part_s
 }
 
 // ------------------------------------------------------------------ SiLU · up
-// gate_up is [n, 2*inter] with the gate in the first `inter` columns:
-// out = silu(gate) * up, silu(z) = z / (1 + exp(-z))  (gllm/model/layers/mlp.py:44-47)
+// gate_up is [n, 2*inter]: out = silu(gate) * up, silu(z) = z / (1 + exp(-z))
+// (gllm/model/layers/mlp.py:44-47).  block == 0: the gate is the first `inter` columns, the up the
+// rest.  block > 0: blocks of `block` gate columns alternate with the `block` up columns of the
+// same features (the layout the gated product's weight uses).
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_rows, int inter) {
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_rows, int inter,
+                                int block) {
   pdl_trigger();
   pdl_wait();
   const size_t total = (size_t)n_rows * inter;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t r = idx / inter, c = idx - r * inter;
-    const float g = to_float(gate_up[r * 2 * inter + c]);
-    const float u = to_float(gate_up[r * 2 * inter + inter + c]);
+    const size_t gc = block ? (c / block) * 2 * block + c % block : c;
+    const float g = to_float(gate_up[r * 2 * inter + gc]);
+    const float u = to_float(gate_up[r * 2 * inter + gc + (block ? block : inter)]);
     const float s = g / (1.0f + expf(-g));
     out[idx] = from_float<T>(s * u);
   }
 }
 
 template <typename T>
-__global__ void silu_mul_wide_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_rows, int inter) {
+__global__ void silu_mul_wide_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int n_rows, int inter,
+                                     int block) {
   pdl_trigger();
   pdl_wait();
   const int per_row = inter / 8;
@@ -312,8 +317,9 @@ __global__ void silu_mul_wide_kernel(const T* __restrict__ gate_up, T* __restric
     const size_t r = idx / per_row;
     const int c = (int)(idx - r * per_row) * 8;
     float g[8], u[8], y[8];
-    Vec8<T>::load(gate_up + r * 2 * inter + c, g);
-    Vec8<T>::load(gate_up + r * 2 * inter + inter + c, u);
+    const int gc = block ? (c / block) * 2 * block + c % block : c;
+    Vec8<T>::load(gate_up + r * 2 * inter + gc, g);
+    Vec8<T>::load(gate_up + r * 2 * inter + gc + (block ? block : inter), u);
 #pragma unroll
     for (int e = 0; e < 8; ++e) y[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
     Vec8<T>::store(out + r * inter + c, y);
@@ -321,25 +327,28 @@ __global__ void silu_mul_wide_kernel(const T* __restrict__ gate_up, T* __restric
 }
 
 template <typename T>
-static int silu_mul_launch(const T* gate_up, T* out, int n_rows, int inter, cudaStream_t stream) {
+static int silu_mul_launch(const T* gate_up, T* out, int n_rows, int inter, int block, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  if (inter % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
+  if (block < 0 || (block > 0 && inter % block)) return (int)cudaErrorInvalidValue;
+  if (inter % 8 == 0 && block % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
     const size_t chunks = (size_t)n_rows * (inter / 8);
     int wide_blocks = (int)((chunks + 255) / 256);
     if (wide_blocks > 148 * 16) wide_blocks = 148 * 16;
-    return gllm_launch(silu_mul_wide_kernel<T>, dim3(wide_blocks), dim3(256), 0, stream, gate_up, out, n_rows, inter);
+    return gllm_launch(silu_mul_wide_kernel<T>, dim3(wide_blocks), dim3(256), 0, stream, gate_up, out, n_rows, inter,
+                       block);
   }
   const size_t total = (size_t)n_rows * inter;
   int blocks = (int)((total + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  return gllm_launch(silu_mul_kernel<T>, dim3(blocks), dim3(256), 0, stream, gate_up, out, n_rows, inter);
+  return gllm_launch(silu_mul_kernel<T>, dim3(blocks), dim3(256), 0, stream, gate_up, out, n_rows, inter, block);
 }
-GLLM_API int gllm_silu_mul_f32(const float* gate_up, float* out, int n_rows, int inter, cudaStream_t stream) {
-  return silu_mul_launch<float>(gate_up, out, n_rows, inter, stream);
+GLLM_API int gllm_silu_mul_f32(const float* gate_up, float* out, int n_rows, int inter, int block,
+                               cudaStream_t stream) {
+  return silu_mul_launch<float>(gate_up, out, n_rows, inter, block, stream);
 }
-GLLM_API int gllm_silu_mul_bf16(const __nv_bfloat16* gate_up, __nv_bfloat16* out, int n_rows, int inter,
+GLLM_API int gllm_silu_mul_bf16(const __nv_bfloat16* gate_up, __nv_bfloat16* out, int n_rows, int inter, int block,
                                 cudaStream_t stream) {
-  return silu_mul_launch<__nv_bfloat16>(gate_up, out, n_rows, inter, stream);
+  return silu_mul_launch<__nv_bfloat16>(gate_up, out, n_rows, inter, block, stream);
 }
 
 // ------------------------------------------- rotary positions + cache store

@@ -166,7 +166,10 @@ __device__ __forceinline__ Item item_of(int w, int tiles_a, int splits) {
 
 // SWAPPED = false: A = X (tile rows are tokens), B = W (tile columns are weight rows).
 // SWAPPED = true : A = W (tile rows are weight rows), B = X (tile columns are tokens).
-template <int BN, bool SWAPPED, typename OutT>
+// GATED: the weight rows come in blocks of 64 gate rows followed by the 64 up rows of the same
+// features; the epilogue writes silu(gate) * up, [M, N/2] (gllm/model/layers/mlp.py:44-47), instead
+// of the [M, N] product.  Only with splits == 1.
+template <int BN, bool SWAPPED, typename OutT, bool GATED>
 __global__ void __launch_bounds__(THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  OutT* __restrict__ out, int M, int N, int K, int64_t ldo, int splits, int kb_per_split,
@@ -296,6 +299,68 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       }
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
       float* mine = partial + (int64_t)item.split * M * N;
+      if (GATED) {
+        const int n_out = N / 2;
+        if (!SWAPPED) {
+          // this thread's token row holds, per 128 columns, 64 gates then their 64 ups
+          const int m = item.a_row0 + row;
+#pragma unroll 1
+          for (int c2 = 0; c2 < BN / 2; c2 += 16) {
+            const int gate_col = (c2 / 64) * 128 + (c2 % 64);
+            float g[16], u[16];
+            tmem_ld16(taddr + (uint32_t)gate_col, g);
+            tmem_ld16(taddr + (uint32_t)(gate_col + 64), u);
+            const int f0 = item.b_row0 / 2 + c2;
+            if (m < M && f0 < n_out) {
+              float y[16];
+#pragma unroll
+              for (int i = 0; i < 16; ++i) y[i] = g[i] / (1.0f + __expf(-g[i])) * u[i];
+              OutT* dst = out + (int64_t)m * ldo + f0;
+              if (f0 + 16 <= n_out && sizeof(OutT) == 2 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+                uint4 p0, p1;
+                __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&p0);
+                __nv_bfloat162* h1 = reinterpret_cast<__nv_bfloat162*>(&p1);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  h0[i] = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
+                  h1[i] = __floats2bfloat162_rn(y[8 + 2 * i], y[8 + 2 * i + 1]);
+                }
+                reinterpret_cast<uint4*>(dst)[0] = p0;
+                reinterpret_cast<uint4*>(dst)[1] = p1;
+              } else {
+                for (int i = 0; i < 16 && f0 + i < n_out; ++i) dst[i] = cast_out<OutT>(y[i]);
+              }
+            }
+          }
+        } else {
+          // rows 0..63 of the tile are gates, rows 64..127 the ups of the same 64 features: the
+          // upper half hands its values to the lower half through shared memory
+          __shared__ float exch[64][(BN <= 64 ? BN : 1) + 1];
+#pragma unroll 1
+          for (int c = 0; c < BN; c += 16) {
+            float v[16];
+            tmem_ld16(taddr + (uint32_t)c, v);
+            if (row >= 64) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) exch[row - 64][c + i] = v[i];
+            }
+            epilogue_sync();
+            if (row < 64) {
+              const int f = item.a_row0 / 2 + row;
+              if (f < n_out) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  const int m = item.b_row0 + c + i;
+                  if (m < M) {
+                    const float g = v[i], u = exch[row][c + i];
+                    out[(int64_t)m * ldo + f] = cast_out<OutT>(g / (1.0f + __expf(-g)) * u);
+                  }
+                }
+              }
+            }
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN; c += 16) {
         float v[16];
@@ -424,7 +489,7 @@ int sm_count() {
   return n;
 }
 
-template <int BN, bool SWAPPED, typename OutT>
+template <int BN, bool SWAPPED, typename OutT, bool GATED>
 int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int64_t ldx,
                 int64_t ldw, int64_t ldo, int splits, float* partial, int* tickets, int reduce_in_kernel, int* status,
                 cudaStream_t stream) {
@@ -435,7 +500,7 @@ int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M
   if (!ok) return (int)cudaErrorInvalidValue;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<BN, SWAPPED, OutT>,
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<BN, SWAPPED, OutT, GATED>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
@@ -446,17 +511,17 @@ int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M
   const int tiles_a = (a_rows + BM - 1) / BM, tiles_b = (b_rows + BN - 1) / BN;
   const int num_items = tiles_a * tiles_b * splits;
   const int grid = num_items < sm_count() ? num_items : sm_count();
-  return gllm_launch(umma_gemm_kernel<BN, SWAPPED, OutT>, dim3(grid), dim3(THREADS), (size_t)S::SMEM, stream, map_a,
+  return gllm_launch(umma_gemm_kernel<BN, SWAPPED, OutT, GATED>, dim3(grid), dim3(THREADS), (size_t)S::SMEM, stream, map_a,
                      map_b, out, M, N, K, ldo, splits, kb_per_split, tiles_a, num_items, partial, tickets,
                      reduce_in_kernel, status);
 }
 
-template <typename OutT>
+template <typename OutT, bool GATED>
 int umma_dispatch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int64_t ldx,
                   int64_t ldw, int64_t ldo, int splits, float* partial, int* tickets, int reduce_in_kernel, int* status,
                   cudaStream_t stream) {
 #define GLLM_UMMA(BN, SW) \
-  return umma_launch<BN, SW, OutT>(X, W, out, M, N, K, ldx, ldw, ldo, splits, partial, tickets, reduce_in_kernel, \
+  return umma_launch<BN, SW, OutT, GATED>(X, W, out, M, N, K, ldx, ldw, ldo, splits, partial, tickets, reduce_in_kernel, \
                                    status, stream)
   if (M <= 16) GLLM_UMMA(16, true);
   if (M <= 32) GLLM_UMMA(32, true);
@@ -499,8 +564,22 @@ GLLM_API int gllm_gemm_bf16(const __nv_bfloat16* X, const __nv_bfloat16* W, void
       (reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
     return (int)cudaErrorInvalidValue;
   if (out_is_f32)
-    return umma_dispatch<float>(X, W, (float*)out, M, N, K, ldx, ldw, ldo, splits, partial, tickets, reduce_in_kernel,
+    return umma_dispatch<float, false>(X, W, (float*)out, M, N, K, ldx, ldw, ldo, splits, partial, tickets, reduce_in_kernel,
                                 status, stream);
-  return umma_dispatch<__nv_bfloat16>(X, W, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, splits, partial, tickets,
-                                      reduce_in_kernel, status, stream);
+  return umma_dispatch<__nv_bfloat16, false>(X, W, (__nv_bfloat16*)out, M, N, K, ldx, ldw, ldo, splits, partial,
+                                             tickets, reduce_in_kernel, status, stream);
+}
+
+// The gated feed-forward's first product with SiLU(gate) * up in the epilogue: W is [2*I, K] with
+// rows in blocks of 64 gate rows followed by the 64 up rows of the same features (I % 64 == 0);
+// out is [M, I] bf16.  Never cut along K.
+GLLM_API int gllm_gemm_bf16_gated(const __nv_bfloat16* X, const __nv_bfloat16* W, __nv_bfloat16* out, int M,
+                                  int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int* status,
+                                  cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || N % 128 || (reinterpret_cast<uintptr_t>(X) & 15) ||
+      (reinterpret_cast<uintptr_t>(W) & 15))
+    return (int)cudaErrorInvalidValue;
+  return umma_dispatch<__nv_bfloat16, true>(X, W, out, M, N, K, ldx, ldw, ldo, 1, nullptr, nullptr, 0, status,
+                                            stream);
 }

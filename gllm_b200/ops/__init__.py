@@ -34,6 +34,8 @@ __all__ = [
     "argmax",
     "SplitSum",
     "as_tensor",
+    "linear_gated",
+    "interleave_gate_up",
 ]
 
 P = c_void_p
@@ -42,7 +44,7 @@ _SIGNATURES = {
         "gllm_embedding_{t}": [P, P, P, P, P, c_int, c_int, c_int, P, P],
         "gllm_add_rmsnorm_{t}": [P, P, c_int, c_int64, P, P, P, P, c_int, c_int, c_float, c_int, P],
         "gllm_sum_parts_{t}": [P, c_int, c_int64, P, c_int64, P],
-        "gllm_silu_mul_{t}": [P, P, c_int, c_int, P],
+        "gllm_silu_mul_{t}": [P, P, c_int, c_int, c_int, P],
         "gllm_rope_store_{t}": [P, P, c_int, c_int64, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_int, P, P],
     },
@@ -273,8 +275,12 @@ def add_rmsnorm(
 
 
 # ------------------------------------------------------------------ SiLU·up
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``silu(gate) * up`` of ``[n, 2*inter]`` (gate first)."""
+GATED_BLOCK = 64
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None, block: int = 0) -> torch.Tensor:
+    """``silu(gate) * up`` of ``[n, 2*inter]``.  ``block`` 0: gate columns first, up columns after;
+    ``block`` b: b gate columns alternate with the b up columns of the same features."""
     _cuda(gate_up, "gate_up")
     n, two_i = gate_up.shape
     if two_i % 2:
@@ -283,8 +289,33 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor | None = None) -> torch.Te
     if out is None:
         out = torch.empty((n, inter), dtype=gate_up.dtype, device=gate_up.device)
     f = _fn("elementwise", f"gllm_silu_mul_{_suffix(gate_up.dtype)}")
-    _check(f(gate_up.data_ptr(), out.data_ptr(), n, inter, _stream()), "silu_mul")
+    _check(f(gate_up.data_ptr(), out.data_ptr(), n, inter, int(block), _stream()), "silu_mul")
     return out
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int = GATED_BLOCK) -> torch.Tensor:
+    """Stack ``gate`` and ``up`` ``[inter, hidden]`` so that ``block`` gate rows alternate with the
+    ``block`` up rows of the same features (``inter`` must be a multiple of ``block``)."""
+    inter, hidden = gate.shape
+    if inter % block:
+        raise ValueError("intermediate size must be a multiple of the block")
+    stacked = torch.stack([gate.view(inter // block, block, hidden), up.view(inter // block, block, hidden)], dim=1)
+    return stacked.reshape(2 * inter, hidden).contiguous()
+
+
+def linear_gated(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``silu(x @ Wg.T) * (x @ Wu.T)`` for a weight stacked by ``interleave_gate_up``: one kernel
+    with the activation in the product's epilogue where the tensor-core kernel takes the operands,
+    the product and ``silu_mul`` otherwise."""
+    _cuda(x, "x")
+    _cuda(weight, "weight", x.dtype)
+    if x.dtype == torch.bfloat16:
+        from gllm_b200.ops import gemm_bf16
+
+        fused = gemm_bf16.linear_gated(x, weight)
+        if fused is not None:
+            return fused
+    return silu_mul(linear(x, weight), block=GATED_BLOCK)
 
 
 # --------------------------------------------------- rotary + cache store

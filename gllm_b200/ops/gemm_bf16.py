@@ -48,7 +48,10 @@ def _umma_fns():
         lib.gllm_gemm_bf16_splits.restype = c_int
         lib.gllm_gemm_bf16_tiles.argtypes = [c_int, c_int]
         lib.gllm_gemm_bf16_tiles.restype = c_int
-        _umma = (f, lib.gllm_gemm_bf16_splits, lib.gllm_gemm_bf16_tiles)
+        g = lib.gllm_gemm_bf16_gated
+        g.argtypes = [P, P, P, c_int, c_int, c_int, c_int64, c_int64, c_int64, P, P]
+        g.restype = c_int
+        _umma = (f, lib.gllm_gemm_bf16_splits, lib.gllm_gemm_bf16_tiles, g)
     return _umma
 
 
@@ -76,7 +79,7 @@ def tensor_core_kernel_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     from gllm_b200 import ops
 
-    f, splits_of, tiles_of = _umma_fns()
+    f, splits_of, tiles_of, _ = _umma_fns()
     m, k = x.shape
     n = weight.shape[0]
     splits = splits_of(m, n, k)
@@ -95,7 +98,7 @@ def linear_split(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype):
 
     if _BACKEND != "tcgen05" or not tensor_core_kernel_takes(x, weight):
         return None
-    f, splits_of, tiles_of = _umma_fns()
+    f, splits_of, tiles_of, _ = _umma_fns()
     m, k = x.shape
     n = weight.shape[0]
     splits = splits_of(m, n, k)
@@ -117,4 +120,21 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> tor
     else:
         # fp32 logits from bf16 operands: accumulate and write in fp32
         out.copy_(torch.mm(x, weight.t(), out_dtype=torch.float32))
+    return out
+
+
+def linear_gated(x: torch.Tensor, weight: torch.Tensor):
+    """``silu(gate) * up`` of a weight stacked in blocks of 64 gate / 64 up rows, fused into the
+    product's epilogue; None when the kernel does not take these operands."""
+    from gllm_b200 import ops
+
+    n, k = weight.shape
+    if _BACKEND != "tcgen05" or not tensor_core_kernel_takes(x, weight) or n % 128:
+        return None
+    m = x.shape[0]
+    out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
+    g = _umma_fns()[3]
+    code = g(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), weight.stride(0), out.stride(0),
+             ops.status_word(x.device).data_ptr(), ops._stream())
+    ops._check(code, "gemm_bf16_gated")
     return out

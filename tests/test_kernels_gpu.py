@@ -365,3 +365,24 @@ def test_unsummed_splits_are_summed_by_their_consumers(ops):
     q1 = ops.rope_store(summed.clone(), positions, inv_freq, slots, c1, hq, hkv, d, d)
     q2 = ops.rope_store(ops.linear(x, w, split_ok=True), positions, inv_freq, slots, c2, hq, hkv, d, d)
     assert torch.equal(q1, q2) and torch.equal(c1, c2)
+
+
+@pytest.mark.parametrize("m", [1, 8, 33, 64, 65, 300])
+@pytest.mark.parametrize("inter,k", [(128, 64), (192, 96), (8192, 2048)])
+def test_gemm_gated_epilogue(ops, m, inter, k):
+    """silu(x Wg^T) * (x Wu^T) in the product's epilogue, both orientations, against the plain formula;
+    and the unfused route (product, then silu_mul over the same block layout) gives the same."""
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+    wg = (torch.randn(inter, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).cuda()
+    wu = (torch.randn(inter, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).cuda()
+    w = ops.interleave_gate_up(wg, wu)
+    assert w.shape == (2 * inter, k) and torch.equal(w[:64], wg[:64]) and torch.equal(w[64:128], wu[:64])
+    got = ops.linear_gated(x, w)
+    ops.check_status()
+    a, b = x.double() @ wg.double().T, x.double() @ wu.double().T
+    want = a * torch.sigmoid(a) * b
+    assert got.shape == (m, inter) and got.dtype == torch.bfloat16
+    torch.testing.assert_close(got.double(), want, rtol=2e-2, atol=2e-2)
+    unfused = ops.silu_mul(ops.linear(x, w), block=64)
+    torch.testing.assert_close(unfused.double(), want, rtol=3e-2, atol=3e-2)
