@@ -35,22 +35,25 @@ def _time(fn, iters: int, flush) -> float:
     return times[len(times) // 2]
 
 
-def _paged_cache(batch, context, hkv, d, block_size, extra_tokens=0):
-    """A pool holding ``batch`` requests of ``context`` tokens on scattered pages."""
+def _paged_cache(batch, context, hkv, d, block_size, extra_tokens=0, sequential=0):
+    """A pool holding ``batch`` requests of ``context`` tokens on scattered pages
+    (``sequential``: each request's pages lie one after another instead)."""
     pages_per_req = -(-(context + extra_tokens) // block_size)
     num_pages = batch * pages_per_req + 1
     g = torch.Generator(device="cuda").manual_seed(0)
     pool = torch.randn((num_pages, 2, hkv, block_size, d), generator=g, device="cuda", dtype=torch.float32)
     pool = pool.to(torch.bfloat16)
     perm = torch.randperm(num_pages - 1, generator=g, device="cuda").to(torch.int32)
+    if sequential:
+        perm = torch.arange(num_pages - 1, device="cuda", dtype=torch.int32)
     table = perm[: batch * pages_per_req].view(batch, pages_per_req).contiguous()
     return pool, table
 
 
-def attention_decode(batch=64, context=2048, hq=32, hkv=8, d=64, block_size=16, iters=5, peaks=None):
+def attention_decode(batch=64, context=2048, hq=32, hkv=8, d=64, block_size=16, iters=5, peaks=None, sequential=0):
     from gllm_b200.ops import attention_bf16
 
-    pool, table = _paged_cache(batch, context, hkv, d, block_size)
+    pool, table = _paged_cache(batch, context, hkv, d, block_size, sequential=sequential)
     qkv = torch.randn(batch, (hq + 2 * hkv) * d, device="cuda").to(torch.bfloat16)
     positions = torch.full((batch,), context - 1, dtype=torch.int32, device="cuda")
     rows = torch.arange(batch, dtype=torch.int32, device="cuda")

@@ -149,6 +149,13 @@ def compile_module(module: str, verbose: bool = True) -> Path:
             pass
         raise ExtensionError(f"nvcc failed on {source.name} (exit {proc.returncode}):\n{output}")
     os.replace(tmp_out, out)
+    # libraries of older versions of this module's source are of no use any more
+    for old in out_dir.glob(f"gllm_{module}.*.so"):
+        if old != out:
+            try:
+                old.unlink()
+            except OSError:
+                pass
     if verbose:
         print(f"[gllm_b200] built {out.name} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
     return out
