@@ -1,0 +1,406 @@
+// Causal prefill attention over the paged cache on the 5th-generation tensor cores.
+//
+// The same job as attention_prefill_bf16.cu (portions of prompts attend over everything their
+// request has cached, through the block table; replaces the reference's gather + dense
+// softmax(QK^T/sqrt(D) + bias)V, gllm/model/layers/attention.py:165-173,
+// gllm/ops/attention/reference_attention.py:40-48), but both products run as tcgen05.mma with
+// their accumulators in tensor memory, so they take no issue slots from the softmax:
+//
+//   one CTA = 128 rows (128/G' query tokens x the G' query heads of one kv head), key tiles of 128;
+//   warp 0 (one thread): TMA loads. Q once (a 3-D box: 64 dims x G' heads x tokens), then per key
+//           tile the K and V pages, one box per page, straight out of the cache pool, 128-byte swizzle;
+//   warp 1 (one thread): S = Q K^T into tensor memory (128 x 128 fp32), later O += P V (128 x D);
+//   warps 2-5 (one thread per row): read S from tensor memory, mask, running maximum and sum in
+//           fp32, rescale O in tensor memory when the maximum moved, write P (bf16) into shared
+//           memory in the swizzled layout the second product reads, at the end O / sum -> global.
+//
+// V is used as it lies in the cache ([key][dim], i.e. the "MN-major" operand of the second
+// product); nothing is transposed or gathered.  Keys outside a row's view get probability 0 and the
+// value rows that hold no key of the request yet are zeroed in shared memory before they are
+// multiplied, so stale pool contents never reach the output.  Every mbarrier wait is bounded.
+// No TMA load uses cluster multicast.
+#include "umma_utils.cuh"
+
+namespace {
+constexpr int BM = 128, BN = 128, THREADS = 192;
+
+template <int D>
+struct TShape {
+  static constexpr int DB = D / 64;                     // 64-wide blocks of the head dimension
+  static constexpr int TILE = 128 * 128;                // bytes of a [128 x 64] bf16 tile
+  static constexpr int Q_BYTES = DB * TILE;
+  static constexpr int KV_STAGE = DB * TILE;            // K (or V) of one key tile
+  static constexpr int P_BYTES = 2 * TILE;              // [128 rows x 128 keys] as two 64-key blocks
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + Q_BYTES;         // 2 stages
+  static constexpr int OFF_V = OFF_K + 2 * KV_STAGE;    // 2 stages
+  static constexpr int OFF_P = OFF_V + 2 * KV_STAGE;
+  static constexpr int SMEM = OFF_P + P_BYTES + 1024;
+  static constexpr int TMEM_COLS = 256;                 // S: 128 columns, O: D columns
+  static constexpr int COL_S = 0, COL_O = 128;
+};
+
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
+                    __nv_bfloat16* __restrict__ out, int64_t out_stride, const int* __restrict__ block_table,
+                    int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
+                    const int* __restrict__ slots, int hq, int hkv, int gp, int block_size, int num_pages,
+                    float scale_log2, int window, int* __restrict__ status) {
+  using S = TShape<D>;
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], kv_empty[2], s_full, p_full, o_ready;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  pdl_trigger();
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t base = (smem_addr(smem_dyn) + 1023u) & ~1023u;
+  unsigned char* base_ptr = smem_dyn + (base - smem_addr(smem_dyn));
+
+  // ---- which rows and keys this CTA owns (host-side sizes only; device data is read after pdl_wait)
+  const int r = blockIdx.z;
+  const int group = hq / hkv;
+  const int tiles_per_kv = group / gp;
+  const int kvh = blockIdx.y / tiles_per_kv;
+  const int h0 = kvh * group + (blockIdx.y - kvh * tiles_per_kv) * gp;
+  const int qt = BM / gp;                               // query tokens per CTA
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_addr(&q_full), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_addr(&k_full[s]), 1);
+      mbar_init(smem_addr(&v_full[s]), 1);
+      mbar_init(smem_addr(&kv_empty[s]), 1);
+    }
+    mbar_init(smem_addr(&s_full), 1);
+    mbar_init(smem_addr(&p_full), 4);                   // one arrival per softmax warp
+    mbar_init(smem_addr(&o_ready), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(&tmem_base_slot)),
+                 "r"((uint32_t)S::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+  pdl_wait();
+
+  const int tok_begin = cu_q[r], q_len = cu_q[r + 1] - tok_begin;
+  const int n_qtiles = (q_len + qt - 1) / qt;
+  const bool active = (int)blockIdx.x < n_qtiles;       // uniform over the CTA
+  const int qtile = n_qtiles - 1 - (int)blockIdx.x;     // longest rows first
+  const int t0 = qtile * qt;
+  const int t_count = active ? min(qt, q_len - t0) : 0;
+  const int ctx = ctx_lens[r];
+  const int pos_first = ctx + t0, pos_last = ctx + t0 + t_count - 1;
+  const int kv_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+  const int tile_first = kv_lo / BN, tile_last = pos_last / BN;
+  const int n_tiles = active ? tile_last - tile_first + 1 : 0;
+
+  if (active && warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      const int* bt = block_table + (int64_t)slots[r] * bt_stride;
+      const int null_page = num_pages - 1;              // the cache's spare page: always there, never a request's
+      const int pages_per_tile = BN / block_size;
+      mbar_expect_tx(smem_addr(&q_full), (uint32_t)S::Q_BYTES);
+      for (int db = 0; db < S::DB; ++db)
+        tma_load_3d(base + S::OFF_Q + db * S::TILE, &map_q, db * 64, h0, tok_begin + t0, smem_addr(&q_full));
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(smem_addr(&kv_empty[s]), ((uint32_t)(j >> 1) & 1u) ^ 1u, status, &abort_flag)) break;
+        const int key0 = (tile_first + j) * BN;
+        mbar_expect_tx(smem_addr(&k_full[s]), (uint32_t)S::KV_STAGE);
+        mbar_expect_tx(smem_addr(&v_full[s]), (uint32_t)S::KV_STAGE);
+        for (int p = 0; p < pages_per_tile; ++p) {
+          const int key = key0 + p * block_size;
+          int page = null_page;
+          if (key <= pos_last && key + block_size > kv_lo) {
+            page = bt[key / block_size];
+            if (page < 0 || page >= num_pages) {
+              if (page >= num_pages) atomicOr(status, GLLM_STATUS_PAGE_RANGE);
+              page = null_page;
+            }
+          }
+          const int row_k = ((page * 2 + 0) * hkv + kvh) * block_size;
+          const int row_v = ((page * 2 + 1) * hkv + kvh) * block_size;
+          for (int db = 0; db < S::DB; ++db) {
+            const uint32_t off = (uint32_t)(s * S::KV_STAGE + db * S::TILE + p * block_size * 128);
+            tma_load_2d(base + S::OFF_K + off, &map_kv, db * 64, row_k, smem_addr(&k_full[s]));
+            tma_load_2d(base + S::OFF_V + off, &map_kv, db * 64, row_v, smem_addr(&v_full[s]));
+          }
+        }
+      }
+    }
+  } else if (active && warp == 1) {
+    // -------------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc(BM, BN);
+      constexpr uint32_t idesc_o = umma_idesc_b_mn(BM, 64);
+      const uint32_t tmem_s = tmem_base + S::COL_S, tmem_o = tmem_base + S::COL_O;
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1;
+        if (!mbar_wait(smem_addr(&k_full[s]), (uint32_t)(j >> 1) & 1u, status, &abort_flag)) return false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int db = 0; db < S::DB; ++db)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_bf16(tmem_s, umma_desc(base + S::OFF_Q + db * S::TILE + k * 32),
+                      umma_desc(base + S::OFF_K + s * S::KV_STAGE + db * S::TILE + k * 32), idesc_s,
+                      (db > 0 || k > 0) ? 1u : 0u);
+        umma_commit(smem_addr(&s_full));
+        return true;
+      };
+      bool ok = mbar_wait(smem_addr(&q_full), 0u, status, &abort_flag);
+      if (ok) ok = issue_s(0);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j & 1;
+        ok = mbar_wait(smem_addr(&p_full), (uint32_t)j & 1u, status, &abort_flag);
+        if (ok) ok = mbar_wait(smem_addr(&v_full[s]), (uint32_t)(j >> 1) & 1u, status, &abort_flag);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+        for (int db = 0; db < S::DB; ++db)
+#pragma unroll
+          for (int k = 0; k < 8; ++k)      // 16 keys per MMA: P block k/4, 32 bytes per step; V rows 16 k ..
+            umma_bf16(tmem_o + db * 64, umma_desc(base + S::OFF_P + (k >> 2) * S::TILE + (k & 3) * 32),
+                      umma_desc(base + S::OFF_V + s * S::KV_STAGE + db * S::TILE + k * 16 * 128), idesc_o,
+                      (j > 0 || k > 0) ? 1u : 0u);
+        umma_commit(smem_addr(&kv_empty[s]));           // K and V of this stage are consumed
+        umma_commit(smem_addr(&o_ready));               // O holds tiles 0 .. j
+        if (j + 1 < n_tiles) ok = issue_s(j + 1);
+      }
+    }
+  } else if (active && warp >= 2) {
+    // ------------------------------------------------- softmax, correction, epilogue
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;                 // row of the tile = TMEM lane
+    const int tl = row / gp, g = row - tl * gp;
+    const bool row_ok = tl < t_count;
+    const int qpos = pos_first + tl;
+    const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
+    const uint32_t tmem_s = tmem_base + S::COL_S + lane_addr, tmem_o = tmem_base + S::COL_O + lane_addr;
+    unsigned char* p_row = base_ptr + S::OFF_P + row * 128;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      const int s = j & 1;
+      const int kv0 = (tile_first + j) * BN;
+      mbar_wait(smem_addr(&s_full), (uint32_t)j & 1u, status, &abort_flag);
+      asm volatile("bar.sync 1, 128;" ::: "memory");     // the four warps go on together
+      if (abort_flag) { ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const bool need_mask = (kv0 + BN - 1 > pos_first) || window > 0 || t_count < qt;
+      // pass 1: this row's maximum over the tile
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        float v[32];
+        tmem_ld32(tmem_s + (uint32_t)c, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int key = kv0 + c + i;
+          const bool hidden = need_mask && (!row_ok || key > qpos || (window > 0 && key <= qpos - window));
+          mx = fmaxf(mx, hidden ? -INFINITY : v[i]);
+        }
+      }
+      const float m_new = fmaxf(m, mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float corr = m == -INFINITY ? 0.f : exp2f((m - m_use) * scale_log2);
+      const float neg_mc = -m_use * scale_log2;
+      // the output so far is rescaled when some row of the warp saw its maximum move
+      if (j > 0) {
+        mbar_wait(smem_addr(&o_ready), (uint32_t)(j - 1) & 1u, status, &abort_flag);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            float v[32];
+            tmem_ld32(tmem_o + (uint32_t)c, v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= corr;
+            tmem_st32(tmem_o + (uint32_t)c, v);
+          }
+        }
+      }
+      m = m_new;
+      l *= corr;
+      // pass 2: probabilities -> shared memory (bf16, the layout the second product reads)
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        float v[32];
+        tmem_ld32(tmem_s + (uint32_t)c, v);
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0, p1;
+          {
+            const int key = kv0 + c + i;
+            const bool h0m = need_mask && (!row_ok || key > qpos || (window > 0 && key <= qpos - window));
+            const bool h1m = need_mask && (!row_ok || key + 1 > qpos || (window > 0 && key + 1 <= qpos - window));
+            p0 = h0m ? 0.f : exp2f(fmaf(v[i], scale_log2, neg_mc));
+            p1 = h1m ? 0.f : exp2f(fmaf(v[i + 1], scale_log2, neg_mc));
+          }
+          l += p0 + p1;
+          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        // keys c .. c+31 = four 16-byte pieces of block c/64; piece index XOR (row % 8)
+        unsigned char* blk = p_row + (c >> 6) * S::TILE;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int piece = ((c & 63) >> 3) + q4;
+          *reinterpret_cast<uint4*>(blk + ((piece ^ (row & 7)) << 4)) =
+              make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+        }
+      }
+      // value rows of keys the request does not hold (yet): zero them so 0 * stale never matters
+      if (kv0 + BN - 1 > pos_last || kv0 < kv_lo) {
+        mbar_wait(smem_addr(&v_full[s]), (uint32_t)(j >> 1) & 1u, status, &abort_flag);
+        const int key = kv0 + row;                       // thread <-> key row of the V tile
+        if (key > pos_last || key < kv_lo) {
+          for (int db = 0; db < S::DB; ++db) {
+            uint4* vrow = reinterpret_cast<uint4*>(base_ptr + S::OFF_V + s * S::KV_STAGE + db * S::TILE + row * 128);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) vrow[i] = make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P and V writes -> visible to the tensor core
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_addr(&p_full));
+    }
+    // ---- O / l -> global
+    if (ok && n_tiles > 0) {
+      mbar_wait(smem_addr(&o_ready), (uint32_t)(n_tiles - 1) & 1u, status, &abort_flag);
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!abort_flag) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        __nv_bfloat16* dst = out + (int64_t)(tok_begin + t0 + tl) * out_stride + (int64_t)(h0 + g) * D;
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          float v[32];
+          tmem_ld32(tmem_o + (uint32_t)c, v);            // every lane takes part in the load
+          if (row_ok) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 pk;
+              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                h[i] = __floats2bfloat162_rn(v[q4 * 8 + 2 * i] * inv, v[q4 * 8 + 2 * i + 1] * inv);
+              *reinterpret_cast<uint4*>(dst + c + q4 * 8) = pk;
+            }
+          }
+        }
+      }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+template <int D>
+int prefill_tmem_launch(const __nv_bfloat16* q, int64_t q_stride, __nv_bfloat16* out, int64_t out_stride,
+                        const __nv_bfloat16* cache, const int* block_table, int bt_stride, const int* cu_q,
+                        const int* ctx_lens, const int* slots, int num_requests, int max_q_len, int n_tokens,
+                        int hq, int hkv, int block_size, int num_pages, float scale, int window, int* status,
+                        cudaStream_t stream) {
+  using S = TShape<D>;
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return (int)cudaErrorNotSupported;
+  const int group = hq / hkv;
+  const int gp = (group <= BM && BM % group == 0) ? group : 1;
+  const int qt = BM / gp;
+  CUtensorMap map_q, map_kv;
+  {
+    // q as [tokens][heads][D]: boxes of 64 dims x gp heads x qt tokens
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)hq, (cuuint64_t)n_tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)q_stride * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)gp, (cuuint32_t)qt};
+    cuuint32_t elem[3] = {1, 1, 1};
+    if (fn(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<__nv_bfloat16*>(q), dims, strides, box, elem,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return (int)cudaErrorInvalidValue;
+  }
+  {
+    // the cache layer as rows of D: [pages * 2 * kv_heads * block_size][D]; one box = one page of one head
+    cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * 2 * hkv * block_size};
+    cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)block_size};
+    cuuint32_t elem[2] = {1, 1};
+    if (fn(&map_kv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(cache), dims, strides, box,
+           elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return (int)cudaErrorInvalidValue;
+  }
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_tmem_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  dim3 grid((max_q_len + qt - 1) / qt, hkv * (group / gp), num_requests);
+  return gllm_launch(prefill_tmem_kernel<D>, grid, dim3(THREADS), (size_t)S::SMEM, stream, map_q, map_kv, out,
+                     out_stride, block_table, bt_stride, cu_q, ctx_lens, slots, hq, hkv, gp, block_size, num_pages,
+                     scale * 1.4426950408889634f, window, status);
+}
+}  // namespace
+
+// 1 when the kernel takes this head size and page size.
+GLLM_API int gllm_attention_prefill_tmem_supports(int d, int block_size) {
+  return (d == 64 || d == 128) && block_size >= 8 && block_size <= 128 && (block_size & (block_size - 1)) == 0;
+}
+
+// As gllm_attention_prefill_bf16, plus n_tokens (rows of q).  q and the cache layer must be 16-byte
+// aligned, q_stride a multiple of 8; num_pages counts the cache's spare last page, which must exist.
+GLLM_API int gllm_attention_prefill_tmem(const __nv_bfloat16* q, int64_t q_stride, __nv_bfloat16* out,
+                                         int64_t out_stride, const __nv_bfloat16* cache, const int* block_table,
+                                         int bt_stride, const int* cu_q, const int* ctx_lens, const int* slots,
+                                         int num_requests, int max_q_len, int n_tokens, int hq, int hkv, int d,
+                                         int block_size, int num_pages, float scale, int window, int* status,
+                                         cudaStream_t stream) {
+  if (num_requests <= 0 || max_q_len <= 0) return 0;
+  if (!gllm_attention_prefill_tmem_supports(d, block_size) || hq <= 0 || hkv <= 0 || hq % hkv ||
+      num_requests > 65535 || (q_stride % 8) || (out_stride % 8) || (reinterpret_cast<uintptr_t>(q) & 15) ||
+      (reinterpret_cast<uintptr_t>(cache) & 15) || (reinterpret_cast<uintptr_t>(out) & 15) || num_pages < 1)
+    return (int)cudaErrorInvalidValue;
+  if (d == 64)
+    return prefill_tmem_launch<64>(q, q_stride, out, out_stride, cache, block_table, bt_stride, cu_q, ctx_lens, slots,
+                                   num_requests, max_q_len, n_tokens, hq, hkv, block_size, num_pages, scale, window,
+                                   status, stream);
+  return prefill_tmem_launch<128>(q, q_stride, out, out_stride, cache, block_table, bt_stride, cu_q, ctx_lens, slots,
+                                  num_requests, max_q_len, n_tokens, hq, hkv, block_size, num_pages, scale, window,
+                                  status, stream);
+}

@@ -28,9 +28,7 @@
 // again), frees its tensor memory and returns.
 //
 // No TMA load here uses cluster multicast; every CTA fetches its own tiles.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "umma_utils.cuh"
 
 namespace {
 constexpr int BM = 128;          // rows of the accumulator tile (MMA M)
@@ -38,95 +36,6 @@ constexpr int BK = 64;           // k per stage: 64 bf16 = one 128-byte swizzle 
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr int SMEM_BUDGET = 200 * 1024;
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ unsigned long long global_timer() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-// Bounded wait: false (and a status bit) when the phase does not complete in time.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_timer();
-  uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 1023u) == 0) {
-      if (*abort_flag) return false;
-      if (global_timer() - t0 > WAIT_LIMIT_NS) {
-        atomicOr(status, GLLM_STATUS_WAIT_TIMEOUT);
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-  return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-      : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte swizzle,
-// 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((addr >> 4) & 0x3FFF);
-  d |= (uint64_t)1 << 16;                 // leading byte offset (unused with a swizzled K-major tile)
-  d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                 // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
-  return d;
-}
-// Instruction descriptor of kind::f16: bf16 x bf16 -> fp32, both operands K-major.
-__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                          uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 template <typename OutT> __device__ __forceinline__ OutT cast_out(float v);
 template <> __device__ __forceinline__ float cast_out<float>(float v) { return v; }
@@ -142,9 +51,6 @@ struct Shape {
   static constexpr int SMEM = STAGES * STAGE + 1024;                         // + slack to align the base
 };
 
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
 struct Item {
@@ -238,7 +144,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (uint32_t i = first; i < it; ++i) {
           const unsigned long long t0 = global_timer();
           while (!mbar_try_wait(smem_addr(&full_bar[i % S::STAGES]), (i / S::STAGES) & 1u)) {
-            if (global_timer() - t0 > WAIT_LIMIT_NS) break;
+            if (global_timer() - t0 > UMMA_WAIT_LIMIT_NS) break;
           }
         }
       }

@@ -34,6 +34,47 @@ def _prefill_fn():
     return _prefill
 
 
+_prefill_tmem = None
+# portions shorter than this run the mma.sync kernel (its 64-row tiles waste less on short portions)
+TMEM_MIN_Q_LEN = 32
+
+
+def _prefill_tmem_fn():
+    global _prefill_tmem
+    if _prefill_tmem is None:
+        lib = load_module("attention_prefill_tmem")
+        f = lib.gllm_attention_prefill_tmem
+        f.argtypes = [P, c_int64, P, c_int64, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                      c_int, c_float, c_int, P, P]
+        f.restype = c_int
+        lib.gllm_attention_prefill_tmem_supports.argtypes = [c_int, c_int]
+        lib.gllm_attention_prefill_tmem_supports.restype = c_int
+        _prefill_tmem = (f, lib.gllm_attention_prefill_tmem_supports)
+    return _prefill_tmem
+
+
+def prefill_tmem_supports(head_dim: int, block_size: int, q: torch.Tensor, cache_layer: torch.Tensor) -> bool:
+    return (head_dim in (64, 128) and bool(_prefill_tmem_fn()[1](head_dim, block_size))
+            and q.data_ptr() % 16 == 0 and cache_layer.data_ptr() % 16 == 0 and q.stride(0) % 8 == 0)
+
+
+def prefill_attention_tmem(q, q_stride, cache_layer, block_table, cu_q, ctx_lens, slots, num_requests, max_q_len,
+                           num_heads, scale, window, out):
+    """tcgen05 attention of the first ``num_requests`` requests of the flat batch.  The cache layer's
+    last page must be the cache's spare page (it stands in for pages a request does not hold)."""
+    from gllm_b200 import ops
+
+    num_pages, _, hkv, block_size, d = cache_layer.shape
+    code = _prefill_tmem_fn()[0](
+        q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), cache_layer.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), cu_q.data_ptr(), ctx_lens.data_ptr(), slots.data_ptr(), num_requests, max_q_len,
+        q.shape[0], num_heads, hkv, d, block_size, num_pages, float(scale), int(window),
+        ops.status_word(q.device).data_ptr(), ops._stream(),
+    )
+    ops._check(code, "attention_prefill_tmem")
+    return out
+
+
 def prefill_supports(head_dim: int, block_size: int) -> bool:
     return head_dim in _PREFILL_HEAD_DIMS and (block_size * head_dim) % 8 == 0
 
@@ -116,7 +157,11 @@ def paged_attention_bf16(qkv, cache_layer, block_table, positions, token_row, nu
     n = qkv.shape[0]
     n_pf = batch.num_prefill_tokens
     d, block_size = cache_layer.shape[4], cache_layer.shape[3]
-    if n_pf > 0 and prefill_supports(d, block_size):
+    if n_pf > 0 and batch.max_q_len >= TMEM_MIN_Q_LEN and prefill_tmem_supports(d, block_size, qkv, cache_layer):
+        prefill_attention_tmem(qkv[:n_pf], qkv.shape[1], cache_layer, block_table, batch.cu_q, batch.context_lens,
+                               batch.state_slots, batch.num_prefill_requests, batch.max_q_len, num_heads, scale,
+                               window, out)
+    elif n_pf > 0 and prefill_supports(d, block_size):
         prefill_attention(qkv, qkv.shape[1], cache_layer, block_table, batch.cu_q, batch.context_lens,
                           batch.state_slots, batch.num_prefill_requests, batch.max_q_len, num_heads, scale, window,
                           out)

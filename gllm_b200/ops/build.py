@@ -45,6 +45,7 @@ MODULES = {
     "gemm_bf16": "gemm_bf16.cu",
     "attention_bf16": "attention_bf16.cu",
     "attention_prefill_bf16": "attention_prefill_bf16.cu",
+    "attention_prefill_tmem": "attention_prefill_tmem.cu",
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}
