@@ -7,8 +7,9 @@
 // their accumulators in tensor memory, so they take no issue slots from the softmax:
 //
 //   one CTA = 128 rows (128/G' query tokens x the G' query heads of one kv head), key tiles of 128;
-//   warp 0 (one thread): TMA loads. Q once (a 3-D box: 64 dims x G' heads x tokens), then per key
-//           tile the K and V pages, one box per page, straight out of the cache pool, 128-byte swizzle;
+//   warp 0: TMA loads. Q once (a 3-D box: 64 dims x G' heads x tokens); per key tile the K and V
+//           pages straight out of the cache pool, one box per page, each lane issuing its own page's
+//           boxes, 128-byte swizzle;
 //   warp 1 (one thread): S = Q K^T into tensor memory (128 x 128 fp32), later O += P V (128 x D);
 //   warps 2-5 (one thread per row): read S from tensor memory, mask, running maximum and sum in
 //           fp32, rescale O in tensor memory when the maximum moved, write P (bf16) into shared
@@ -16,13 +17,20 @@
 //
 // V is used as it lies in the cache ([key][dim], i.e. the "MN-major" operand of the second
 // product); nothing is transposed or gathered.  Keys outside a row's view get probability 0 and the
-// value rows that hold no key of the request yet are zeroed in shared memory before they are
+// value rows that hold no key of the request are zeroed in shared memory before they are
 // multiplied, so stale pool contents never reach the output.  Every mbarrier wait is bounded.
 // No TMA load uses cluster multicast.
 #include "umma_utils.cuh"
 
 namespace {
 constexpr int BM = 128, BN = 128, THREADS = 192;
+
+// 2^x in one instruction (ex2.approx: about 2 ulp; -inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <int D>
 struct TShape {
@@ -62,8 +70,8 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int r = blockIdx.z;
   const int group = hq / hkv;
   const int tiles_per_kv = group / gp;
-  const int kvh = blockIdx.y / tiles_per_kv;
-  const int h0 = kvh * group + (blockIdx.y - kvh * tiles_per_kv) * gp;
+  const int kvh = blockIdx.x / tiles_per_kv;
+  const int h0 = kvh * group + (blockIdx.x - kvh * tiles_per_kv) * gp;
   const int qt = BM / gp;                               // query tokens per CTA
 
   if (threadIdx.x == 0) {
@@ -93,8 +101,8 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   const int tok_begin = cu_q[r], q_len = cu_q[r + 1] - tok_begin;
   const int n_qtiles = (q_len + qt - 1) / qt;
-  const bool active = (int)blockIdx.x < n_qtiles;       // uniform over the CTA
-  const int qtile = n_qtiles - 1 - (int)blockIdx.x;     // longest rows first
+  const bool active = (int)blockIdx.y < n_qtiles;       // uniform over the CTA
+  const int qtile = n_qtiles - 1 - (int)blockIdx.y;     // longest rows first (y is the slower grid axis)
   const int t0 = qtile * qt;
   const int t_count = active ? min(qt, q_len - t0) : 0;
   const int ctx = ctx_lens[r];
@@ -105,36 +113,48 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (active && warp == 0) {
     // ------------------------------------------------------------------ TMA producer
+    // The whole warp takes part: lane p looks page p of the tile up and issues the boxes of that page
+    // (one box = the rows of one page of one kv head, 64 dims wide), so the block-table reads and the
+    // copies of a tile are in flight together.  Pages the rows cannot see are not read at all.
+    const int* bt = block_table + (int64_t)slots[r] * bt_stride;
+    const int pages_per_tile = BN / block_size;
+    const uint32_t page_bytes = (uint32_t)(S::DB * block_size * 128);
     if (lane == 0) {
-      const int* bt = block_table + (int64_t)slots[r] * bt_stride;
-      const int null_page = num_pages - 1;              // the cache's spare page: always there, never a request's
-      const int pages_per_tile = BN / block_size;
       mbar_expect_tx(smem_addr(&q_full), (uint32_t)S::Q_BYTES);
       for (int db = 0; db < S::DB; ++db)
         tma_load_3d(base + S::OFF_Q + db * S::TILE, &map_q, db * 64, h0, tok_begin + t0, smem_addr(&q_full));
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(smem_addr(&kv_empty[s]), ((uint32_t)(j >> 1) & 1u) ^ 1u, status, &abort_flag)) break;
-        const int key0 = (tile_first + j) * BN;
-        mbar_expect_tx(smem_addr(&k_full[s]), (uint32_t)S::KV_STAGE);
-        mbar_expect_tx(smem_addr(&v_full[s]), (uint32_t)S::KV_STAGE);
-        for (int p = 0; p < pages_per_tile; ++p) {
-          const int key = key0 + p * block_size;
-          int page = null_page;
-          if (key <= pos_last && key + block_size > kv_lo) {
-            page = bt[key / block_size];
-            if (page < 0 || page >= num_pages) {
-              if (page >= num_pages) atomicOr(status, GLLM_STATUS_PAGE_RANGE);
-              page = null_page;
-            }
-          }
-          const int row_k = ((page * 2 + 0) * hkv + kvh) * block_size;
-          const int row_v = ((page * 2 + 1) * hkv + kvh) * block_size;
-          for (int db = 0; db < S::DB; ++db) {
-            const uint32_t off = (uint32_t)(s * S::KV_STAGE + db * S::TILE + p * block_size * 128);
-            tma_load_2d(base + S::OFF_K + off, &map_kv, db * 64, row_k, smem_addr(&k_full[s]));
-            tma_load_2d(base + S::OFF_V + off, &map_kv, db * 64, row_v, smem_addr(&v_full[s]));
-          }
+    }
+    for (int j = 0; j < n_tiles; ++j) {
+      const int s = j & 1;
+      const int key0 = (tile_first + j) * BN;
+      int page = -1;                                    // -1: nothing to read for this lane
+      const int key = key0 + lane * block_size;
+      if (lane < pages_per_tile && key <= pos_last && key + block_size > kv_lo) {
+        page = bt[key / block_size];
+        if (page >= num_pages) {
+          atomicOr(status, GLLM_STATUS_PAGE_RANGE);
+          page = -1;
+        }
+      }
+      const int n_present = __popc(__ballot_sync(0xffffffffu, page >= 0));
+      int ok = 1;
+      if (lane == 0) {
+        ok = mbar_wait(smem_addr(&kv_empty[s]), ((uint32_t)(j >> 1) & 1u) ^ 1u, status, &abort_flag) ? 1 : 0;
+        if (ok) {
+          mbar_expect_tx(smem_addr(&k_full[s]), (uint32_t)n_present * page_bytes);
+          mbar_expect_tx(smem_addr(&v_full[s]), (uint32_t)n_present * page_bytes);
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);             // also orders the expect before every lane's copies
+      if (!ok) break;
+      if (page >= 0) {
+        const int row_k = ((page * 2 + 0) * hkv + kvh) * block_size;
+        const int row_v = ((page * 2 + 1) * hkv + kvh) * block_size;
+#pragma unroll
+        for (int db = 0; db < S::DB; ++db) {
+          const uint32_t off = (uint32_t)(s * S::KV_STAGE + db * S::TILE + lane * block_size * 128);
+          tma_load_2d(base + S::OFF_K + off, &map_kv, db * 64, row_k, smem_addr(&k_full[s]));
+          tma_load_2d(base + S::OFF_V + off, &map_kv, db * 64, row_v, smem_addr(&v_full[s]));
         }
       }
     }
@@ -165,6 +185,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         ok = mbar_wait(smem_addr(&p_full), (uint32_t)j & 1u, status, &abort_flag);
         if (ok) ok = mbar_wait(smem_addr(&v_full[s]), (uint32_t)(j >> 1) & 1u, status, &abort_flag);
         if (!ok) break;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int db = 0; db < S::DB; ++db)
@@ -191,29 +212,38 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      const int s = j & 1;
       const int kv0 = (tile_first + j) * BN;
       mbar_wait(smem_addr(&s_full), (uint32_t)j & 1u, status, &abort_flag);
       asm volatile("bar.sync 1, 128;" ::: "memory");     // the four warps go on together
       if (abort_flag) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // keys this row sees in the tile: lo <= key <= hi (hi < lo: none).  A tile that every row of the
+      // CTA sees whole takes the plain path.
       const bool need_mask = (kv0 + BN - 1 > pos_first) || window > 0 || t_count < qt;
+      const int hi = row_ok ? qpos : -1;
+      const int lo = window > 0 ? max(0, qpos - window + 1) : 0;
+      const unsigned span = hi >= lo ? (unsigned)(hi - lo) : 0u;
+      const int lo_eff = hi >= lo ? lo : 0x7fffff00;     // no key passes when the row sees nothing
       // pass 1: this row's maximum over the tile
       float mx = -INFINITY;
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         float v[32];
         tmem_ld32(tmem_s + (uint32_t)c, v);
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int key = kv0 + c + i;
-          const bool hidden = need_mask && (!row_ok || key > qpos || (window > 0 && key <= qpos - window));
-          mx = fmaxf(mx, hidden ? -INFINITY : v[i]);
+          for (int i = 0; i < 32; ++i) {
+            const bool seen = (unsigned)(kv0 + c + i - lo_eff) <= span;
+            mx = fmaxf(mx, seen ? v[i] : -INFINITY);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
         }
       }
       const float m_new = fmaxf(m, mx);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float corr = m == -INFINITY ? 0.f : exp2f((m - m_use) * scale_log2);
+      const float corr = m == -INFINITY ? 0.f : fast_exp2((m - m_use) * scale_log2);
       const float neg_mc = -m_use * scale_log2;
       // the output so far is rescaled when some row of the warp saw its maximum move
       if (j > 0) {
@@ -238,19 +268,25 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         float v[32];
         tmem_ld32(tmem_s + (uint32_t)c, v);
         uint32_t packed[16];
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0, p1;
-          {
-            const int key = kv0 + c + i;
-            const bool h0m = need_mask && (!row_ok || key > qpos || (window > 0 && key <= qpos - window));
-            const bool h1m = need_mask && (!row_ok || key + 1 > qpos || (window > 0 && key + 1 <= qpos - window));
-            p0 = h0m ? 0.f : exp2f(fmaf(v[i], scale_log2, neg_mc));
-            p1 = h1m ? 0.f : exp2f(fmaf(v[i + 1], scale_log2, neg_mc));
+          for (int i = 0; i < 32; i += 2) {
+            const bool s0 = (unsigned)(kv0 + c + i - lo_eff) <= span, s1 = (unsigned)(kv0 + c + i + 1 - lo_eff) <= span;
+            const float p0 = s0 ? fast_exp2(fmaf(v[i], scale_log2, neg_mc)) : 0.f;
+            const float p1 = s1 ? fast_exp2(fmaf(v[i + 1], scale_log2, neg_mc)) : 0.f;
+            l += p0 + p1;
+            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
           }
-          l += p0 + p1;
-          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = fast_exp2(fmaf(v[i], scale_log2, neg_mc));
+            const float p1 = fast_exp2(fmaf(v[i + 1], scale_log2, neg_mc));
+            l += p0 + p1;
+            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+          }
         }
         // keys c .. c+31 = four 16-byte pieces of block c/64; piece index XOR (row % 8)
         unsigned char* blk = p_row + (c >> 6) * S::TILE;
@@ -261,13 +297,15 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
               make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
         }
       }
-      // value rows of keys the request does not hold (yet): zero them so 0 * stale never matters
+      // value rows of keys the request does not hold (a page's unwritten tail, a page that was not
+      // read): zero them, so that probability 0 times a stale value never reaches the output
       if (kv0 + BN - 1 > pos_last || kv0 < kv_lo) {
-        mbar_wait(smem_addr(&v_full[s]), (uint32_t)(j >> 1) & 1u, status, &abort_flag);
+        mbar_wait(smem_addr(&v_full[j & 1]), (uint32_t)(j >> 1) & 1u, status, &abort_flag);
         const int key = kv0 + row;                       // thread <-> key row of the V tile
         if (key > pos_last || key < kv_lo) {
           for (int db = 0; db < S::DB; ++db) {
-            uint4* vrow = reinterpret_cast<uint4*>(base_ptr + S::OFF_V + s * S::KV_STAGE + db * S::TILE + row * 128);
+            uint4* vrow =
+                reinterpret_cast<uint4*>(base_ptr + S::OFF_V + (j & 1) * S::KV_STAGE + db * S::TILE + row * 128);
 #pragma unroll
             for (int i = 0; i < 8; ++i) vrow[i] = make_uint4(0u, 0u, 0u, 0u);
           }
@@ -371,7 +409,7 @@ int prefill_tmem_launch(const __nv_bfloat16* q, int64_t q_stride, __nv_bfloat16*
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  dim3 grid((max_q_len + qt - 1) / qt, hkv * (group / gp), num_requests);
+  dim3 grid(hkv * (group / gp), (max_q_len + qt - 1) / qt, num_requests);
   return gllm_launch(prefill_tmem_kernel<D>, grid, dim3(THREADS), (size_t)S::SMEM, stream, map_q, map_kv, out,
                      out_stride, block_table, bt_stride, cu_q, ctx_lens, slots, hq, hkv, gp, block_size, num_pages,
                      scale * 1.4426950408889634f, window, status);
@@ -384,7 +422,7 @@ GLLM_API int gllm_attention_prefill_tmem_supports(int d, int block_size) {
 }
 
 // As gllm_attention_prefill_bf16, plus n_tokens (rows of q).  q and the cache layer must be 16-byte
-// aligned, q_stride a multiple of 8; num_pages counts the cache's spare last page, which must exist.
+// aligned, q_stride a multiple of 8.
 GLLM_API int gllm_attention_prefill_tmem(const __nv_bfloat16* q, int64_t q_stride, __nv_bfloat16* out,
                                          int64_t out_stride, const __nv_bfloat16* cache, const int* block_table,
                                          int bt_stride, const int* cu_q, const int* ctx_lens, const int* slots,

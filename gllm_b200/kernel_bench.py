@@ -80,7 +80,7 @@ def attention_decode(batch=64, context=2048, hq=32, hkv=8, d=64, block_size=16, 
             "shape": dict(batch=batch, context=context, heads=hq, kv_heads=hkv, head_dim=d, block_size=block_size)}
 
 
-def attention_prefill(tokens=2048, context=0, hq=32, hkv=8, d=64, block_size=16, iters=5, peaks=None):
+def attention_prefill(tokens=2048, context=0, hq=32, hkv=8, d=64, block_size=16, iters=5, peaks=None, tmem=1):
     from gllm_b200.ops import attention_bf16
 
     pool, table = _paged_cache(1, context + tokens, hkv, d, block_size)
@@ -90,12 +90,12 @@ def attention_prefill(tokens=2048, context=0, hq=32, hkv=8, d=64, block_size=16,
     slots = torch.zeros(1, dtype=torch.int32, device="cuda")
     out = torch.empty(tokens, hq * d, dtype=torch.bfloat16, device="cuda")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    fn = lambda: attention_bf16.prefill_attention(qkv, qkv.shape[1], pool, table, cu, ctx, slots, 1, tokens, hq,
-                                                  1.0 / math.sqrt(d), 0, out)
+    kernel = attention_bf16.prefill_attention_tmem if tmem else attention_bf16.prefill_attention
+    fn = lambda: kernel(qkv, qkv.shape[1], pool, table, cu, ctx, slots, 1, tokens, hq, 1.0 / math.sqrt(d), 0, out)
     us = _time(fn, iters, flush)
     flops = 4.0 * d * hq * (tokens * context + tokens * (tokens + 1) / 2)
     tf = flops / us / 1e6
-    return {"kernel": "attention_prefill", "us": round(us, 2), "flops": flops, "achieved_tflops": round(tf, 1),
+    return {"kernel": "attention_prefill (tcgen05)" if tmem else "attention_prefill (mma.sync)", "us": round(us, 2), "flops": flops, "achieved_tflops": round(tf, 1),
             "frac_of_bf16_peak": round(tf / peaks["bf16_tflops"], 4),
             "shape": dict(tokens=tokens, context=context, heads=hq, kv_heads=hkv, head_dim=d, block_size=block_size)}
 

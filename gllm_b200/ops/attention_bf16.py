@@ -60,8 +60,7 @@ def prefill_tmem_supports(head_dim: int, block_size: int, q: torch.Tensor, cache
 
 def prefill_attention_tmem(q, q_stride, cache_layer, block_table, cu_q, ctx_lens, slots, num_requests, max_q_len,
                            num_heads, scale, window, out):
-    """tcgen05 attention of the first ``num_requests`` requests of the flat batch.  The cache layer's
-    last page must be the cache's spare page (it stands in for pages a request does not hold)."""
+    """tcgen05 attention of the first ``num_requests`` requests of the flat batch."""
     from gllm_b200 import ops
 
     num_pages, _, hkv, block_size, d = cache_layer.shape

@@ -264,14 +264,21 @@ def test_attention_mixed_batch_uses_both_kernels(ops):
     (4, 1, 64, 16, None), (3, 1, 32, 8, None), (32, 8, 64, 16, None), (6, 3, 128, 32, 100), (8, 8, 64, 4, 70),
     (16, 2, 128, 16, None), (5, 5, 32, 16, 24), (64, 1, 64, 16, None),
 ])
-def test_attention_prefill_tensor_cores(ops, hq, hkv, d, bs, window):
+@pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05"])
+def test_attention_prefill_tensor_cores(ops, hq, hkv, d, bs, window, kernel):
     """Portions of prompts over a cache: a whole prompt, a portion after 250 cached tokens, two-token
-    portions, portions that end inside a page and inside a 64-key tile; the far keys carry the weight."""
+    portions, portions that end inside a page and inside a key tile; the far keys carry the weight.
+    Both tensor-core kernels: mma.sync (64-key tiles) and tcgen05 with tensor memory (128-key tiles)."""
     from gllm_b200.ops import attention_bf16
+
+    if kernel == "tcgen05" and (d not in (64, 128) or bs < 8):
+        pytest.skip("the tcgen05 kernel takes head sizes 64 and 128 and pages of at least 8 tokens")
 
     g = torch.Generator().manual_seed(8)
     lens, q_counts = [130, 300, 2, 64, 67, 451], [130, 50, 2, 2, 65, 200]
     pool, table, ks, vs, qs, pos, rows = _paged_case(g, torch.bfloat16, lens, hq, hkv, d, bs, q_counts)
+    # the cache's spare last page (finite), as the cache manager provides it; every other unused slot is NaN
+    pool = torch.cat([pool, torch.zeros(1, *pool.shape[1:], dtype=pool.dtype)], 0)
     n = pos.numel()
     qkv = torch.zeros(n, (hq + 2 * hkv) * d, dtype=torch.bfloat16)
     qkv[:, : hq * d] = torch.cat(qs).reshape(n, hq * d)
@@ -281,8 +288,11 @@ def test_attention_prefill_tensor_cores(ops, hq, hkv, d, bs, window):
     ctx = torch.tensor([a - b for a, b in zip(lens, q_counts)], dtype=torch.int32).cuda()
     slots = torch.arange(1, len(lens) + 1, dtype=torch.int32).cuda()
     out = torch.full((n, hq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
-    attention_bf16.prefill_attention(qkv.cuda(), qkv.shape[1], pool.cuda(), table.cuda(), cu, ctx, slots, len(lens),
-                                     max(q_counts), hq, scale, window or 0, out)
+    run = attention_bf16.prefill_attention if kernel == "mma_sync" else attention_bf16.prefill_attention_tmem
+    qd, pd = qkv.cuda(), pool.cuda()
+    if kernel == "tcgen05":
+        assert attention_bf16.prefill_tmem_supports(d, bs, qd, pd)
+    run(qd, qkv.shape[1], pd, table.cuda(), cu, ctx, slots, len(lens), max(q_counts), hq, scale, window or 0, out)
     ops.check_status()
     off = 0
     for r, nq in enumerate(q_counts):
