@@ -10,7 +10,8 @@
 //   warp 0: TMA loads. Q once (a 3-D box: 64 dims x G' heads x tokens); per key tile the K and V
 //           pages straight out of the cache pool, one box per page, each lane issuing its own page's
 //           boxes, 128-byte swizzle;
-//   warp 1 (one thread): S = Q K^T into tensor memory (128 x 128 fp32), later O += P V (128 x D);
+//   warp 1 (one thread): S = Q K^T into tensor memory (128 x 128 fp32, two buffers: the scores of
+//           the next tile are computed while this one is exponentiated), later O += P V (128 x D);
 //   warps 2-5 (one thread per row): read S from tensor memory, mask, running maximum and sum in
 //           fp32, rescale O in tensor memory when the maximum moved, write P (bf16) into shared
 //           memory in the swizzled layout the second product reads, at the end O / sum -> global.
@@ -44,8 +45,8 @@ struct TShape {
   static constexpr int OFF_V = OFF_K + 2 * KV_STAGE;    // 2 stages
   static constexpr int OFF_P = OFF_V + 2 * KV_STAGE;
   static constexpr int SMEM = OFF_P + P_BYTES + 1024;
-  static constexpr int TMEM_COLS = 256;                 // S: 128 columns, O: D columns
-  static constexpr int COL_S = 0, COL_O = 128;
+  static constexpr int TMEM_COLS = 512;                 // S twice: 128 columns each, O: D columns
+  static constexpr int COL_S = 0, COL_O = 256;
 };
 
 template <int D>
@@ -57,7 +58,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     float scale_log2, int window, int* __restrict__ status) {
   using S = TShape<D>;
   extern __shared__ unsigned char smem_dyn[];
-  __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], kv_empty[2], s_full, p_full, o_ready;
+  __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full, o_ready;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
   pdl_trigger();
@@ -79,9 +80,10 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_addr(&k_full[s]), 1);
       mbar_init(smem_addr(&v_full[s]), 1);
-      mbar_init(smem_addr(&kv_empty[s]), 1);
+      mbar_init(smem_addr(&k_empty[s]), 1);
+      mbar_init(smem_addr(&v_empty[s]), 1);
+      mbar_init(smem_addr(&s_full[s]), 1);
     }
-    mbar_init(smem_addr(&s_full), 1);
     mbar_init(smem_addr(&p_full), 4);                   // one arrival per softmax warp
     mbar_init(smem_addr(&o_ready), 1);
     abort_flag = 0;
@@ -124,39 +126,49 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       for (int db = 0; db < S::DB; ++db)
         tma_load_3d(base + S::OFF_Q + db * S::TILE, &map_q, db * 64, h0, tok_begin + t0, smem_addr(&q_full));
     }
-    for (int j = 0; j < n_tiles; ++j) {
-      const int s = j & 1;
-      const int key0 = (tile_first + j) * BN;
-      int page = -1;                                    // -1: nothing to read for this lane
-      const int key = key0 + lane * block_size;
-      if (lane < pages_per_tile && key <= pos_last && key + block_size > kv_lo) {
+    // this lane's page of tile j (-1: nothing to read) and how many lanes have one
+    auto lookup = [&](int j) -> int {
+      int page = -1;
+      const int key = (tile_first + j) * BN + lane * block_size;
+      if (j < n_tiles && lane < pages_per_tile && key <= pos_last && key + block_size > kv_lo) {
         page = bt[key / block_size];
         if (page >= num_pages) {
           atomicOr(status, GLLM_STATUS_PAGE_RANGE);
           page = -1;
         }
       }
+      return page;
+    };
+    // K (plane 0) or V (plane 1) of tile j into its stage, once the product that read the stage's
+    // previous tile is done
+    auto load = [&](int j, int page, int plane) -> bool {
+      const int s = j & 1;
+      const uint32_t full = smem_addr(plane ? &v_full[s] : &k_full[s]);
       const int n_present = __popc(__ballot_sync(0xffffffffu, page >= 0));
       int ok = 1;
       if (lane == 0) {
-        ok = mbar_wait(smem_addr(&kv_empty[s]), ((uint32_t)(j >> 1) & 1u) ^ 1u, status, &abort_flag) ? 1 : 0;
-        if (ok) {
-          mbar_expect_tx(smem_addr(&k_full[s]), (uint32_t)n_present * page_bytes);
-          mbar_expect_tx(smem_addr(&v_full[s]), (uint32_t)n_present * page_bytes);
-        }
+        ok = mbar_wait(smem_addr(plane ? &v_empty[s] : &k_empty[s]), ((uint32_t)(j >> 1) & 1u) ^ 1u, status, &abort_flag)
+                 ? 1 : 0;
+        if (ok) mbar_expect_tx(full, (uint32_t)n_present * page_bytes);
       }
       ok = __shfl_sync(0xffffffffu, ok, 0);             // also orders the expect before every lane's copies
-      if (!ok) break;
+      if (!ok) return false;
       if (page >= 0) {
-        const int row_k = ((page * 2 + 0) * hkv + kvh) * block_size;
-        const int row_v = ((page * 2 + 1) * hkv + kvh) * block_size;
+        const int row0 = ((page * 2 + plane) * hkv + kvh) * block_size;
+        const uint32_t dst = base + (plane ? S::OFF_V : S::OFF_K) + (uint32_t)(s * S::KV_STAGE + lane * block_size * 128);
 #pragma unroll
-        for (int db = 0; db < S::DB; ++db) {
-          const uint32_t off = (uint32_t)(s * S::KV_STAGE + db * S::TILE + lane * block_size * 128);
-          tma_load_2d(base + S::OFF_K + off, &map_kv, db * 64, row_k, smem_addr(&k_full[s]));
-          tma_load_2d(base + S::OFF_V + off, &map_kv, db * 64, row_v, smem_addr(&v_full[s]));
-        }
+        for (int db = 0; db < S::DB; ++db) tma_load_2d(dst + db * S::TILE, &map_kv, db * 64, row0, full);
       }
+      return true;
+    };
+    // order: K0, then K(j+1) before V(j): the next scores are issued before this tile's values are used
+    int page = lookup(0);
+    bool ok = n_tiles > 0 && load(0, page, 0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const int page_next = lookup(j + 1);
+      if (j + 1 < n_tiles) ok = load(j + 1, page_next, 0);
+      if (ok) ok = load(j, page, 1);
+      page = page_next;
     }
   } else if (active && warp == 1) {
     // -------------------------------------------------------------------- MMA issuer
@@ -172,20 +184,22 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         for (int db = 0; db < S::DB; ++db)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_s, umma_desc(base + S::OFF_Q + db * S::TILE + k * 32),
+            umma_bf16(tmem_s + s * BN, umma_desc(base + S::OFF_Q + db * S::TILE + k * 32),
                       umma_desc(base + S::OFF_K + s * S::KV_STAGE + db * S::TILE + k * 32), idesc_s,
                       (db > 0 || k > 0) ? 1u : 0u);
-        umma_commit(smem_addr(&s_full));
+        umma_commit(smem_addr(&k_empty[s]));            // K of this stage is consumed
+        umma_commit(smem_addr(&s_full[s]));
         return true;
       };
+      // scores run one tile ahead of the softmax: S(j+1) is computed while tile j is exponentiated
       bool ok = mbar_wait(smem_addr(&q_full), 0u, status, &abort_flag);
       if (ok) ok = issue_s(0);
+      if (ok && n_tiles > 1) ok = issue_s(1);
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int s = j & 1;
-        ok = mbar_wait(smem_addr(&p_full), (uint32_t)j & 1u, status, &abort_flag);
+        ok = mbar_wait(smem_addr(&p_full), (uint32_t)j & 1u, status, &abort_flag);   // P(j) written, S(j) read
         if (ok) ok = mbar_wait(smem_addr(&v_full[s]), (uint32_t)(j >> 1) & 1u, status, &abort_flag);
         if (!ok) break;
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int db = 0; db < S::DB; ++db)
@@ -194,9 +208,9 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             umma_bf16(tmem_o + db * 64, umma_desc(base + S::OFF_P + (k >> 2) * S::TILE + (k & 3) * 32),
                       umma_desc(base + S::OFF_V + s * S::KV_STAGE + db * S::TILE + k * 16 * 128), idesc_o,
                       (j > 0 || k > 0) ? 1u : 0u);
-        umma_commit(smem_addr(&kv_empty[s]));           // K and V of this stage are consumed
-        umma_commit(smem_addr(&o_ready));               // O holds tiles 0 .. j
-        if (j + 1 < n_tiles) ok = issue_s(j + 1);
+        umma_commit(smem_addr(&v_empty[s]));            // V of this stage is consumed
+        umma_commit(smem_addr(&o_ready));               // O holds tiles 0 .. j, P may be overwritten
+        if (j + 2 < n_tiles) ok = issue_s(j + 2);
       }
     }
   } else if (active && warp >= 2) {
@@ -207,13 +221,14 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const bool row_ok = tl < t_count;
     const int qpos = pos_first + tl;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tmem_s = tmem_base + S::COL_S + lane_addr, tmem_o = tmem_base + S::COL_O + lane_addr;
+    const uint32_t tmem_s0 = tmem_base + S::COL_S + lane_addr, tmem_o = tmem_base + S::COL_O + lane_addr;
     unsigned char* p_row = base_ptr + S::OFF_P + row * 128;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int kv0 = (tile_first + j) * BN;
-      mbar_wait(smem_addr(&s_full), (uint32_t)j & 1u, status, &abort_flag);
+      const uint32_t tmem_s = tmem_s0 + (uint32_t)((j & 1) * BN);
+      mbar_wait(smem_addr(&s_full[j & 1]), (uint32_t)(j >> 1) & 1u, status, &abort_flag);
       asm volatile("bar.sync 1, 128;" ::: "memory");     // the four warps go on together
       if (abort_flag) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -245,7 +260,8 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       const float corr = m == -INFINITY ? 0.f : fast_exp2((m - m_use) * scale_log2);
       const float neg_mc = -m_use * scale_log2;
-      // the output so far is rescaled when some row of the warp saw its maximum move
+      // the previous tile's P V must be done before P is overwritten and the output touched; the
+      // output so far is rescaled when some row of the warp saw its maximum move
       if (j > 0) {
         mbar_wait(smem_addr(&o_ready), (uint32_t)(j - 1) & 1u, status, &abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
