@@ -48,7 +48,6 @@ decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride,
   __shared__ float red_m[W][ROWS], red_l[W][ROWS];
 
   pdl_trigger();
-  pdl_wait();
   const int split = blockIdx.x;
   const int group = hq / hkv;
   const int head_tiles = (group + ROWS - 1) / ROWS;
@@ -63,6 +62,7 @@ decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride,
   const int c1 = min((split + 1) * S::CHUNK, qpos + 1);
   float* my_ml = part_ml + (((int64_t)n * hq + h0) * num_chunks + split) * 2;
   if (c0 >= c1) {                                       // nothing of this chunk is visible
+    pdl_wait();
     if (threadIdx.x < heads) {
       float* ml = my_ml + (int64_t)threadIdx.x * num_chunks * 2;
       ml[0] = -INFINITY;
@@ -75,7 +75,10 @@ decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride,
   const int64_t page_elems = 2 * (int64_t)hkv * head_elems;
   const int64_t v_off = (int64_t)hkv * head_elems;
 
-  // ---- this warp's 64 keys and values: all copies are issued before anything waits
+  // ---- this warp's keys and values: all copies are issued before anything waits.
+  // The positions, the block table and every cached row but the newest (key == qpos, written by the
+  // kernel just before this one) are older than the step's kernels: they are requested before the
+  // dependency wait, so the cache streams in while the kernels before this one still run.
   const int k0 = split * S::CHUNK + warp * TILE;
   const bool warp_has_keys = k0 < c1 && k0 + TILE > c0;
   // Every lane first resolves its share of the tile's rows (page lookup, offset in the page) and leaves
@@ -102,11 +105,22 @@ decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride,
       const int row = idx / C, piece = idx - row * C;
       const int64_t base = row_base[warp][row];
       const bool ok = base >= 0;
+      if (k0 + row == qpos) continue;                   // the newest row: after the wait
       const __nv_bfloat16* src = cache + (ok ? base : 0) + piece * 8;
       const int off = (row * C + swizzle<C>(row, piece)) * 16;
       cp_async16(smem_u32(k_sm + off), src, ok);
       cp_async16(smem_u32(v_sm + off), src + v_off, ok);
     }
+  }
+  pdl_wait();
+  if (warp_has_keys && qpos >= k0 && qpos < k0 + TILE && lane < C) {
+    const int row = qpos - k0, piece = lane;
+    const int64_t base = row_base[warp][row];
+    const bool ok = base >= 0;
+    const __nv_bfloat16* src = cache + (ok ? base : 0) + piece * 8;
+    const int off = (row * C + swizzle<C>(row, piece)) * 16;
+    cp_async16(smem_u32(k_sm + off), src, ok);
+    cp_async16(smem_u32(v_sm + off), src + v_off, ok);
   }
   // ---- the query heads of this kv head: row i <-> head h0 + i (rows past the group are zeros)
   for (int idx = threadIdx.x; idx < ROWS * C; idx += W * 32) {

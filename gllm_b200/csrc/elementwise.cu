@@ -7,6 +7,8 @@
 // T is the activation / weight-matrix type (float or bf16).  The residual
 // stream, norm weights, norm statistics and rotation angles are always fp32.
 #include "common.cuh"
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
 
 // ------------------------------------------------- 8 elements at a time
 // Vec8<T>: eight consecutive elements of an activation row as fp32, moved with 16-byte
@@ -136,6 +138,14 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ branch, const float* __
   extern __shared__ float row_buf[];  // hidden floats + 32 scratch
   float* scratch = row_buf + hidden;
   pdl_trigger();
+  // the norm's weight never depends on the kernel before this one: it is fetched before the wait
+  constexpr int WPRE = 4;
+  float wpre[WPRE];
+#pragma unroll
+  for (int k = 0; k < WPRE; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    wpre[k] = c < hidden ? weight[c] : 0.f;
+  }
   pdl_wait();
   const int i = blockIdx.x;
   if (i >= n_rows) return;
@@ -159,7 +169,12 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ branch, const float* __
   const float total = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
   T* o = out + (size_t)i * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+#pragma unroll
+  for (int k = 0; k < WPRE; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < hidden) o[c] = from_float<T>(row_buf[c] * inv * (unit_offset ? 1.0f + wpre[k] : wpre[k]));
+  }
+  for (int c = threadIdx.x + WPRE * blockDim.x; c < hidden; c += blockDim.x) {
     const float w = unit_offset ? 1.0f + weight[c] : weight[c];
     o[c] = from_float<T>(row_buf[c] * inv * w);
   }
@@ -214,6 +229,62 @@ __global__ void add_rmsnorm_wide_kernel(const T* __restrict__ branch, const floa
   }
 }
 
+// The same for a few rows whose branch arrives as unsummed splits (decoding): a cluster of blocks
+// shares one row, each block sums, adds and squares its stretch of columns, the blocks exchange
+// their sums of squares through distributed shared memory (added in rank order) and each
+// normalises its own stretch.  A row of a handful of tokens is then read through many SMs' ports
+// instead of one.  Up to 4 columns per thread.
+template <typename T>
+__global__ void add_rmsnorm_cluster_kernel(const float* __restrict__ parts, int n_parts, int64_t part_stride,
+                                           float* __restrict__ resid, const float* __restrict__ weight,
+                                           T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps,
+                                           int unit_offset) {
+  __shared__ float scratch[32];
+  __shared__ float my_ss;
+  pdl_trigger();
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank(), n_ranks = (int)cluster.num_blocks();
+  const int cols_per = (hidden + n_ranks - 1) / n_ranks;
+  const int c_begin = rank * cols_per, c_end = min(hidden, c_begin + cols_per);
+  constexpr int PER = 4;
+  float w[PER], x[PER];
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {                       // the weight does not depend on the kernel before
+    const int c = c_begin + threadIdx.x + k * blockDim.x;
+    w[k] = c < c_end ? weight[c] : 0.f;
+  }
+  const int i = blockIdx.y;
+  const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+  pdl_wait();
+  float* res = resid + r * hidden;
+  const float* pr = parts + r * hidden;
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int c = c_begin + threadIdx.x + k * blockDim.x;
+    x[k] = 0.f;
+    if (c < c_end) {
+      const float b = sum_parts16(pr + c, n_parts, part_stride);
+      x[k] = res[c] + to_float(from_float<T>(b));       // rounded as the product itself would have rounded it
+      if (!rows) res[c] = x[k];
+      ss += x[k] * x[k];
+    }
+  }
+  const float mine = block_sum(ss, scratch);
+  if (threadIdx.x == 0) my_ss = mine;
+  cluster.sync();
+  float total = 0.f;
+  for (int rk = 0; rk < n_ranks; ++rk) total += *cluster.map_shared_rank(&my_ss, rk);
+  cluster.sync();                                       // nobody leaves while its sum may still be read
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  T* o = out + (size_t)i * hidden;
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int c = c_begin + threadIdx.x + k * blockDim.x;
+    if (c < c_end) o[c] = from_float<T>(x[k] * inv * (unit_offset ? 1.0f + w[k] : w[k]));
+  }
+}
+
 template <typename T>
 static int add_rmsnorm_launch(const T* branch, const float* parts, int n_parts, int64_t part_stride, float* resid,
                               const float* weight, T* out, const int* rows, int n_rows, int hidden, float eps,
@@ -228,6 +299,10 @@ static int add_rmsnorm_launch(const T* branch, const float* parts, int n_parts, 
     if (chunks <= wide_threads * 4)
       return gllm_launch(add_rmsnorm_wide_kernel<T, 4>, dim3(n_rows), dim3(wide_threads), 0, stream, branch, parts,
                          n_parts, part_stride, resid, weight, out, rows, n_rows, hidden, eps, unit_offset);
+  }
+  if (parts && !branch && n_rows <= 64 && hidden >= 1024 && hidden <= 8 * 4 * 256) {
+    return gllm_launch_cluster(add_rmsnorm_cluster_kernel<T>, dim3(8, n_rows), dim3(256), 0, stream, 8u, parts,
+                               n_parts, part_stride, resid, weight, out, rows, hidden, eps, unit_offset);
   }
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
   if (parts) threads = hidden >= 1024 ? 1024 : threads;
@@ -510,6 +585,68 @@ __global__ void rope_store_wide_kernel(T* __restrict__ qkv, const float* __restr
   }
 }
 
+// The same for a projection that arrives as unsummed splits, a few tokens at a time (decoding):
+// one thread owns one pair of one head, sums the splits of its two elements, rotates them and
+// writes them to qkv and, for k and v, to the cache: no value makes a second trip through global
+// memory.  The position, the cache slot, the frequency and so the sine and cosine do not depend on
+// the kernel before this one: they are ready when the dependency wait returns.
+template <typename T>
+__global__ void rope_store_parts_kernel(T* __restrict__ qkv, const float* __restrict__ parts, int n_parts,
+                                        int64_t part_stride, const int* __restrict__ positions,
+                                        const float* __restrict__ inv_freq, const int* __restrict__ slot_mapping,
+                                        T* __restrict__ cache, int n_tokens, int hq, int hkv, int d, int rotary_dim,
+                                        int interleaved, int block_size, int num_pages, int* __restrict__ status) {
+  pdl_trigger();
+  const int n = blockIdx.y;
+  const int half_d = d / 2;
+  const int item = blockIdx.x * blockDim.x + threadIdx.x;
+  const bool live = item < (hq + 2 * hkv) * half_d;
+  const int h = live ? item / half_d : 0, i = live ? item - h * half_d : 0;
+  const int half = inv_freq ? rotary_dim / 2 : 0;
+  const bool rotated = h < hq + hkv && i < half;
+  int i0, i1;
+  if (rotated) {
+    i0 = interleaved ? 2 * i : i;
+    i1 = interleaved ? 2 * i + 1 : i + half;
+  } else if (h < hq + hkv) {
+    i0 = 2 * half + 2 * (i - half);                      // the head's tail past the rotated dims
+    i1 = i0 + 1;
+  } else {
+    i0 = 2 * i;
+    i1 = i0 + 1;
+  }
+  float sn = 0.f, cs = 1.f;
+  if (live && rotated) sincosf((float)positions[n] * inv_freq[i], &sn, &cs);
+  int64_t cache_base = -1;
+  if (live && slot_mapping && h >= hq) {
+    const int slot = slot_mapping[n];
+    if (slot >= 0) {
+      const int page = slot / block_size, off = slot - page * block_size;
+      if (page >= num_pages) atomicOr(status, GLLM_STATUS_PAGE_RANGE);
+      else {
+        const bool is_v = h >= hq + hkv;
+        const int kvh = is_v ? h - hq - hkv : h - hq;
+        cache_base = (((int64_t)page * 2 + (is_v ? 1 : 0)) * hkv + kvh) * block_size * d + (int64_t)off * d;
+      }
+    }
+  }
+  pdl_wait();
+  if (!live) return;
+  const int width = (hq + 2 * hkv) * d;
+  const float* src = parts + (size_t)n * width + (size_t)h * d;
+  const T x0 = from_float<T>(sum_parts16(src + i0, n_parts, part_stride));   // rounded as the product would be
+  const T x1 = from_float<T>(sum_parts16(src + i1, n_parts, part_stride));
+  const T y0 = from_float<T>(to_float(x0) * cs - to_float(x1) * sn);
+  const T y1 = from_float<T>(to_float(x0) * sn + to_float(x1) * cs);
+  T* row = qkv + (size_t)n * width + (size_t)h * d;
+  row[i0] = rotated ? y0 : x0;
+  row[i1] = rotated ? y1 : x1;
+  if (cache_base >= 0) {
+    cache[cache_base + i0] = rotated ? y0 : x0;
+    cache[cache_base + i1] = rotated ? y1 : x1;
+  }
+}
+
 template <typename T>
 static int rope_store_launch(T* qkv, const float* parts, int n_parts, int64_t part_stride, const int* positions,
                              const float* inv_freq, const int* slot_mapping,
@@ -524,6 +661,12 @@ static int rope_store_launch(T* qkv, const float* parts, int n_parts, int64_t pa
     return gllm_launch(rope_store_wide_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, qkv, parts, n_parts,
                        part_stride, positions, inv_freq, slot_mapping, cache, n_tokens, hq, hkv, d, rotary_dim,
                        block_size, num_pages, status);
+  }
+  if (parts && n_tokens <= 64 && d % 2 == 0) {
+    const int items = (hq + 2 * hkv) * (d / 2);
+    return gllm_launch(rope_store_parts_kernel<T>, dim3((items + 255) / 256, n_tokens), dim3(256), 0, stream, qkv,
+                       parts, n_parts, part_stride, positions, inv_freq, slot_mapping, cache, n_tokens, hq, hkv, d,
+                       rotary_dim, interleaved, block_size, num_pages, status);
   }
   int work = max((hq + hkv) * (rotary_dim / 2), hkv * d);
   int threads = work >= 512 ? 256 : (work >= 128 ? 128 : 64);

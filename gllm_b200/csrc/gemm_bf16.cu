@@ -115,27 +115,47 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
-  // set-up is done (barriers, tensor memory); everything below touches global memory
-  pdl_wait();
+  // set-up is done (barriers, tensor memory).  The weight never depends on the kernel before this
+  // one, so its first tiles are requested before the dependency wait: the weight stream starts while
+  // the previous kernel is still running.  Activations are read, and anything is written, after it.
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      const CUtensorMap* map_w = SWAPPED ? &map_a : &map_b;
+      const CUtensorMap* map_x = SWAPPED ? &map_b : &map_a;
+      const uint32_t off_w = SWAPPED ? 0u : (uint32_t)S::STAGE_A, off_x = SWAPPED ? (uint32_t)S::STAGE_A : 0u;
       uint32_t it = 0;                                   // k-blocks issued so far, over all items
       bool ok = true;
-      for (int w = blockIdx.x; w < num_items && ok; w += gridDim.x) {
-        const Item item = item_of<BN, SWAPPED>(w, tiles_a, splits);
-        const int kb_begin = item.split * kb_per_split;
-        const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
-        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
-          const uint32_t s = it % S::STAGES, round = it / S::STAGES;
-          ok = mbar_wait(smem_addr(&empty_bar[s]), (round & 1u) ^ 1u, status, &abort_flag);
-          if (!ok) break;
-          const uint32_t bar = smem_addr(&full_bar[s]);
-          mbar_expect_tx(bar, (uint32_t)(S::STAGE_A + S::STAGE_B));
-          const uint32_t dst = tile_base + s * S::STAGE;
-          tma_load_2d(dst, &map_a, kb * BK, item.a_row0, bar);
-          tma_load_2d(dst + S::STAGE_A, &map_b, kb * BK, item.b_row0, bar);
+      // pass 0: the weight tiles of the first STAGES k-blocks; pass 1: their activation tiles, then
+      // both operands of every later block as stages come free
+      for (int pass = 0; pass < 2 && ok; ++pass) {
+        if (pass == 1) pdl_wait();
+        it = 0;
+        bool more = true;
+        for (int w = blockIdx.x; w < num_items && ok && more; w += gridDim.x) {
+          const Item item = item_of<BN, SWAPPED>(w, tiles_a, splits);
+          const int kb_begin = item.split * kb_per_split;
+          const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
+          const int row_w = SWAPPED ? item.a_row0 : item.b_row0, row_x = SWAPPED ? item.b_row0 : item.a_row0;
+          for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
+            const uint32_t s = it % S::STAGES, round = it / S::STAGES;
+            const uint32_t bar = smem_addr(&full_bar[s]);
+            const uint32_t dst = tile_base + s * S::STAGE;
+            if (pass == 0) {
+              if (round > 0) { more = false; break; }
+              mbar_expect_tx(bar, (uint32_t)(S::STAGE_A + S::STAGE_B));
+              tma_load_2d(dst + off_w, map_w, kb * BK, row_w, bar);
+            } else if (round == 0) {
+              tma_load_2d(dst + off_x, map_x, kb * BK, row_x, bar);
+            } else {
+              ok = mbar_wait(smem_addr(&empty_bar[s]), (round & 1u) ^ 1u, status, &abort_flag);
+              if (!ok) break;
+              mbar_expect_tx(bar, (uint32_t)(S::STAGE_A + S::STAGE_B));
+              tma_load_2d(dst + off_w, map_w, kb * BK, row_w, bar);
+              tma_load_2d(dst + off_x, map_x, kb * BK, row_x, bar);
+            }
+          }
         }
       }
       if (abort_flag) {
@@ -186,6 +206,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else {
     // ---------------------------------------------------------------- epilogue
+    pdl_wait();                                          // nothing is written before the previous kernel is done
     const int quarter = warp & 3;                        // the TMEM lanes this warp may read: 32*quarter ..
     const int row = quarter * 32 + lane;                 // row of the accumulator tile
     const int ep_thread = (warp - 2) * 32 + lane;        // 0 .. 127

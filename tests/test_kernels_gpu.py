@@ -344,8 +344,14 @@ def test_gemm_bf16_odd_inner_size_goes_to_the_library(ops):
 
 
 def test_unsummed_splits_are_summed_by_their_consumers(ops):
-    """A product cut along K may hand its fp32 partial results to add_rmsnorm or rope_store; both
-    give exactly what they give for the summed product."""
+    """A product cut along K may hand its fp32 partial results to add_rmsnorm or rope_store.  The
+    residual stream, the rotated rows and the cache come out exactly as for the summed product; the
+    normalised rows may differ by one bf16 step where the sum of squares, added in another order,
+    moves the scale by one fp32 step."""
+
+    def same_up_to_one_step(p, q):
+        p, q = p.float(), q.float()
+        return bool(((p - q).abs() <= p.abs() * 2.0 ** -7).all()) and float((p != q).float().mean()) < 0.02
     g = torch.Generator().manual_seed(11)
     m, k = 8, 2048
     x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
@@ -360,11 +366,13 @@ def test_unsummed_splits_are_summed_by_their_consumers(ops):
     a = ops.add_rmsnorm(summed, r1, wn, 1e-5, torch.bfloat16)
     split = ops.linear(x, w, split_ok=True)
     b = ops.add_rmsnorm(split, r2, wn, 1e-5, torch.bfloat16)
-    assert torch.equal(a, b) and torch.equal(r1, r2)
+    assert torch.equal(r1, r2) and same_up_to_one_step(a, b)
+    want = r1.double() * torch.rsqrt(r1.double().pow(2).mean(-1, keepdim=True) + 1e-5)
+    torch.testing.assert_close(b.double(), want, rtol=2.0 ** -8, atol=1e-6)
     rows = torch.tensor([5, 1], dtype=torch.int32).cuda()
     split = ops.linear(x, w, split_ok=True)
-    assert torch.equal(ops.add_rmsnorm(split, resid.clone(), wn, 1e-5, torch.bfloat16, rows=rows),
-                       ops.add_rmsnorm(summed, resid.clone(), wn, 1e-5, torch.bfloat16, rows=rows))
+    assert same_up_to_one_step(ops.add_rmsnorm(split, resid.clone(), wn, 1e-5, torch.bfloat16, rows=rows),
+                               ops.add_rmsnorm(summed, resid.clone(), wn, 1e-5, torch.bfloat16, rows=rows))
     # rotary + store: 24 query heads and 4 kv heads of 64 make a width of 2048
     hq, hkv, d, bs = 24, 4, 64, 16
     positions = torch.arange(100, 100 + m, dtype=torch.int32).cuda()
