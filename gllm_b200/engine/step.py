@@ -38,10 +38,14 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._buffers: dict[str, torch.Tensor] = {}
+        # buffers that were outgrown stay allocated: a captured graph may still hold their address
+        self._retired: list[torch.Tensor] = []
 
     def get(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
         buf = self._buffers.get(name)
         if buf is None or buf.numel() < numel or buf.dtype != dtype:
+            if buf is not None:
+                self._retired.append(buf)
             buf = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
             self._buffers[name] = buf
         return buf[:numel]

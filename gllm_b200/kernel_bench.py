@@ -50,7 +50,8 @@ def _paged_cache(batch, context, hkv, d, block_size, extra_tokens=0, sequential=
     return pool, table
 
 
-def attention_decode(batch=64, context=2048, hq=32, hkv=8, d=64, block_size=16, iters=5, peaks=None, sequential=0):
+def attention_decode(batch=64, context=2048, hq=32, hkv=8, d=64, block_size=16, iters=5, peaks=None, sequential=0,
+                     stream=1):
     from gllm_b200.ops import attention_bf16
 
     pool, table = _paged_cache(batch, context, hkv, d, block_size, sequential=sequential)
@@ -71,11 +72,12 @@ def attention_decode(batch=64, context=2048, hq=32, hkv=8, d=64, block_size=16, 
 
     ws = _WS()
     fn = lambda: attention_bf16.decode_attention(qkv, qkv.shape[1], pool, table, positions, rows, hq,
-                                                 1.0 / math.sqrt(d), 0, context, ws, out)
+                                                 1.0 / math.sqrt(d), 0, context, ws, out,
+                                                 kernel="stream" if stream else "split")
     us = _time(fn, iters, flush)
     nbytes = batch * context * 2 * hkv * d * 2
     gbs = nbytes / us / 1e3
-    return {"kernel": "attention_decode (split + merge)", "us": round(us, 2), "bytes": nbytes,
+    return {"kernel": "attention_decode (stream + merge)" if stream else "attention_decode (split + merge)", "us": round(us, 2), "bytes": nbytes,
             "achieved_gbs": round(gbs, 1), "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4),
             "shape": dict(batch=batch, context=context, heads=hq, kv_heads=hkv, head_dim=d, block_size=block_size)}
 

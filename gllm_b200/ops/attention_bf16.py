@@ -109,6 +109,37 @@ def _decode_fn():
     return _decode
 
 
+_decode_stream = None
+STREAM_SPAN = 128
+# the stream kernel has one work item per 128 keys of a request: below this many items the split
+# kernel, with a work item per kv head as well, fills the machine better
+STREAM_MIN_ITEMS = 296
+
+
+def _decode_stream_fn():
+    global _decode_stream
+    if _decode_stream is None:
+        lib = load_module("attention_decode_tma")
+        f = lib.gllm_attention_decode_stream
+        f.argtypes = [P, c_int64, P, c_int64, P, P, c_int, P, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int,
+                      c_int, c_float, c_int, P, P]
+        f.restype = c_int
+        lib.gllm_attention_decode_stream_parts.argtypes = [c_int, c_int, c_int, c_int]
+        lib.gllm_attention_decode_stream_parts.restype = c_int
+        _decode_stream = (f, lib.gllm_attention_decode_stream_parts)
+    return _decode_stream
+
+
+def decode_stream_parts(head_dim: int, num_heads: int, num_kv_heads: int, block_size: int,
+                        q: torch.Tensor, cache_layer: torch.Tensor) -> int:
+    """Partial results per 128 keys that the persistent TMA kernel leaves for these sizes; 0 when it
+    does not take them (head sizes 64 and 128, up to 8 kv heads of up to 16 query heads, pages of 16
+    or 32 tokens, 16-byte aligned operands)."""
+    if head_dim not in (64, 128) or q.data_ptr() % 16 or cache_layer.data_ptr() % 16 or q.stride(0) % 8:
+        return 0
+    return int(_decode_stream_fn()[1](head_dim, num_heads, num_kv_heads, block_size))
+
+
 def decode_chunk(head_dim: int) -> int:
     """Keys per split of the decode kernel for this head size: a constant, so
     the cut of a request's keys depends on positions only."""
@@ -126,27 +157,41 @@ def decode_scratch_elems(num_queries: int, num_heads: int, head_dim: int, max_se
 
 
 def decode_attention(q, q_stride, cache_layer, block_table, positions, token_row, num_heads, scale, window,
-                     max_seq_len, workspace, out):
-    """Split-KV attention of ``positions.numel()`` single query tokens."""
+                     max_seq_len, workspace, out, kernel: str = "auto"):
+    """Split-KV attention of ``positions.numel()`` single query tokens.  ``kernel``: "split" (one
+    CTA per chunk of keys and kv head), "stream" (one persistent CTA per SM, TMA) or "auto" (stream
+    when the step has enough keys to keep every SM's stream busy)."""
     from gllm_b200 import ops
 
     num_pages, _, hkv, block_size, d = cache_layer.shape
     n = positions.numel()
-    chunks, n_o, n_ml = decode_scratch_elems(n, num_heads, d, max_seq_len)
+    parts = decode_stream_parts(d, num_heads, hkv, block_size, q, cache_layer) if kernel != "split" else 0
+    if kernel == "stream" and not parts:
+        raise ValueError(f"the stream decode kernel does not take {num_heads}/{hkv} heads of {d} with pages of "
+                         f"{block_size}")
+    spans = max(1, -(-max_seq_len // STREAM_SPAN))
+    use_stream = bool(parts) and (kernel == "stream" or n * spans >= STREAM_MIN_ITEMS)
+    if use_stream:
+        chunks = spans
+        n_o, n_ml = n * num_heads * spans * parts * d, n * num_heads * spans * parts * 2
+        fn, name = _decode_stream_fn()[0], "attention_decode_stream"
+    else:
+        chunks, n_o, n_ml = decode_scratch_elems(n, num_heads, d, max_seq_len)
+        fn, name = _decode_fn()[0], "attention_decode_bf16"
     if workspace is not None:
         part_o = workspace.get("attention_decode_partial_out", n_o, torch.float32)
         part_ml = workspace.get("attention_decode_partial_max_sum", n_ml, torch.float32)
     else:
         part_o = torch.empty(n_o, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(n_ml, dtype=torch.float32, device=q.device)
-    code = _decode_fn()[0](
+    code = fn(
         q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), cache_layer.data_ptr(), block_table.data_ptr(),
         block_table.stride(0), positions.data_ptr(), token_row.data_ptr(), n, part_o.data_ptr(),
         part_ml.data_ptr(), num_heads, hkv, d, block_size, num_pages, chunks, float(scale),
         int(window), ops.status_word(q.device).data_ptr(), ops._stream(),
     )
-    ops._check(code, "attention_decode_bf16")
-    ops.launch_count += 1  # two kernels: split and merge
+    ops._check(code, name)
+    ops.launch_count += 1  # two kernels: split (or stream) and merge
     return out
 
 

@@ -46,6 +46,7 @@ MODULES = {
     "attention_bf16": "attention_bf16.cu",
     "attention_prefill_bf16": "attention_prefill_bf16.cu",
     "attention_prefill_tmem": "attention_prefill_tmem.cu",
+    "attention_decode_tma": "attention_decode_tma.cu",
 }
 
 _loaded: dict[str, ctypes.CDLL] = {}

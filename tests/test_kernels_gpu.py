@@ -205,11 +205,17 @@ def test_attention_simt(ops, dtype, hq, hkv, d, bs, window):
 @pytest.mark.parametrize("hq,hkv,d,bs,window", [
     (4, 2, 32, 4, None), (3, 1, 32, 8, None), (5, 5, 32, 16, 24), (32, 8, 64, 16, None), (6, 3, 128, 32, 100),
     (16, 1, 64, 16, None), (12, 2, 128, 16, 300), (7, 7, 64, 8, None), (40, 2, 64, 16, None),
+    (9, 3, 64, 32, 200), (32, 8, 128, 16, None),
 ])
-def test_attention_decode_split_kv(ops, hq, hkv, d, bs, window):
+@pytest.mark.parametrize("kernel", ["split", "stream"])
+def test_attention_decode_split_kv(ops, hq, hkv, d, bs, window, kernel):
     """One query token per request over caches of 1 .. 1500 tokens: several chunks of keys (128 or 256 by head size), a chunk
-    that holds a single key, windows that start inside a chunk; the far keys carry the weight."""
+    that holds a single key, windows that start inside a chunk; the far keys carry the weight.  Both
+    kernels: one CTA per chunk, and the persistent TMA stream (head sizes 64 and 128, pages of 8 and more)."""
     from gllm_b200.ops import attention_bf16
+
+    if kernel == "stream" and (d not in (64, 128) or bs not in (16, 32) or hkv > 8 or hq // hkv > 16):
+        pytest.skip("the stream kernel takes head sizes 64 and 128, pages of 16 and 32, up to 8 kv heads")
 
     g = torch.Generator().manual_seed(6)
     lens = [1, 37, 128, 129, 300, 1500, 64, 256, 257]
@@ -221,7 +227,7 @@ def test_attention_decode_split_kv(ops, hq, hkv, d, bs, window):
     assert attention_bf16.supports(d, bs)
     out = torch.full((n, hq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
     attention_bf16.decode_attention(qkv.cuda(), qkv.shape[1], pool.cuda(), table.cuda(), pos.cuda(), rows.cuda(), hq,
-                                    scale, window or 0, max(lens), None, out)
+                                    scale, window or 0, max(lens), None, out, kernel=kernel)
     ops.check_status()
     for r in range(n):
         want = _plain_attn(qs[r], ks[r], vs[r], pos[r:r + 1].long(), window, scale)
