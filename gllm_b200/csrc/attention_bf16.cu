@@ -253,24 +253,43 @@ decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride,
   }
 }
 
-// Merges the chunks of one (request, query head) in ascending order.
+// Merges the partial results of one (request, query head) in ascending order, in one pass (running
+// maximum, sum and output).  Only the chunks that can hold a visible key are read: those of the keys
+// kstart .. qpos, `per_span` consecutive chunks for every `span_keys` keys.
 template <int D>
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    __nv_bfloat16* __restrict__ out, int64_t out_stride, int hq, int num_chunks) {
+                     __nv_bfloat16* __restrict__ out, int64_t out_stride, int hq, int num_chunks,
+                     const int* __restrict__ positions, int window, int span_keys, int per_span) {
   pdl_trigger();
-  pdl_wait();
   const int n = blockIdx.y, h = blockIdx.x, d = threadIdx.x;
+  const int qpos = positions[n];                          // a step input: older than the step's kernels
+  const int kstart = window > 0 ? max(0, qpos - window + 1) : 0;
+  const int first = (kstart / span_keys) * per_span;
+  const int last = min(num_chunks, (qpos / span_keys + 1) * per_span);
+  pdl_wait();
   const float* ml = part_ml + ((int64_t)n * hq + h) * num_chunks * 2;
   const float* po = part_o + ((int64_t)n * hq + h) * num_chunks * D;
-  float mm = -INFINITY;
-  for (int s = 0; s < num_chunks; ++s) mm = fmaxf(mm, ml[2 * s]);
-  float o = 0.f, l = 0.f;
-  for (int s = 0; s < num_chunks; ++s) {
-    const float ms = ml[2 * s];
-    if (ms == -INFINITY) continue;
-    const float f = fast_exp2(ms - mm);
-    o += po[(int64_t)s * D + d] * f;
-    l += ml[2 * s + 1] * f;
+  float mm = -INFINITY, o = 0.f, l = 0.f;
+  constexpr int B = 8;                                    // chunks whose loads are in flight together
+  for (int s0 = first; s0 < last; s0 += B) {
+    float ms[B], ls[B], os[B];
+#pragma unroll
+    for (int i = 0; i < B; ++i) {
+      const bool in = s0 + i < last;
+      const float2 v = in ? __ldcg(reinterpret_cast<const float2*>(ml) + s0 + i) : make_float2(-INFINITY, 0.f);
+      ms[i] = v.x;
+      ls[i] = v.y;
+      os[i] = in ? __ldcg(po + (int64_t)(s0 + i) * D + d) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < B; ++i) {
+      if (ms[i] == -INFINITY) continue;
+      const float m_new = fmaxf(mm, ms[i]);
+      const float f_old = fast_exp2(mm - m_new), f_new = fast_exp2(ms[i] - m_new);   // f_old = 0 at the first chunk
+      o = o * f_old + os[i] * f_new;
+      l = l * f_old + ls[i] * f_new;
+      mm = m_new;
+    }
   }
   out[(int64_t)n * out_stride + (int64_t)h * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
 }
@@ -294,7 +313,7 @@ int decode_launch(const __nv_bfloat16* q, int64_t q_stride, __nv_bfloat16* out, 
                       num_chunks, scale * 1.4426950408889634f, window, status);
   if (e) return e;
   return gllm_launch(decode_merge_kernel<D>, dim3(hq, num_queries), dim3(D), 0, stream, part_o, part_ml, out,
-                     out_stride, hq, num_chunks);
+                     out_stride, hq, num_chunks, positions, window, S::CHUNK, 1);
 }
 }  // namespace
 

@@ -33,6 +33,9 @@ constexpr int ROWS = 16;        // query heads per kv head at most (rows of the 
 constexpr int CWARPS = 8;       // consumer warps
 constexpr int THREADS = (1 + CWARPS) * 32;
 constexpr int SPAN = 128;       // keys per work item
+// keys a warp takes from a stage: 32 (two pages of 16, or one of 32); 16 where 32 would not leave
+// room for two stages (head size 128 with pages of 16)
+__host__ __device__ constexpr int keys_per_warp(int d, int block_size) { return (d <= 64 || block_size == 32) ? 32 : 16; }
 constexpr int MAXQ = 512;       // requests whose position and block-table row are kept in shared memory
 constexpr int SMEM_BUDGET = 214 * 1024;
 
@@ -44,7 +47,8 @@ static __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, 
 
 // Sizes of a launch, the same on host and device.
 struct StreamPlan {
-  int pps;            // pages per stage (hkv * pps <= 8 warps)
+  int pps;            // warp tiles (of keys_per_warp keys) per stage and kv head (hkv * pps <= 8 warps)
+  int pages;          // pages per stage: pps * keys_per_warp / block_size
   int page_bytes;     // K (or V) of one page, all kv heads, one 64-dim block
   int kv_bytes;       // K (or V) of one stage
   int q_bytes;        // the query area of a stage: (hq + 16) rows of D
@@ -53,10 +57,12 @@ struct StreamPlan {
 };
 __host__ __device__ inline StreamPlan make_plan(int d, int hq, int hkv, int block_size) {
   StreamPlan p;
+  const int kpw = keys_per_warp(d, block_size);
   p.pps = CWARPS / hkv;
-  if (p.pps > SPAN / block_size) p.pps = SPAN / block_size;
+  if (p.pps > SPAN / kpw) p.pps = SPAN / kpw;
+  p.pages = p.pps * (kpw / block_size);
   p.page_bytes = hkv * block_size * 128;
-  p.kv_bytes = (d / 64) * p.pps * p.page_bytes;
+  p.kv_bytes = (d / 64) * p.pages * p.page_bytes;
   p.q_bytes = (((hq + ROWS) * d * 2 + 1023) / 1024) * 1024;
   p.stage_bytes = 2 * p.kv_bytes + p.q_bytes;
   p.stages = SMEM_BUDGET / p.stage_bytes;
@@ -77,6 +83,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const __nv_bflo
                      float* __restrict__ part_o, float* __restrict__ part_ml, int num_queries, int hq, int hkv,
                      int num_pages, int num_spans, float scale_log2, int window, int* __restrict__ status) {
   constexpr int DB = D / 64;
+  constexpr int KPW = keys_per_warp(D, BS);
   constexpr int PAGES_PER_SPAN = SPAN / BS;
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[8], empty_bar[8];
@@ -128,9 +135,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const __nv_bflo
     it.empty = it.c0 >= it.c1;
     return it;
   };
-  // the stages of an item: groups of pps pages from the first page with a visible key to the last
-  auto first_group = [&](const WorkItem& it) { return (it.c0 - it.span * SPAN) / (BS * plan.pps); };
-  auto last_group = [&](const WorkItem& it) { return (it.c1 - 1 - it.span * SPAN) / (BS * plan.pps); };
+  // the stages of an item: groups of plan.pages pages from the first page with a visible key to the last
+  auto first_group = [&](const WorkItem& it) { return (it.c0 - it.span * SPAN) / (BS * plan.pages); };
+  auto last_group = [&](const WorkItem& it) { return (it.c1 - 1 - it.span * SPAN) / (BS * plan.pages); };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -170,10 +177,10 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const __nv_bflo
         for (int g = g0; g <= g1; ++g, ++it) {
           const uint32_t s = it % STAGES, round = it / STAGES;
           if (pass == 0 && round > 0) { more = false; break; }
-          // lanes 0 .. pps-1 take the pages of this stage
-          const int page = __shfl_sync(0xffffffffu, my_page, min(g * plan.pps + lane, 31));
-          const int key = item.span * SPAN + (g * plan.pps + lane) * BS;
-          const bool mine = lane < plan.pps && page >= 0;
+          // lanes 0 .. pages-1 take the pages of this stage
+          const int page = __shfl_sync(0xffffffffu, my_page, min(g * plan.pages + lane, 31));
+          const int key = item.span * SPAN + (g * plan.pages + lane) * BS;
+          const bool mine = lane < plan.pages && page >= 0;
           const bool newest = key <= item.qpos && item.qpos < key + BS;
           const int n_present = __popc(__ballot_sync(0xffffffffu, mine));
           const bool with_q = g == g0;
@@ -194,8 +201,8 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const __nv_bflo
             const uint32_t dst = stage + (uint32_t)(lane * plan.page_bytes);
 #pragma unroll
             for (int db = 0; db < DB; ++db) {
-              tma_load_2d(dst + db * plan.pps * plan.page_bytes, &map_kv, db * 64, row_k, bar);
-              tma_load_2d(dst + plan.kv_bytes + db * plan.pps * plan.page_bytes, &map_kv, db * 64, row_v, bar);
+              tma_load_2d(dst + db * plan.pages * plan.page_bytes, &map_kv, db * 64, row_k, bar);
+              tma_load_2d(dst + plan.kv_bytes + db * plan.pages * plan.page_bytes, &map_kv, db * 64, row_v, bar);
             }
           }
           if (lane == 0 && with_q && pass == 1)
@@ -261,34 +268,40 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const __nv_bflo
               ldmatrix_x4(qf[ks], smem_u32(q_sm + row * (D * 2) + piece * 16));
             }
           }
-          // this warp's tile of the stage: page `slot`, head kvh: BS rows of 128 bytes per 64-dim block
-          const int k0 = item.span * SPAN + (g * plan.pps + slot) * BS;
-          if (k0 < item.c1 && k0 + BS > item.c0) {
-            const uint32_t tile = (uint32_t)(slot * plan.page_bytes + kvh * BS * 128);
-            const uint32_t blk = (uint32_t)(plan.pps * plan.page_bytes);
-            // value rows without a visible key (the unwritten tail of a page, keys before the window)
-            if (k0 < item.c0 || k0 + BS > item.c1) {
-              for (int idx = lane; idx < BS * DB * 8; idx += 32) {
+          // this warp's tile of the stage: KPW keys of head kvh, i.e. the pages slot * PPW .. of the
+          // stage; a page's rows of one head are BS rows of 128 bytes per 64-dim block
+          constexpr int PPW = KPW / BS;
+          const int k0 = item.span * SPAN + (g * plan.pps + slot) * KPW;
+          if (k0 < item.c1 && k0 + KPW > item.c0) {
+            const uint32_t blk = (uint32_t)(plan.pages * plan.page_bytes);
+            // byte offset of key kk (0 .. KPW-1) of the tile inside a 64-dim block
+            auto key_row = [&](int kk) -> uint32_t {
+              return (uint32_t)((slot * PPW + kk / BS) * plan.page_bytes + kvh * BS * 128 + (kk % BS) * 128);
+            };
+            // value rows without a visible key (the unwritten tail of a page, a page that was not read,
+            // keys before the window)
+            if (k0 < item.c0 || k0 + KPW > item.c1) {
+              for (int idx = lane; idx < KPW * DB * 8; idx += 32) {
                 const int r = idx / (DB * 8), rest = idx - r * (DB * 8);
                 if (k0 + r < item.c0 || k0 + r >= item.c1)
-                  *reinterpret_cast<uint4*>(v_sm + tile + (rest >> 3) * blk + r * 128 + ((rest & 7) << 4)) =
+                  *reinterpret_cast<uint4*>(v_sm + key_row(r) + (rest >> 3) * blk + ((rest & 7) << 4)) =
                       make_uint4(0u, 0u, 0u, 0u);
               }
               __syncwarp();
             }
-            // ---- S = Q K^T (16 heads x BS keys)
-            float sc[BS / 8][4];
+            // ---- S = Q K^T (16 heads x KPW keys)
+            float sc[KPW / 8][4];
 #pragma unroll
-            for (int nt = 0; nt < BS / 8; ++nt)
+            for (int nt = 0; nt < KPW / 8; ++nt)
 #pragma unroll
               for (int e = 0; e < 4; ++e) sc[nt][e] = 0.f;
 #pragma unroll
             for (int ks = 0; ks < D / 16; ++ks) {
 #pragma unroll
-              for (int np = 0; np < BS / 16; ++np) {
+              for (int np = 0; np < KPW / 16; ++np) {
                 const int row = np * 16 + (mat >> 1) * 8 + rl, piece = 2 * ks + (mat & 1);
                 uint32_t b[4];
-                ldmatrix_x4(b, smem_u32(k_sm + tile + (piece >> 3) * blk + row * 128 + (((piece & 7) ^ (row & 7)) << 4)));
+                ldmatrix_x4(b, smem_u32(k_sm + key_row(row) + (piece >> 3) * blk + (((piece & 7) ^ (row & 7)) << 4)));
                 mma_bf16(sc[2 * np], qf[ks], b[0], b[1]);
                 mma_bf16(sc[2 * np + 1], qf[ks], b[2], b[3]);
               }
@@ -296,7 +309,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const __nv_bflo
             // ---- mask, scale, running softmax (rows g8 and g8 + 8)
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int nt = 0; nt < BS / 8; ++nt)
+            for (int nt = 0; nt < KPW / 8; ++nt)
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const int key = k0 + nt * 8 + 2 * t4 + (e & 1);
@@ -316,7 +329,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const __nv_bflo
             }
             float ls[2] = {0.f, 0.f};
 #pragma unroll
-            for (int nt = 0; nt < BS / 8; ++nt)
+            for (int nt = 0; nt < KPW / 8; ++nt)
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const float p = fast_exp2(sc[nt][e] - m[e >> 1]);
@@ -338,7 +351,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const __nv_bflo
             }
             // ---- O += P V
 #pragma unroll
-            for (int kk = 0; kk < BS / 16; ++kk) {
+            for (int kk = 0; kk < KPW / 16; ++kk) {
               uint32_t a[4];
               a[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
               a[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
@@ -348,7 +361,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const __nv_bflo
               for (int nd2 = 0; nd2 < D / 16; ++nd2) {
                 const int row = kk * 16 + (mat & 1) * 8 + rl, piece = 2 * nd2 + (mat >> 1);
                 uint32_t b[4];
-                ldmatrix_x4_trans(b, smem_u32(v_sm + tile + (piece >> 3) * blk + row * 128 + (((piece & 7) ^ (row & 7)) << 4)));
+                ldmatrix_x4_trans(b, smem_u32(v_sm + key_row(row) + (piece >> 3) * blk + (((piece & 7) ^ (row & 7)) << 4)));
                 mma_bf16(o[2 * nd2], a, b[0], b[1]);
                 mma_bf16(o[2 * nd2 + 1], a, b[2], b[3]);
               }
@@ -384,25 +397,43 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const __nv_bflo
   }
 }
 
-// Merges the partial results of one (request, query head) in ascending order.
+// Merges the partial results of one (request, query head) in ascending order, in one pass (running
+// maximum, sum and output).  Only the chunks that can hold a visible key are read: those of the keys
+// kstart .. qpos, `per_span` consecutive chunks for every `span_keys` keys.
 template <int D>
 __global__ void decode_stream_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                           __nv_bfloat16* __restrict__ out, int64_t out_stride, int hq,
-                                           int num_chunks) {
+                     __nv_bfloat16* __restrict__ out, int64_t out_stride, int hq, int num_chunks,
+                     const int* __restrict__ positions, int window, int span_keys, int per_span) {
   pdl_trigger();
-  pdl_wait();
   const int n = blockIdx.y, h = blockIdx.x, d = threadIdx.x;
+  const int qpos = positions[n];                          // a step input: older than the step's kernels
+  const int kstart = window > 0 ? max(0, qpos - window + 1) : 0;
+  const int first = (kstart / span_keys) * per_span;
+  const int last = min(num_chunks, (qpos / span_keys + 1) * per_span);
+  pdl_wait();
   const float* ml = part_ml + ((int64_t)n * hq + h) * num_chunks * 2;
   const float* po = part_o + ((int64_t)n * hq + h) * num_chunks * D;
-  float mm = -INFINITY;
-  for (int s = 0; s < num_chunks; ++s) mm = fmaxf(mm, ml[2 * s]);
-  float o = 0.f, l = 0.f;
-  for (int s = 0; s < num_chunks; ++s) {
-    const float ms = ml[2 * s];
-    if (ms == -INFINITY) continue;
-    const float f = fast_exp2(ms - mm);
-    o += po[(int64_t)s * D + d] * f;
-    l += ml[2 * s + 1] * f;
+  float mm = -INFINITY, o = 0.f, l = 0.f;
+  constexpr int B = 8;                                    // chunks whose loads are in flight together
+  for (int s0 = first; s0 < last; s0 += B) {
+    float ms[B], ls[B], os[B];
+#pragma unroll
+    for (int i = 0; i < B; ++i) {
+      const bool in = s0 + i < last;
+      const float2 v = in ? __ldcg(reinterpret_cast<const float2*>(ml) + s0 + i) : make_float2(-INFINITY, 0.f);
+      ms[i] = v.x;
+      ls[i] = v.y;
+      os[i] = in ? __ldcg(po + (int64_t)(s0 + i) * D + d) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < B; ++i) {
+      if (ms[i] == -INFINITY) continue;
+      const float m_new = fmaxf(mm, ms[i]);
+      const float f_old = fast_exp2(mm - m_new), f_new = fast_exp2(ms[i] - m_new);   // f_old = 0 at the first chunk
+      o = o * f_old + os[i] * f_new;
+      l = l * f_old + ls[i] * f_new;
+      mm = m_new;
+    }
   }
   out[(int64_t)n * out_stride + (int64_t)h * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
 }
@@ -465,7 +496,7 @@ int stream_launch(const __nv_bfloat16* q, int64_t q_stride, __nv_bfloat16* out, 
                       num_spans, scale * 1.4426950408889634f, window, status);
   if (e) return e;
   return gllm_launch(decode_stream_merge_kernel<D>, dim3(hq, num_queries), dim3(D), 0, stream, part_o, part_ml, out,
-                     out_stride, hq, num_spans * plan.pps);
+                     out_stride, hq, num_spans * plan.pps, positions, window, SPAN, plan.pps);
 }
 
 int sm_count() {
