@@ -10,8 +10,9 @@
 //   warp 0: TMA loads. Q once (a 3-D box: 64 dims x G' heads x tokens); per key tile the K and V
 //           pages straight out of the cache pool, one box per page, each lane issuing its own page's
 //           boxes, 128-byte swizzle;
-//   warp 1 (one thread): S = Q K^T into tensor memory (128 x 128 fp32, two buffers: the scores of
-//           the next tile are computed while this one is exponentiated), later O += P V (128 x D);
+//   warp 1 (one thread): S = Q K^T into tensor memory (128 x 128 fp32), later O += P V (128 x D).
+//           Head size 128: two score buffers, the scores of the next tile are computed while this one
+//           is exponentiated.  Head size 64: one buffer, and two CTAs per SM that fill one another's gaps;
 //   warps 2-5 (one thread per row): read S from tensor memory, mask, running maximum and sum in
 //           fp32, rescale O in tensor memory when the maximum moved, write P (bf16) into shared
 //           memory in the swizzled layout the second product reads, at the end O / sum -> global.
@@ -38,25 +39,30 @@ struct TShape {
   static constexpr int DB = D / 64;                     // 64-wide blocks of the head dimension
   static constexpr int TILE = 128 * 128;                // bytes of a [128 x 64] bf16 tile
   static constexpr int Q_BYTES = DB * TILE;
+  // Head size 64: two CTAs share an SM (one buffer each for K, V and the scores), and overlap one
+  // another's softmax and products.  Head size 128: one CTA with two of each.
+  static constexpr int NBUF = D <= 64 ? 1 : 2;
+  static constexpr int CTAS_PER_SM = D <= 64 ? 2 : 1;
   static constexpr int KV_STAGE = DB * TILE;            // K (or V) of one key tile
   static constexpr int P_BYTES = 2 * TILE;              // [128 rows x 128 keys] as two 64-key blocks
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;         // 2 stages
-  static constexpr int OFF_V = OFF_K + 2 * KV_STAGE;    // 2 stages
-  static constexpr int OFF_P = OFF_V + 2 * KV_STAGE;
+  static constexpr int OFF_V = OFF_K + NBUF * KV_STAGE;
+  static constexpr int OFF_P = OFF_V + NBUF * KV_STAGE;
   static constexpr int SMEM = OFF_P + P_BYTES + 1024;
-  static constexpr int TMEM_COLS = 512;                 // S twice: 128 columns each, O: D columns
-  static constexpr int COL_S = 0, COL_O = 256;
+  static constexpr int TMEM_COLS = NBUF == 1 ? 256 : 512;   // S: 128 columns per buffer, O: D columns
+  static constexpr int COL_S = 0, COL_O = NBUF * 128;
 };
 
 template <int D>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, TShape<D>::CTAS_PER_SM)
 prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                     __nv_bfloat16* __restrict__ out, int64_t out_stride, const int* __restrict__ block_table,
                     int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                     const int* __restrict__ slots, int hq, int hkv, int gp, int block_size, int num_pages,
                     float scale_log2, int window, int* __restrict__ status) {
   using S = TShape<D>;
+  constexpr int NB = S::NBUF;
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full, o_ready;
   __shared__ uint32_t tmem_base_slot;
@@ -77,7 +83,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(smem_addr(&q_full), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < NB; ++s) {
       mbar_init(smem_addr(&k_full[s]), 1);
       mbar_init(smem_addr(&v_full[s]), 1);
       mbar_init(smem_addr(&k_empty[s]), 1);
@@ -142,12 +148,12 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // K (plane 0) or V (plane 1) of tile j into its stage, once the product that read the stage's
     // previous tile is done
     auto load = [&](int j, int page, int plane) -> bool {
-      const int s = j & 1;
+      const int s = j % NB;
       const uint32_t full = smem_addr(plane ? &v_full[s] : &k_full[s]);
       const int n_present = __popc(__ballot_sync(0xffffffffu, page >= 0));
       int ok = 1;
       if (lane == 0) {
-        ok = mbar_wait(smem_addr(plane ? &v_empty[s] : &k_empty[s]), ((uint32_t)(j >> 1) & 1u) ^ 1u, status, &abort_flag)
+        ok = mbar_wait(smem_addr(plane ? &v_empty[s] : &k_empty[s]), ((uint32_t)(j / NB) & 1u) ^ 1u, status, &abort_flag)
                  ? 1 : 0;
         if (ok) mbar_expect_tx(full, (uint32_t)n_present * page_bytes);
       }
@@ -161,13 +167,19 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       return true;
     };
-    // order: K0, then K(j+1) before V(j): the next scores are issued before this tile's values are used
+    // order: K0, then (two buffers) K(j+1) before V(j): the next scores are issued before this tile's
+    // values are used
     int page = lookup(0);
     bool ok = n_tiles > 0 && load(0, page, 0);
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int page_next = lookup(j + 1);
-      if (j + 1 < n_tiles) ok = load(j + 1, page_next, 0);
-      if (ok) ok = load(j, page, 1);
+      if (NB == 1) {                                    // the order in which the stages come free
+        ok = load(j, page, 1);
+        if (ok && j + 1 < n_tiles) ok = load(j + 1, page_next, 0);
+      } else {
+        if (j + 1 < n_tiles) ok = load(j + 1, page_next, 0);
+        if (ok) ok = load(j, page, 1);
+      }
       page = page_next;
     }
   } else if (active && warp == 1) {
@@ -177,8 +189,8 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       constexpr uint32_t idesc_o = umma_idesc_b_mn(BM, 64);
       const uint32_t tmem_s = tmem_base + S::COL_S, tmem_o = tmem_base + S::COL_O;
       auto issue_s = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!mbar_wait(smem_addr(&k_full[s]), (uint32_t)(j >> 1) & 1u, status, &abort_flag)) return false;
+        const int s = j % NB;
+        if (!mbar_wait(smem_addr(&k_full[s]), (uint32_t)(j / NB) & 1u, status, &abort_flag)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int db = 0; db < S::DB; ++db)
@@ -194,11 +206,11 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // scores run one tile ahead of the softmax: S(j+1) is computed while tile j is exponentiated
       bool ok = mbar_wait(smem_addr(&q_full), 0u, status, &abort_flag);
       if (ok) ok = issue_s(0);
-      if (ok && n_tiles > 1) ok = issue_s(1);
+      if (NB > 1 && ok && n_tiles > 1) ok = issue_s(1);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j & 1;
+        const int s = j % NB;
         ok = mbar_wait(smem_addr(&p_full), (uint32_t)j & 1u, status, &abort_flag);   // P(j) written, S(j) read
-        if (ok) ok = mbar_wait(smem_addr(&v_full[s]), (uint32_t)(j >> 1) & 1u, status, &abort_flag);
+        if (ok) ok = mbar_wait(smem_addr(&v_full[s]), (uint32_t)(j / NB) & 1u, status, &abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -210,7 +222,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                       (j > 0 || k > 0) ? 1u : 0u);
         umma_commit(smem_addr(&v_empty[s]));            // V of this stage is consumed
         umma_commit(smem_addr(&o_ready));               // O holds tiles 0 .. j, P may be overwritten
-        if (j + 2 < n_tiles) ok = issue_s(j + 2);
+        if (j + NB < n_tiles) ok = issue_s(j + NB);
       }
     }
   } else if (active && warp >= 2) {
@@ -227,8 +239,8 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
       const int kv0 = (tile_first + j) * BN;
-      const uint32_t tmem_s = tmem_s0 + (uint32_t)((j & 1) * BN);
-      mbar_wait(smem_addr(&s_full[j & 1]), (uint32_t)(j >> 1) & 1u, status, &abort_flag);
+      const uint32_t tmem_s = tmem_s0 + (uint32_t)((j % NB) * BN);
+      mbar_wait(smem_addr(&s_full[j % NB]), (uint32_t)(j / NB) & 1u, status, &abort_flag);
       asm volatile("bar.sync 1, 128;" ::: "memory");     // the four warps go on together
       if (abort_flag) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -316,12 +328,12 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // value rows of keys the request does not hold (a page's unwritten tail, a page that was not
       // read): zero them, so that probability 0 times a stale value never reaches the output
       if (kv0 + BN - 1 > pos_last || kv0 < kv_lo) {
-        mbar_wait(smem_addr(&v_full[j & 1]), (uint32_t)(j >> 1) & 1u, status, &abort_flag);
+        mbar_wait(smem_addr(&v_full[j % NB]), (uint32_t)(j / NB) & 1u, status, &abort_flag);
         const int key = kv0 + row;                       // thread <-> key row of the V tile
         if (key > pos_last || key < kv_lo) {
           for (int db = 0; db < S::DB; ++db) {
             uint4* vrow =
-                reinterpret_cast<uint4*>(base_ptr + S::OFF_V + (j & 1) * S::KV_STAGE + db * S::TILE + row * 128);
+                reinterpret_cast<uint4*>(base_ptr + S::OFF_V + (j % NB) * S::KV_STAGE + db * S::TILE + row * 128);
 #pragma unroll
             for (int i = 0; i < 8; ++i) vrow[i] = make_uint4(0u, 0u, 0u, 0u);
           }
