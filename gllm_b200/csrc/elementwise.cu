@@ -240,7 +240,7 @@ __global__ void add_rmsnorm_cluster_kernel(const float* __restrict__ parts, int 
                                            T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps,
                                            int unit_offset) {
   __shared__ float scratch[32];
-  __shared__ float my_ss;
+  __shared__ float all_ss[16];
   pdl_trigger();
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = (int)cluster.block_rank(), n_ranks = (int)cluster.num_blocks();
@@ -270,12 +270,13 @@ __global__ void add_rmsnorm_cluster_kernel(const float* __restrict__ parts, int 
       ss += x[k] * x[k];
     }
   }
+  // every block pushes its sum into all blocks' slots: after one cluster barrier each reads only its
+  // own shared memory, so none has to stay for the others
   const float mine = block_sum(ss, scratch);
-  if (threadIdx.x == 0) my_ss = mine;
+  if (threadIdx.x < n_ranks) *cluster.map_shared_rank(&all_ss[rank], threadIdx.x) = mine;
   cluster.sync();
   float total = 0.f;
-  for (int rk = 0; rk < n_ranks; ++rk) total += *cluster.map_shared_rank(&my_ss, rk);
-  cluster.sync();                                       // nobody leaves while its sum may still be read
+  for (int rk = 0; rk < n_ranks; ++rk) total += all_ss[rk];
   const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
   T* o = out + (size_t)i * hidden;
 #pragma unroll

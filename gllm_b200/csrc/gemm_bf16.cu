@@ -466,10 +466,16 @@ GLLM_API int gllm_gemm_bf16_splits(int M, int N, int K) {
   const int bucket = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   const int tiles = (N + BM - 1) / BM;
   const int num_kb = (K + BK - 1) / BK;
-  int s = 1;
   if (tiles >= 96) return 1;                    // wide enough to keep most SMs streaming without a cut
-  while (s < 16 && tiles * s < 148 && 2 * s <= K / (8 * bucket) && num_kb / (2 * s) >= 2) s *= 2;
-  return s;
+  // as many splits as give every SM at most one item (one pipeline ramp per SM), each at least two
+  // k-blocks long, none empty, the partial tiles a small part of the weight's bytes
+  int best = 1;
+  for (int s = 2; s <= 16; ++s) {
+    if (tiles * s > 148 || s > K / (8 * bucket) || num_kb / s < 2) break;
+    const int per = (num_kb + s - 1) / s;
+    if (per * (s - 1) < num_kb) best = s;        // the last split is not empty
+  }
+  return best;
 }
 
 // Output tiles of the launch (the ticket array needs this many zeroed ints when splits > 1).

@@ -113,7 +113,7 @@ _decode_stream = None
 STREAM_SPAN = 128
 # the stream kernel has one work item per 128 keys of a request: below this many items the split
 # kernel, with a work item per kv head as well, fills the machine better
-STREAM_MIN_ITEMS = 296
+STREAM_MIN_ITEMS = int(__import__('os').environ.get('GLLM_B200_STREAM_MIN_ITEMS', 296))
 
 
 def _decode_stream_fn():
