@@ -21,6 +21,8 @@
 //
 // One block of 1024 threads per row.
 #include "common.cuh"
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
 
 namespace {
 constexpr int THREADS = 1024;
@@ -347,22 +349,45 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int V, const
   }
 }
 
+// A cluster of ARGMAX_CLUSTER blocks shares one row (a row of a large vocabulary read through one
+// SM's port takes longer than the rest of a decode step's tail): each block takes a stretch of the
+// row, pushes its (maximum, index) into every block's shared memory, and after one cluster barrier
+// rank 0 picks the winner (the lowest index among equal maxima, as a single block would).
+constexpr int ARGMAX_CLUSTER = 8;
 __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, int64_t row_stride, int V, int* __restrict__ out_token,
               const int* __restrict__ out_index) {
   __shared__ Smem s;
+  __shared__ float peer_v[ARGMAX_CLUSTER];
+  __shared__ int peer_i[ARGMAX_CLUSTER];
   pdl_trigger();
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank(), n_ranks = (int)cluster.num_blocks();
+  const int row = blockIdx.y;
+  const int per = (V + n_ranks - 1) / n_ranks;
+  const int j0 = rank * per, j1 = min(V, j0 + per);
   pdl_wait();
-  const float* x = logits + (int64_t)blockIdx.x * row_stride;
+  const float* x = logits + (int64_t)row * row_stride;
   float vmax = -INFINITY;
   int imax = 0x7fffffff;
-  for (int j = threadIdx.x; j < V; j += THREADS) {
+  for (int j = j0 + threadIdx.x; j < j1; j += THREADS) {
     const float v = x[j];
     if (v > vmax) { vmax = v; imax = j; }
   }
   int arg;
-  block_max_arg(vmax, imax, &arg, s);
-  if (threadIdx.x == 0) out_token[out_index ? out_index[blockIdx.x] : blockIdx.x] = arg;
+  const float best = block_max_arg(vmax, imax, &arg, s);
+  if (threadIdx.x == 0) {
+    *cluster.map_shared_rank(&peer_v[rank], 0) = best;
+    *cluster.map_shared_rank(&peer_i[rank], 0) = arg;
+  }
+  cluster.sync();
+  if (rank == 0 && threadIdx.x == 0) {
+    float bv = peer_v[0];
+    int bi = peer_i[0];
+    for (int r = 1; r < n_ranks; ++r)
+      if (peer_v[r] > bv || (peer_v[r] == bv && peer_i[r] < bi)) { bv = peer_v[r]; bi = peer_i[r]; }
+    out_token[out_index ? out_index[row] : row] = bi;
+  }
 }
 }  // namespace
 
@@ -383,6 +408,6 @@ GLLM_API int gllm_argmax(const float* logits, int64_t row_stride, int rows, int 
                          const int* out_index, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (V <= 0) return (int)cudaErrorInvalidValue;
-  return gllm_launch(argmax_kernel, dim3(rows), dim3(THREADS), 0, stream, logits, row_stride, V, out_token,
-                     out_index);
+  return gllm_launch_cluster(argmax_kernel, dim3(ARGMAX_CLUSTER, rows), dim3(THREADS), 0, stream,
+                             (unsigned)ARGMAX_CLUSTER, logits, row_stride, V, out_token, out_index);
 }
