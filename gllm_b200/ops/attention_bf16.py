@@ -8,6 +8,7 @@ so each kernel works on one contiguous run of tokens.
 
 from __future__ import annotations
 
+import os
 from ctypes import c_float, c_int, c_int64, c_void_p
 
 import torch
@@ -113,7 +114,8 @@ _decode_stream = None
 STREAM_SPAN = 128
 # the stream kernel has one work item per 128 keys of a request: below this many items the split
 # kernel, with a work item per kv head as well, fills the machine better
-STREAM_MIN_ITEMS = int(__import__('os').environ.get('GLLM_B200_STREAM_MIN_ITEMS', 296))
+# (GLLM_B200_STREAM_MIN_ITEMS overrides the threshold: tests use 1 to run small steps through it)
+STREAM_MIN_ITEMS = int(os.environ.get("GLLM_B200_STREAM_MIN_ITEMS", 296))
 
 
 def _decode_stream_fn():

@@ -151,3 +151,22 @@ def test_replay_all_cuts(name, dtype, tmp_path):
     steps, index = mixed_steps(seqs, max_tokens=448, seed=9)
     results = replay(folder, dtype, steps, str(tmp_path / "out2"), max_tokens=448, vocab=vocab)
     compare(results, index, plain, *tol)
+
+
+def test_replay_through_the_stream_decode_kernel(tmp_path, monkeypatch):
+    """The single tokens of tiny D (head size 64, one kv head, a window of 40 on one layer, pages of
+    16) through the persistent TMA decode kernel, which steps this small would not pick by themselves:
+    the tail decoded token by token, and the mixed steps with pages used again."""
+    monkeypatch.setenv("GLLM_B200_STREAM_MIN_ITEMS", "1")
+    folder = write_tiny("D", str(tmp_path / "model"), sharp=False)
+    cfg, weights = read_raw(folder, round_to_bf16=True)
+    vocab = cfg["vocab_size"]
+    seqs = sequences(vocab, seed=5)
+    plain = {k: plain_forward(cfg, weights, v, torch.float64) for k, v in seqs.items()}
+    steps, index = single_request_steps(seqs)
+    results = replay(folder, "bfloat16", steps, str(tmp_path / "out1"), max_tokens=rounded(max(LENGTHS.values())),
+                     vocab=vocab)
+    compare(results, index, plain, BF16_TOL_MAX, BF16_TOL_MEAN)
+    steps, index = mixed_steps(seqs, max_tokens=448, seed=9)
+    results = replay(folder, "bfloat16", steps, str(tmp_path / "out2"), max_tokens=448, vocab=vocab)
+    compare(results, index, plain, BF16_TOL_MAX, BF16_TOL_MEAN)
