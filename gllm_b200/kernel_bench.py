@@ -102,19 +102,28 @@ def attention_prefill(tokens=2048, context=0, hq=32, hkv=8, d=64, block_size=16,
             "shape": dict(tokens=tokens, context=context, heads=hq, kv_heads=hkv, head_dim=d, block_size=block_size)}
 
 
-def linear(m=8, n=16384, k=2048, iters=5, peaks=None, out_fp32=False):
+def linear(m=8, n=16384, k=2048, iters=5, peaks=None, out_fp32=False, gated=0, split=0):
+    """x [m, k] times a [n, k] weight.  ``gated``: the weight is a gate/up stack (n = 2 x features) and
+    the epilogue writes SiLU(gate) * up.  ``split``: a product cut along K leaves its splits unsummed,
+    as the decode step's products do (their consumers add them)."""
     from gllm_b200 import ops
 
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
     out = torch.empty(m, n, dtype=torch.float32 if out_fp32 else torch.bfloat16, device="cuda")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    fn = lambda: ops.linear(x, w, out_dtype=out.dtype, out=out)
+    if gated:
+        fn = lambda: ops.linear_gated(x, w)
+    elif split:
+        fn = lambda: ops.linear(x, w, split_ok=True)
+    else:
+        fn = lambda: ops.linear(x, w, out_dtype=out.dtype, out=out)
     us = _time(fn, iters, flush)
     nbytes = (m * k + n * k) * 2 + out.numel() * out.element_size()
     flops = 2.0 * m * n * k
     gbs, tf = nbytes / us / 1e3, flops / us / 1e6
-    return {"kernel": "linear", "us": round(us, 2), "achieved_gbs": round(gbs, 1), "achieved_tflops": round(tf, 1),
+    name = "linear (gated epilogue)" if gated else ("linear (unsummed splits)" if split else "linear")
+    return {"kernel": name, "us": round(us, 2), "achieved_gbs": round(gbs, 1), "achieved_tflops": round(tf, 1),
             "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4), "frac_of_bf16_peak": round(tf / peaks["bf16_tflops"], 4),
             "shape": dict(m=m, n=n, k=k)}
 
