@@ -14,8 +14,8 @@
 //           Head size 128: two score buffers, the scores of the next tile are computed while this one
 //           is exponentiated.  Head size 64: one buffer, and two CTAs per SM that fill one another's gaps;
 //   warps 2-5 (one thread per row): read S from tensor memory, mask, running maximum and sum in
-//           fp32, rescale O in tensor memory when the maximum moved, write P (bf16) into shared
-//           memory in the swizzled layout the second product reads, at the end O / sum -> global.
+//           fp32, rescale O in tensor memory when the maximum moved, write P (bf16) back into tensor
+//           memory, from where the second product takes it as its A operand; at the end O / sum -> global.
 //
 // V is used as it lies in the cache ([key][dim], i.e. the "MN-major" operand of the second
 // product); nothing is transposed or gathered.  Keys outside a row's view get probability 0 and the
@@ -39,19 +39,20 @@ struct TShape {
   static constexpr int DB = D / 64;                     // 64-wide blocks of the head dimension
   static constexpr int TILE = 128 * 128;                // bytes of a [128 x 64] bf16 tile
   static constexpr int Q_BYTES = DB * TILE;
-  // Head size 64: two CTAs share an SM (one buffer each for K, V and the scores), and overlap one
-  // another's softmax and products.  Head size 128: one CTA with two of each.
+  // Head size 64: two CTAs share an SM (one score buffer each in tensor memory), and overlap one
+  // another's softmax and products.  Head size 128: one CTA with two score buffers.
   static constexpr int NBUF = D <= 64 ? 1 : 2;
   static constexpr int CTAS_PER_SM = D <= 64 ? 2 : 1;
   static constexpr int KV_STAGE = DB * TILE;            // K (or V) of one key tile
-  static constexpr int P_BYTES = 2 * TILE;              // [128 rows x 128 keys] as two 64-key blocks
   static constexpr int OFF_Q = 0;
   static constexpr int OFF_K = OFF_Q + Q_BYTES;         // 2 stages
-  static constexpr int OFF_V = OFF_K + NBUF * KV_STAGE;
-  static constexpr int OFF_P = OFF_V + NBUF * KV_STAGE;
-  static constexpr int SMEM = OFF_P + P_BYTES + 1024;
-  static constexpr int TMEM_COLS = NBUF == 1 ? 256 : 512;   // S: 128 columns per buffer, O: D columns
-  static constexpr int COL_S = 0, COL_O = NBUF * 128;
+  static constexpr int KV_STAGES = 2;
+  static constexpr int OFF_V = OFF_K + KV_STAGES * KV_STAGE;
+  static constexpr int SMEM = OFF_V + KV_STAGES * KV_STAGE + 1024;
+  // S: 128 columns per buffer (fp32), O: D columns (fp32), P: 64 columns (128 bf16 per row)
+  static constexpr int TMEM_COLS = NBUF == 1 ? 256 : 512;
+  static constexpr int COL_S = 0, COL_O = NBUF * 128, COL_P = COL_O + D;
+  static_assert(COL_P + 64 <= TMEM_COLS, "tensor memory columns");
 };
 
 template <int D>
@@ -62,7 +63,8 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const int* __restrict__ slots, int hq, int hkv, int gp, int block_size, int num_pages,
                     float scale_log2, int window, int* __restrict__ status) {
   using S = TShape<D>;
-  constexpr int NB = S::NBUF;
+  constexpr int NB = S::NBUF;                            // score buffers in tensor memory
+  constexpr int KS = S::KV_STAGES;                       // K (and V) stages in shared memory
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full, o_ready;
   __shared__ uint32_t tmem_base_slot;
@@ -83,7 +85,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(smem_addr(&q_full), 1);
-    for (int s = 0; s < NB; ++s) {
+    for (int s = 0; s < 2; ++s) {
       mbar_init(smem_addr(&k_full[s]), 1);
       mbar_init(smem_addr(&v_full[s]), 1);
       mbar_init(smem_addr(&k_empty[s]), 1);
@@ -148,12 +150,12 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // K (plane 0) or V (plane 1) of tile j into its stage, once the product that read the stage's
     // previous tile is done
     auto load = [&](int j, int page, int plane) -> bool {
-      const int s = j % NB;
+      const int s = j % KS;
       const uint32_t full = smem_addr(plane ? &v_full[s] : &k_full[s]);
       const int n_present = __popc(__ballot_sync(0xffffffffu, page >= 0));
       int ok = 1;
       if (lane == 0) {
-        ok = mbar_wait(smem_addr(plane ? &v_empty[s] : &k_empty[s]), ((uint32_t)(j / NB) & 1u) ^ 1u, status, &abort_flag)
+        ok = mbar_wait(smem_addr(plane ? &v_empty[s] : &k_empty[s]), ((uint32_t)(j / KS) & 1u) ^ 1u, status, &abort_flag)
                  ? 1 : 0;
         if (ok) mbar_expect_tx(full, (uint32_t)n_present * page_bytes);
       }
@@ -173,13 +175,8 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     bool ok = n_tiles > 0 && load(0, page, 0);
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int page_next = lookup(j + 1);
-      if (NB == 1) {                                    // the order in which the stages come free
-        ok = load(j, page, 1);
-        if (ok && j + 1 < n_tiles) ok = load(j + 1, page_next, 0);
-      } else {
-        if (j + 1 < n_tiles) ok = load(j + 1, page_next, 0);
-        if (ok) ok = load(j, page, 1);
-      }
+      if (j + 1 < n_tiles) ok = load(j + 1, page_next, 0);
+      if (ok) ok = load(j, page, 1);
       page = page_next;
     }
   } else if (active && warp == 1) {
@@ -187,20 +184,20 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc(BM, BN);
       constexpr uint32_t idesc_o = umma_idesc_b_mn(BM, 64);
-      const uint32_t tmem_s = tmem_base + S::COL_S, tmem_o = tmem_base + S::COL_O;
+      const uint32_t tmem_s = tmem_base + S::COL_S, tmem_o = tmem_base + S::COL_O, tmem_p = tmem_base + S::COL_P;
       auto issue_s = [&](int j) -> bool {
-        const int s = j % NB;
-        if (!mbar_wait(smem_addr(&k_full[s]), (uint32_t)(j / NB) & 1u, status, &abort_flag)) return false;
+        const int s = j % KS, sb = j % NB;
+        if (!mbar_wait(smem_addr(&k_full[s]), (uint32_t)(j / KS) & 1u, status, &abort_flag)) return false;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int db = 0; db < S::DB; ++db)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_s + s * BN, umma_desc(base + S::OFF_Q + db * S::TILE + k * 32),
+            umma_bf16(tmem_s + sb * BN, umma_desc(base + S::OFF_Q + db * S::TILE + k * 32),
                       umma_desc(base + S::OFF_K + s * S::KV_STAGE + db * S::TILE + k * 32), idesc_s,
                       (db > 0 || k > 0) ? 1u : 0u);
         umma_commit(smem_addr(&k_empty[s]));            // K of this stage is consumed
-        umma_commit(smem_addr(&s_full[s]));
+        umma_commit(smem_addr(&s_full[sb]));
         return true;
       };
       // scores run one tile ahead of the softmax: S(j+1) is computed while tile j is exponentiated
@@ -208,18 +205,18 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (ok) ok = issue_s(0);
       if (NB > 1 && ok && n_tiles > 1) ok = issue_s(1);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % NB;
+        const int s = j % KS;
         ok = mbar_wait(smem_addr(&p_full), (uint32_t)j & 1u, status, &abort_flag);   // P(j) written, S(j) read
-        if (ok) ok = mbar_wait(smem_addr(&v_full[s]), (uint32_t)(j / NB) & 1u, status, &abort_flag);
+        if (ok) ok = mbar_wait(smem_addr(&v_full[s]), (uint32_t)(j / KS) & 1u, status, &abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
         for (int db = 0; db < S::DB; ++db)
 #pragma unroll
-          for (int k = 0; k < 8; ++k)      // 16 keys per MMA: P block k/4, 32 bytes per step; V rows 16 k ..
-            umma_bf16(tmem_o + db * 64, umma_desc(base + S::OFF_P + (k >> 2) * S::TILE + (k & 3) * 32),
-                      umma_desc(base + S::OFF_V + s * S::KV_STAGE + db * S::TILE + k * 16 * 128), idesc_o,
-                      (j > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 8; ++k)      // 16 keys per MMA: 8 columns of P (two bf16 each); V rows 16 k ..
+            umma_bf16_ts(tmem_o + db * 64, tmem_p + k * 8,
+                         umma_desc(base + S::OFF_V + s * S::KV_STAGE + db * S::TILE + k * 16 * 128), idesc_o,
+                         (j > 0 || k > 0) ? 1u : 0u);
         umma_commit(smem_addr(&v_empty[s]));            // V of this stage is consumed
         umma_commit(smem_addr(&o_ready));               // O holds tiles 0 .. j, P may be overwritten
         if (j + NB < n_tiles) ok = issue_s(j + NB);
@@ -234,7 +231,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int qpos = pos_first + tl;
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
     const uint32_t tmem_s0 = tmem_base + S::COL_S + lane_addr, tmem_o = tmem_base + S::COL_O + lane_addr;
-    unsigned char* p_row = base_ptr + S::OFF_P + row * 128;
+    const uint32_t tmem_p = tmem_base + S::COL_P + lane_addr;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
@@ -251,22 +248,24 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int lo = window > 0 ? max(0, qpos - window + 1) : 0;
       const unsigned span = hi >= lo ? (unsigned)(hi - lo) : 0u;
       const int lo_eff = hi >= lo ? lo : 0x7fffff00;     // no key passes when the row sees nothing
-      // pass 1: this row's maximum over the tile
+      // the row's 128 scores come out of tensor memory once and stay in registers
+      float sv[BN];
+#pragma unroll
+      for (int c = 0; c < BN; c += 32) tmem_ld32_nowait(tmem_s + (uint32_t)c, *reinterpret_cast<float(*)[32]>(&sv[c]));
+      tmem_wait_ld();
+#pragma unroll
+      for (int c = 0; c < BN; c += 16) tmem_ld_fence16(&sv[c]);
       float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        float v[32];
-        tmem_ld32(tmem_s + (uint32_t)c, v);
-        if (need_mask) {
+      if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const bool seen = (unsigned)(kv0 + c + i - lo_eff) <= span;
-            mx = fmaxf(mx, seen ? v[i] : -INFINITY);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+        for (int i = 0; i < BN; ++i) {
+          const bool seen = (unsigned)(kv0 + i - lo_eff) <= span;
+          sv[i] = seen ? sv[i] : -INFINITY;
+          mx = fmaxf(mx, sv[i]);
         }
+      } else {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) mx = fmaxf(mx, sv[i]);
       }
       const float m_new = fmaxf(m, mx);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
@@ -290,56 +289,40 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       m = m_new;
       l *= corr;
-      // pass 2: probabilities -> shared memory (bf16, the layout the second product reads)
-#pragma unroll 1
+      // probabilities -> tensor memory (bf16 pairs: the A operand of the second product); a hidden
+      // key has score -inf and so probability 0
+      float l0 = 0.f, l1 = 0.f;
+#pragma unroll
       for (int c = 0; c < BN; c += 32) {
-        float v[32];
-        tmem_ld32(tmem_s + (uint32_t)c, v);
         uint32_t packed[16];
-        if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const bool s0 = (unsigned)(kv0 + c + i - lo_eff) <= span, s1 = (unsigned)(kv0 + c + i + 1 - lo_eff) <= span;
-            const float p0 = s0 ? fast_exp2(fmaf(v[i], scale_log2, neg_mc)) : 0.f;
-            const float p1 = s1 ? fast_exp2(fmaf(v[i + 1], scale_log2, neg_mc)) : 0.f;
-            l += p0 + p1;
-            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = fast_exp2(fmaf(v[i], scale_log2, neg_mc));
-            const float p1 = fast_exp2(fmaf(v[i + 1], scale_log2, neg_mc));
-            l += p0 + p1;
-            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
-          }
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = fast_exp2(fmaf(sv[c + i], scale_log2, neg_mc));
+          const float p1 = fast_exp2(fmaf(sv[c + i + 1], scale_log2, neg_mc));
+          l0 += p0;
+          l1 += p1;
+          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
         }
-        // keys c .. c+31 = four 16-byte pieces of block c/64; piece index XOR (row % 8)
-        unsigned char* blk = p_row + (c >> 6) * S::TILE;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int piece = ((c & 63) >> 3) + q4;
-          *reinterpret_cast<uint4*>(blk + ((piece ^ (row & 7)) << 4)) =
-              make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-        }
+        tmem_st16_b32(tmem_p + (uint32_t)(c >> 1), packed);   // keys c .. c+31 = 16 columns of two bf16
       }
+      l += l0 + l1;
+      tmem_wait_st();
       // value rows of keys the request does not hold (a page's unwritten tail, a page that was not
       // read): zero them, so that probability 0 times a stale value never reaches the output
       if (kv0 + BN - 1 > pos_last || kv0 < kv_lo) {
-        mbar_wait(smem_addr(&v_full[j % NB]), (uint32_t)(j / NB) & 1u, status, &abort_flag);
+        mbar_wait(smem_addr(&v_full[j % KS]), (uint32_t)(j / KS) & 1u, status, &abort_flag);
         const int key = kv0 + row;                       // thread <-> key row of the V tile
         if (key > pos_last || key < kv_lo) {
           for (int db = 0; db < S::DB; ++db) {
             uint4* vrow =
-                reinterpret_cast<uint4*>(base_ptr + S::OFF_V + (j % NB) * S::KV_STAGE + db * S::TILE + row * 128);
+                reinterpret_cast<uint4*>(base_ptr + S::OFF_V + (j % KS) * S::KV_STAGE + db * S::TILE + row * 128);
 #pragma unroll
             for (int i = 0; i < 8; ++i) vrow[i] = make_uint4(0u, 0u, 0u, 0u);
           }
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // these writes -> visible to the tensor core
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P and V writes -> visible to the tensor core
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_addr(&p_full));

@@ -88,9 +88,12 @@ def _writable_dir() -> Path:
     for d in _build_dirs():
         try:
             d.mkdir(parents=True, exist_ok=True)
-            probe = d / f".probe_{os.getpid()}"
+            probe = d / f".probe_{os.getpid()}_{threading.get_ident()}"       # modules are built in parallel
             probe.write_bytes(b"")
-            probe.unlink()
+            try:
+                probe.unlink()
+            except FileNotFoundError:
+                pass
             return d
         except OSError:
             continue
