@@ -5,7 +5,6 @@ the same command under ``ncu`` gives the profiles kept under ``profiles/``."""
 
 from __future__ import annotations
 
-import json
 import math
 
 import torch

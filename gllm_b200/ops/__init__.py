@@ -12,7 +12,6 @@ rotary frequencies, softmax statistics and logits are fp32 in both.
 
 from __future__ import annotations
 
-import ctypes
 from ctypes import c_float, c_int, c_int64, c_void_p
 
 import torch
@@ -85,9 +84,6 @@ def _fn(module: str, name: str):
         return _functions[name]
     except KeyError:
         raise ExtensionError(f"kernel module {module!r} exports no symbol {name!r}") from None
-
-
-_cudart_error_string = None
 
 
 def _error_string(code: int) -> str:
