@@ -471,7 +471,7 @@ GLLM_API int gllm_gemm_bf16_splits(int M, int N, int K) {
   // k-blocks long, none empty, the partial tiles a small part of the weight's bytes
   int best = 1;
   for (int s = 2; s <= 16; ++s) {
-    if (tiles * s > 148 || s > K / (8 * bucket) || num_kb / s < 2) break;
+    if (tiles * s > 148 || s > K / (4 * bucket) || num_kb / s < 2) break;
     const int per = (num_kb + s - 1) / s;
     if (per * (s - 1) < num_kb) best = s;        // the last split is not empty
   }
