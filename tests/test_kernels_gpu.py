@@ -236,6 +236,32 @@ def test_attention_decode_split_kv(ops, hq, hkv, d, bs, window, kernel):
         torch.testing.assert_close(got, want, **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("kernel", ["split", "stream"])
+def test_attention_decode_long_context(ops, kernel):
+    """Three requests of 20,000, 4,097 and 130 cached tokens in one call (dozens of chunks, spans the
+    stream kernel walks through several times per CTA, a window on top), far keys carrying the weight."""
+    from gllm_b200.ops import attention_bf16
+
+    g = torch.Generator().manual_seed(16)
+    hq, hkv, d, bs = 8, 2, 64, 16
+    lens = [20000, 4097, 130]
+    for window in (None, 5000):
+        pool, table, ks, vs, qs, pos, rows = _paged_case(g, torch.bfloat16, lens, hq, hkv, d, bs, [1] * len(lens))
+        n = pos.numel()
+        qkv = torch.zeros(n, (hq + 2 * hkv) * d, dtype=torch.bfloat16)
+        qkv[:, : hq * d] = torch.cat(qs).reshape(n, hq * d)
+        scale = 1.0 / math.sqrt(d)
+        out = torch.full((n, hq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+        attention_bf16.decode_attention(qkv.cuda(), qkv.shape[1], pool.cuda(), table.cuda(), pos.cuda(), rows.cuda(),
+                                        hq, scale, window or 0, max(lens), None, out, kernel=kernel)
+        ops.check_status()
+        for r in range(n):
+            want = _plain_attn(qs[r], ks[r], vs[r], pos[r:r + 1].long(), window, scale)
+            got = out[r].double().cpu().view(1, hq, d)
+            assert not got.isnan().any()
+            torch.testing.assert_close(got, want, **tol(torch.bfloat16))
+
+
 def test_attention_mixed_batch_uses_both_kernels(ops):
     """Portions first, single tokens after, as the step function lays a batch out."""
     from types import SimpleNamespace
@@ -307,6 +333,40 @@ def test_attention_prefill_tensor_cores(ops, hq, hkv, d, bs, window, kernel):
         assert not got.isnan().any(), r
         torch.testing.assert_close(got, want, **tol(torch.bfloat16))
         off += nq
+
+
+@pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05"])
+@pytest.mark.parametrize("d", [64, 128])
+def test_attention_prefill_long_context(ops, kernel, d):
+    """Portions late in long requests: 700 tokens after 9,000 cached ones (dozens of key tiles before
+    the diagonal, with and without a window) beside a whole prompt of 1,100 tokens."""
+    from gllm_b200.ops import attention_bf16
+
+    g = torch.Generator().manual_seed(17)
+    hq, hkv, bs = 8, 2, 16
+    lens, q_counts = [9700, 1100], [700, 1100]
+    for window in (None, 3000):
+        pool, table, ks, vs, qs, pos, rows = _paged_case(g, torch.bfloat16, lens, hq, hkv, d, bs, q_counts)
+        pool = torch.cat([pool, torch.zeros(1, *pool.shape[1:], dtype=pool.dtype)], 0)
+        n = pos.numel()
+        qkv = torch.zeros(n, (hq + 2 * hkv) * d, dtype=torch.bfloat16)
+        qkv[:, : hq * d] = torch.cat(qs).reshape(n, hq * d)
+        scale = 1.0 / math.sqrt(d)
+        cu = torch.tensor([0] + list(torch.tensor(q_counts).cumsum(0)), dtype=torch.int32).cuda()
+        ctx = torch.tensor([a - b for a, b in zip(lens, q_counts)], dtype=torch.int32).cuda()
+        slots = torch.arange(1, len(lens) + 1, dtype=torch.int32).cuda()
+        out = torch.full((n, hq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+        run = attention_bf16.prefill_attention if kernel == "mma_sync" else attention_bf16.prefill_attention_tmem
+        run(qkv.cuda(), qkv.shape[1], pool.cuda(), table.cuda(), cu, ctx, slots, len(lens), max(q_counts), hq, scale,
+            window or 0, out)
+        ops.check_status()
+        off = 0
+        for r, nq in enumerate(q_counts):
+            want = _plain_attn(qs[r], ks[r], vs[r], pos[off:off + nq].long(), window, scale)
+            got = out[off:off + nq].double().cpu().view(nq, hq, d)
+            assert not got.isnan().any(), r
+            torch.testing.assert_close(got, want, **tol(torch.bfloat16))
+            off += nq
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 311, 72), (8, 3072, 2048), (7, 96, 160), (13, 2048, 8192), (33, 1000, 520),
