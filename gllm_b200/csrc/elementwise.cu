@@ -180,38 +180,40 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ branch, const float* __
   }
 }
 
-// The same with 8 columns per access and the row kept in registers (up to MAXC chunks of 8 per thread).
+// The same with 8 columns per access and the row kept in registers (up to MAXC chunks of 8 per thread;
+// the launcher picks the smallest MAXC that holds a row, since registers decide how many rows an SM has
+// in flight).  The branch is a tensor here, never unsummed splits.  The norm's weight does not depend on
+// the kernel before this one and is fetched before the dependency wait.
 template <typename T, int MAXC>
-__global__ void add_rmsnorm_wide_kernel(const T* __restrict__ branch, const float* __restrict__ parts, int n_parts,
-                                        int64_t part_stride, float* __restrict__ resid,
+__global__ void add_rmsnorm_wide_kernel(const T* __restrict__ branch, float* __restrict__ resid,
                                         const float* __restrict__ weight, T* __restrict__ out,
                                         const int* __restrict__ rows, int n_rows, int hidden, float eps,
                                         int unit_offset) {
   __shared__ float scratch[32];
   pdl_trigger();
-  pdl_wait();
   const int i = blockIdx.x;
-  const size_t r = rows ? (size_t)rows[i] : (size_t)i;
-  float* res = resid + r * hidden;
   float x[MAXC][8], w[MAXC][8];
+#pragma unroll
+  for (int k = 0; k < MAXC; ++k) {
+    const int c = (threadIdx.x + k * blockDim.x) * 8;
+    if (c < hidden) Vec8<float>::load(weight + c, w[k]);
+  }
+  const size_t r = rows ? (size_t)rows[i] : (size_t)i;   // a step input
+  pdl_wait();
+  float* res = resid + r * hidden;
   float ss = 0.f;
 #pragma unroll
   for (int k = 0; k < MAXC; ++k) {
     const int c = (threadIdx.x + k * blockDim.x) * 8;
     if (c >= hidden) break;
     Vec8<float>::load(res + c, x[k]);
-    Vec8<float>::load(weight + c, w[k]);
-    if (parts) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e)
-        x[k][e] += to_float(from_float<T>(sum_parts16(parts + r * hidden + c + e, n_parts, part_stride)));
-    } else if (branch) {
+    if (branch) {
       float b[8];
       Vec8<T>::load(branch + r * hidden + c, b);
 #pragma unroll
       for (int e = 0; e < 8; ++e) x[k][e] += b[e];
+      if (!rows) Vec8<float>::store(res + c, x[k]);
     }
-    if ((branch || parts) && !rows) Vec8<float>::store(res + c, x[k]);
 #pragma unroll
     for (int e = 0; e < 8; ++e) ss += x[k][e] * x[k][e];
   }
@@ -297,9 +299,17 @@ static int add_rmsnorm_launch(const T* branch, const float* parts, int n_parts, 
       (!branch || aligned16(branch))) {
     const int chunks = hidden / 8;
     const int wide_threads = chunks >= 256 ? 256 : (chunks >= 128 ? 128 : (chunks >= 64 ? 64 : 32));
+    // as few chunks per thread as the row needs: the kernel keeps them in registers, and the registers
+    // decide how many rows an SM works on at a time
+    if (chunks <= wide_threads)
+      return gllm_launch(add_rmsnorm_wide_kernel<T, 1>, dim3(n_rows), dim3(wide_threads), 0, stream, branch, resid,
+                         weight, out, rows, n_rows, hidden, eps, unit_offset);
+    if (chunks <= wide_threads * 2)
+      return gllm_launch(add_rmsnorm_wide_kernel<T, 2>, dim3(n_rows), dim3(wide_threads), 0, stream, branch, resid,
+                         weight, out, rows, n_rows, hidden, eps, unit_offset);
     if (chunks <= wide_threads * 4)
-      return gllm_launch(add_rmsnorm_wide_kernel<T, 4>, dim3(n_rows), dim3(wide_threads), 0, stream, branch, parts,
-                         n_parts, part_stride, resid, weight, out, rows, n_rows, hidden, eps, unit_offset);
+      return gllm_launch(add_rmsnorm_wide_kernel<T, 4>, dim3(n_rows), dim3(wide_threads), 0, stream, branch, resid,
+                         weight, out, rows, n_rows, hidden, eps, unit_offset);
   }
   if (parts && !branch && n_rows <= 64 && hidden >= 1024 && hidden <= 8 * 4 * 256) {
     return gllm_launch_cluster(add_rmsnorm_cluster_kernel<T>, dim3(8, n_rows), dim3(256), 0, stream, 8u, parts,
@@ -495,21 +505,20 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const float* __restrict__
   }
 }
 
-// The same for the common case (pairs are the two halves, rotary_dim and head size multiples
-// of 16): one thread owns 8 consecutive pairs, takes sine and cosine once and reuses them for
-// every head, moves 16 bytes at a time and writes the rotated k and the v straight to the cache.
+// The same for the common case (a summed projection; pairs are the two halves; rotary_dim and head size
+// multiples of 16): one thread owns 8 consecutive pairs, takes sine and cosine once and reuses them for
+// every head, moves 16 bytes at a time and writes the rotated k and the v straight to the cache.  The
+// position, the cache slot and so sine and cosine are step inputs: they are ready before the
+// dependency wait returns.  A thread's heads are all loaded before the first is stored.
 template <typename T>
-__global__ void rope_store_wide_kernel(T* __restrict__ qkv, const float* __restrict__ parts, int n_parts,
-                                       int64_t part_stride, const int* __restrict__ positions,
+__global__ void rope_store_wide_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
                                        const float* __restrict__ inv_freq, const int* __restrict__ slot_mapping,
                                        T* __restrict__ cache, int n_tokens, int hq, int hkv, int d, int rotary_dim,
                                        int block_size, int num_pages, int* __restrict__ status) {
   pdl_trigger();
-  pdl_wait();
   const int n = blockIdx.x;
   const int width = (hq + 2 * hkv) * d;
   T* row = qkv + (size_t)n * width;
-  const float* prow = parts ? parts + (size_t)n * width : nullptr;
   const int half = rotary_dim / 2;
   // where this token's k and v go
   int64_t cache_base = -1;
@@ -525,64 +534,70 @@ __global__ void rope_store_wide_kernel(T* __restrict__ qkv, const float* __restr
     }
   }
   const int64_t head_stride = (int64_t)block_size * d, v_plane = (int64_t)hkv * block_size * d;
-  auto load8 = [&](int col, float* v) {
-    if (prow) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] = to_float(from_float<T>(sum_parts16(prow + col + e, n_parts, part_stride)));
-    } else {
-      Vec8<T>::load(row + col, v);
-    }
-  };
-  // rotated part of q and k heads: (head, chunk of 8 pairs)
   const int chunks = inv_freq ? half / 8 : 0;
+  const int my_chunk = chunks > 0 ? threadIdx.x % chunks : 0;
+  float sn[8], cs[8];
   if (chunks > 0) {
-    const int my_chunk = threadIdx.x % chunks;
     const float pos = (float)positions[n];
-    float sn[8], cs[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) sincosf(pos * inv_freq[my_chunk * 8 + e], &sn[e], &cs[e]);
-    for (int h = threadIdx.x / chunks; h < hq + hkv; h += blockDim.x / chunks) {
+  }
+  pdl_wait();
+  // rotated part of q and k heads: (head, chunk of 8 pairs), two heads per turn
+  if (chunks > 0) {
+    const int step = blockDim.x / chunks;
+    for (int h = threadIdx.x / chunks; h < hq + hkv; h += 2 * step) {
+      const int h2 = h + step;
+      const bool two = h2 < hq + hkv;
       const int c0 = h * d + my_chunk * 8, c1 = c0 + half;
-      float a[8], b[8], ra[8], rb[8];
-      load8(c0, a);
-      load8(c1, b);
+      const int e0 = h2 * d + my_chunk * 8, e1 = e0 + half;
+      float a[8], b[8], a2[8], b2[8];
+      Vec8<T>::load(row + c0, a);
+      Vec8<T>::load(row + c1, b);
+      if (two) {
+        Vec8<T>::load(row + e0, a2);
+        Vec8<T>::load(row + e1, b2);
+      }
+      auto finish = [&](int hh, int x0, int x1, float* u, float* v) {
+        float ra[8], rb[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        ra[e] = a[e] * cs[e] - b[e] * sn[e];
-        rb[e] = a[e] * sn[e] + b[e] * cs[e];
-      }
-      Vec8<T>::store(row + c0, ra);
-      Vec8<T>::store(row + c1, rb);
-      if (h >= hq && cache_base >= 0) {
-        T* kdst = cache + cache_base + (int64_t)(h - hq) * head_stride;
-        Vec8<T>::store(kdst + my_chunk * 8, ra);
-        Vec8<T>::store(kdst + half + my_chunk * 8, rb);
-      }
+        for (int e = 0; e < 8; ++e) {
+          ra[e] = u[e] * cs[e] - v[e] * sn[e];
+          rb[e] = u[e] * sn[e] + v[e] * cs[e];
+        }
+        Vec8<T>::store(row + x0, ra);
+        Vec8<T>::store(row + x1, rb);
+        if (hh >= hq && cache_base >= 0) {
+          T* kdst = cache + cache_base + (int64_t)(hh - hq) * head_stride;
+          Vec8<T>::store(kdst + my_chunk * 8, ra);
+          Vec8<T>::store(kdst + half + my_chunk * 8, rb);
+        }
+      };
+      finish(h, c0, c1, a, b);
+      if (two) finish(h2, e0, e1, a2, b2);
     }
   }
-  // everything that is not rotated: the tail of q and k heads past rotary_dim, and v
+  // everything that is not rotated and has to move: the tail of k heads past rotary_dim, and v, to the cache
+  if (cache_base < 0) return;
   const int rot = chunks > 0 ? rotary_dim : 0;
   const int tail_chunks = (d - rot) / 8;
   const int v_chunks = d / 8;
-  const int plain_items = (hq + hkv) * tail_chunks + hkv * v_chunks;
+  const int plain_items = hkv * tail_chunks + hkv * v_chunks;
   for (int item = threadIdx.x; item < plain_items; item += blockDim.x) {
     int h, col_in_head;
-    if (item < (hq + hkv) * tail_chunks) {
-      h = item / tail_chunks;
-      col_in_head = rot + (item - h * tail_chunks) * 8;
+    if (item < hkv * tail_chunks) {
+      h = hq + item / tail_chunks;
+      col_in_head = rot + (item % tail_chunks) * 8;
     } else {
-      const int j = item - (hq + hkv) * tail_chunks;
+      const int j = item - hkv * tail_chunks;
       h = hq + hkv + j / v_chunks;
       col_in_head = (j % v_chunks) * 8;
     }
     float v[8];
-    load8(h * d + col_in_head, v);
-    if (prow) Vec8<T>::store(row + h * d + col_in_head, v);
-    if (h >= hq && cache_base >= 0) {
-      const bool is_v = h >= hq + hkv;
-      const int kvh = is_v ? h - hq - hkv : h - hq;
-      Vec8<T>::store(cache + cache_base + (is_v ? v_plane : 0) + (int64_t)kvh * head_stride + col_in_head, v);
-    }
+    Vec8<T>::load(row + h * d + col_in_head, v);
+    const bool is_v = h >= hq + hkv;
+    const int kvh = is_v ? h - hq - hkv : h - hq;
+    Vec8<T>::store(cache + cache_base + (is_v ? v_plane : 0) + (int64_t)kvh * head_stride + col_in_head, v);
   }
 }
 
@@ -659,9 +674,8 @@ static int rope_store_launch(T* qkv, const float* parts, int n_parts, int64_t pa
   if (!parts && !interleaved && d % 8 == 0 && eff_rot % 16 == 0 && aligned16(qkv) &&
       (!slot_mapping || aligned16(cache)) &&
       (eff_rot == 0 || 128 % (eff_rot / 16) == 0)) {
-    return gllm_launch(rope_store_wide_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, qkv, parts, n_parts,
-                       part_stride, positions, inv_freq, slot_mapping, cache, n_tokens, hq, hkv, d, rotary_dim,
-                       block_size, num_pages, status);
+    return gllm_launch(rope_store_wide_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, qkv, positions, inv_freq,
+                       slot_mapping, cache, n_tokens, hq, hkv, d, rotary_dim, block_size, num_pages, status);
   }
   if (parts && n_tokens <= 64 && d % 2 == 0) {
     const int items = (hq + 2 * hkv) * (d / 2);
