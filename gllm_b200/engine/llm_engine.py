@@ -81,7 +81,8 @@ class LLMEngine(LLMEngineBase):
             device=dev,
         )
         self.runner = StepRunner(self.model, self.cache, gen_params.max_num_batched_tokens,
-                                 cuda_graphs=gen_params.cuda_graphs)
+                                 cuda_graphs=gen_params.cuda_graphs,
+                                 prefill_graph_tokens=(gen_params.prefill_chunk,))
         self.scheduler = Scheduler(gen_params, self.cache)
         self.sampler = Sampler(dev)
         self.request_queue: queue.Queue = queue.Queue()

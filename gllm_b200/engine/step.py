@@ -58,9 +58,12 @@ def _align4(n: int) -> int:
 class StepRunner:
     """Owns the staging buffers of the batch metadata and runs steps."""
 
-    def __init__(self, model, cache: CacheManager, max_tokens_per_step: int, cuda_graphs: bool = True):
+    def __init__(self, model, cache: CacheManager, max_tokens_per_step: int, cuda_graphs: bool = True,
+                 prefill_graph_tokens: tuple[int, ...] = ()):
         self.model = model
         self.cuda_graphs = bool(cuda_graphs) and torch.cuda.is_available()
+        # portion sizes (the scheduler's full prefill portion) whose steps are captured as graphs too
+        self.prefill_graph_tokens = tuple(int(n) for n in prefill_graph_tokens)
         self._graphs: dict = {}
         self._graph_pool = None
         self.graph_replays = 0
@@ -240,9 +243,18 @@ class StepRunner:
 
     # -------------------------------------------------------------------- run
     def _graph_key(self, entries: list[StepEntry]):
-        """(batch bucket, sequence bucket) when the step can run as a captured
-        graph: every entry brings one token and wants its logits."""
-        if not self.cuda_graphs or not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+        """The key of the captured graph this step can run as, or None.
+
+        ("decode", batch bucket, sequence bucket): every entry brings one token and wants its logits.
+        ("prefill", tokens, wanted rows): one request brings a portion of one of the sizes named in
+        ``prefill_graph_tokens``; what it has cached before does not enter the launch geometry of any
+        kernel (they read it from device memory), so one graph serves every context length."""
+        if not self.cuda_graphs:
+            return None
+        if (len(entries) == 1 and len(entries[0].tokens) in self.prefill_graph_tokens
+                and len(entries[0].tokens) > 1 and len(entries[0].tokens) <= self.max_tokens):
+            return ("prefill", len(entries[0].tokens), len(entries[0].want))
+        if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             return None
         bucket = 1
         while bucket < len(entries):
@@ -257,7 +269,7 @@ class StepRunner:
         seq_bucket = 1024
         while seq_bucket < longest:
             seq_bucket *= 2
-        return bucket, min(seq_bucket, max(self.cache.max_seq_len, longest))
+        return ("decode", bucket, min(seq_bucket, max(self.cache.max_seq_len, longest)))
 
     def run(self, entries: list[StepEntry], check: bool = True, greedy: bool = False) -> torch.Tensor:
         """Run one step; returns fp32 logits ``[wanted, vocab]`` on the device,
@@ -267,7 +279,8 @@ class StepRunner:
 
         A step in which every request brings a single token runs as a CUDA
         graph captured once per (batch bucket, sequence bucket): same kernels,
-        same buffers, one launch."""
+        same buffers, one launch.  So does a step that is one full prefill
+        portion of one request (see ``_graph_key``)."""
         wanted = sum(len(e.want) for e in entries)
         key = self._graph_key(entries)
         self.last_argmax = None
@@ -277,9 +290,11 @@ class StepRunner:
             if greedy and wanted:
                 ops.argmax(logits, out=self.sampled, scatter_index=self._row_slots)
         else:
-            bucket, seq_bucket = key
-            key = (bucket, seq_bucket, bool(greedy))
-            tokens, ctx, rows = self.build(entries, pad_to=bucket, seq_bucket=seq_bucket)
+            if key[0] == "decode":
+                tokens, ctx, rows = self.build(entries, pad_to=key[1], seq_bucket=key[2])
+            else:
+                tokens, ctx, rows = self.build(entries)
+            key = key + (bool(greedy),)
             record = self._graphs.get(key)
             if record is None:
                 # first time: run it plainly (this is the step's result), then capture for later

@@ -59,6 +59,31 @@ def test_greedy_generation_through_the_entry_point(name, dtype, tmp_path):
             assert engine.generate([req])[0].token_ids == r.token_ids
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_full_prefill_portions_replay_a_graph(dtype, tmp_path):
+    """A prompt of 150 tokens fed in portions of 32: the first full portion is run and captured, the
+    next three replay the graph over a growing context; the tokens are the plain implementation's."""
+    from gllm_b200 import GenerationRequest, GeneratorParams, LLMEngine
+
+    folder = write_tiny("D", str(tmp_path / "m"), sharp=(dtype == "float32"))
+    cfg, weights = read_raw(folder, round_to_bf16=(dtype == "bfloat16"))
+    g = torch.Generator().manual_seed(14)
+    prompt = torch.randint(0, cfg["vocab_size"], (150,), generator=g).tolist()
+    params = GeneratorParams(block_size=16, max_batch_size=2, max_seq_len=256, model_dtype=dtype, prefill_chunk=32)
+    engine = LLMEngine(folder, params, device="cuda:0")
+    before = engine.runner.graph_replays
+    out = engine.generate([GenerationRequest(prompt_token_ids=prompt, max_new_tokens=8, temperature=0.0,
+                                             ignore_eos=True)])[0]
+    assert any(k[0] == "prefill" and k[1] == 32 for k in engine.runner._graphs)
+    assert engine.runner.graph_replays - before >= 3
+    plain_greedy_check(cfg, weights, prompt, out.token_ids, 1e-5 if dtype == "float32" else 0.05)
+    # a second prompt of another length reuses the graph from its first portion on
+    prompt2 = torch.randint(0, cfg["vocab_size"], (70,), generator=g).tolist()
+    out2 = engine.generate([GenerationRequest(prompt_token_ids=prompt2, max_new_tokens=4, temperature=0.0,
+                                              ignore_eos=True)])[0]
+    plain_greedy_check(cfg, weights, prompt2, out2.token_ids, 1e-5 if dtype == "float32" else 0.05)
+
+
 def test_long_decoding_and_first_tokens(tmp_path):
     from gllm_b200 import GenerationRequest, GeneratorParams, LLMEngine
 
