@@ -13,9 +13,10 @@
 //   warp 1 (one thread): S = Q K^T into tensor memory (128 x 128 fp32), later O += P V (128 x D).
 //           Head size 128: two score buffers, the scores of the next tile are computed while this one
 //           is exponentiated.  Head size 64: one buffer, and two CTAs per SM that fill one another's gaps;
-//   warps 2-5 (one thread per row): read S from tensor memory, mask, running maximum and sum in
-//           fp32, rescale O in tensor memory when the maximum moved, write P (bf16) back into tensor
-//           memory, from where the second product takes it as its A operand; at the end O / sum -> global.
+//   warps 2-9 (two threads per row, each with half of a tile's keys): read S from tensor memory, mask,
+//           running maximum and sum in fp32, rescale O in tensor memory when the maximum moved, write
+//           P (bf16) back into tensor memory, from where the second product takes it as its A
+//           operand; at the end O / sum -> global.
 //
 // V is used as it lies in the cache ([key][dim], i.e. the "MN-major" operand of the second
 // product); nothing is transposed or gathered.  Keys outside a row's view get probability 0 and the
@@ -25,7 +26,7 @@
 #include "umma_utils.cuh"
 
 namespace {
-constexpr int BM = 128, BN = 128, THREADS = 192;
+constexpr int BM = 128, BN = 128, THREADS = 320;       // TMA warp, MMA warp, eight softmax warps
 
 // 2^x in one instruction (ex2.approx: about 2 ulp; -inf gives 0)
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -69,6 +70,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   __shared__ __align__(8) uint64_t q_full, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full[2], p_full, o_ready;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
+  __shared__ float row_max[2][BM];                      // the two halves of a row exchange their maxima here
   pdl_trigger();
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -92,7 +94,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       mbar_init(smem_addr(&v_empty[s]), 1);
       mbar_init(smem_addr(&s_full[s]), 1);
     }
-    mbar_init(smem_addr(&p_full), 4);                   // one arrival per softmax warp
+    mbar_init(smem_addr(&p_full), 8);                   // one arrival per softmax warp
     mbar_init(smem_addr(&o_ready), 1);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -224,49 +226,57 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
   } else if (active && warp >= 2) {
     // ------------------------------------------------- softmax, correction, epilogue
+    // Two threads per row: warps 2-5 take the keys 0 .. 63 of a tile (and the lower half of the output
+    // columns), warps 6-9 the keys 64 .. 127 (and the upper half).  A warp reads the tensor-memory
+    // lanes 32 * (warp % 4) ..: warps w and w + 4 work on the same rows and exchange their rows' maxima
+    // through shared memory.
     const int quarter = warp & 3;
+    const int hsel = (warp - 2) >> 2;                     // which half of the keys and of the output columns
     const int row = quarter * 32 + lane;                 // row of the tile = TMEM lane
     const int tl = row / gp, g = row - tl * gp;
     const bool row_ok = tl < t_count;
     const int qpos = pos_first + tl;
+    constexpr int HK = BN / 2, HD = D / 2;               // keys and output columns per thread
     const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-    const uint32_t tmem_s0 = tmem_base + S::COL_S + lane_addr, tmem_o = tmem_base + S::COL_O + lane_addr;
-    const uint32_t tmem_p = tmem_base + S::COL_P + lane_addr;
+    const uint32_t tmem_s0 = tmem_base + S::COL_S + lane_addr + (uint32_t)(hsel * HK);
+    const uint32_t tmem_o = tmem_base + S::COL_O + lane_addr + (uint32_t)(hsel * HD);
+    const uint32_t tmem_p = tmem_base + S::COL_P + lane_addr + (uint32_t)(hsel * HK / 2);
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      const int kv0 = (tile_first + j) * BN;
+      const int kv0 = (tile_first + j) * BN + hsel * HK;  // this thread's first key of the tile
       const uint32_t tmem_s = tmem_s0 + (uint32_t)((j % NB) * BN);
       mbar_wait(smem_addr(&s_full[j % NB]), (uint32_t)(j / NB) & 1u, status, &abort_flag);
-      asm volatile("bar.sync 1, 128;" ::: "memory");     // the four warps go on together
+      asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight warps go on together
       if (abort_flag) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // keys this row sees in the tile: lo <= key <= hi (hi < lo: none).  A tile that every row of the
       // CTA sees whole takes the plain path.
-      const bool need_mask = (kv0 + BN - 1 > pos_first) || window > 0 || t_count < qt;
+      const bool need_mask = ((tile_first + j) * BN + BN - 1 > pos_first) || window > 0 || t_count < qt;
       const int hi = row_ok ? qpos : -1;
       const int lo = window > 0 ? max(0, qpos - window + 1) : 0;
       const unsigned span = hi >= lo ? (unsigned)(hi - lo) : 0u;
       const int lo_eff = hi >= lo ? lo : 0x7fffff00;     // no key passes when the row sees nothing
-      // the row's 128 scores come out of tensor memory once and stay in registers
-      float sv[BN];
-#pragma unroll
-      for (int c = 0; c < BN; c += 32) tmem_ld32_nowait(tmem_s + (uint32_t)c, *reinterpret_cast<float(*)[32]>(&sv[c]));
-      tmem_wait_ld();
-#pragma unroll
-      for (int c = 0; c < BN; c += 16) tmem_ld_fence16(&sv[c]);
+      // pass 1: the maximum of this thread's half of the row, then of the row
       float mx = -INFINITY;
-      if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < BN; ++i) {
-          const bool seen = (unsigned)(kv0 + i - lo_eff) <= span;
-          sv[i] = seen ? sv[i] : -INFINITY;
-          mx = fmaxf(mx, sv[i]);
+      for (int c = 0; c < HK; c += 32) {
+        float v[32];
+        tmem_ld32(tmem_s + (uint32_t)c, v);
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const bool seen = (unsigned)(kv0 + c + i - lo_eff) <= span;
+            mx = fmaxf(mx, seen ? v[i] : -INFINITY);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
         }
-      } else {
-#pragma unroll
-        for (int i = 0; i < BN; ++i) mx = fmaxf(mx, sv[i]);
       }
+      row_max[hsel][row] = mx;
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      mx = fmaxf(mx, row_max[hsel ^ 1][row]);
       const float m_new = fmaxf(m, mx);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       const float corr = m == -INFINITY ? 0.f : fast_exp2((m - m_use) * scale_log2);
@@ -277,8 +287,8 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         mbar_wait(smem_addr(&o_ready), (uint32_t)(j - 1) & 1u, status, &abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (__any_sync(0xffffffffu, corr != 1.f)) {
-#pragma unroll 1
-          for (int c = 0; c < D; c += 32) {
+#pragma unroll
+          for (int c = 0; c < HD; c += 32) {
             float v[32];
             tmem_ld32(tmem_o + (uint32_t)c, v);
 #pragma unroll
@@ -289,20 +299,34 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       m = m_new;
       l *= corr;
-      // probabilities -> tensor memory (bf16 pairs: the A operand of the second product); a hidden
-      // key has score -inf and so probability 0
+      // pass 2: probabilities -> tensor memory (bf16 pairs: the A operand of the second product)
       float l0 = 0.f, l1 = 0.f;
 #pragma unroll
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = 0; c < HK; c += 32) {
+        float v[32];
+        tmem_ld32(tmem_s + (uint32_t)c, v);
         uint32_t packed[16];
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float p0 = fast_exp2(fmaf(sv[c + i], scale_log2, neg_mc));
-          const float p1 = fast_exp2(fmaf(sv[c + i + 1], scale_log2, neg_mc));
-          l0 += p0;
-          l1 += p1;
-          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+          for (int i = 0; i < 32; i += 2) {
+            const bool s0 = (unsigned)(kv0 + c + i - lo_eff) <= span, s1 = (unsigned)(kv0 + c + i + 1 - lo_eff) <= span;
+            const float p0 = s0 ? fast_exp2(fmaf(v[i], scale_log2, neg_mc)) : 0.f;
+            const float p1 = s1 ? fast_exp2(fmaf(v[i + 1], scale_log2, neg_mc)) : 0.f;
+            l0 += p0;
+            l1 += p1;
+            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = fast_exp2(fmaf(v[i], scale_log2, neg_mc));
+            const float p1 = fast_exp2(fmaf(v[i + 1], scale_log2, neg_mc));
+            l0 += p0;
+            l1 += p1;
+            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+          }
         }
         tmem_st16_b32(tmem_p + (uint32_t)(c >> 1), packed);   // keys c .. c+31 = 16 columns of two bf16
       }
@@ -310,10 +334,11 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tmem_wait_st();
       // value rows of keys the request does not hold (a page's unwritten tail, a page that was not
       // read): zero them, so that probability 0 times a stale value never reaches the output
-      if (kv0 + BN - 1 > pos_last || kv0 < kv_lo) {
+      const int tile0 = (tile_first + j) * BN;
+      if (tile0 + BN - 1 > pos_last || tile0 < kv_lo) {
         mbar_wait(smem_addr(&v_full[j % KS]), (uint32_t)(j / KS) & 1u, status, &abort_flag);
-        const int key = kv0 + row;                       // thread <-> key row of the V tile
-        if (key > pos_last || key < kv_lo) {
+        const int key = tile0 + row;                     // thread <-> key row of the V tile (lower-half warps)
+        if (hsel == 0 && (key > pos_last || key < kv_lo)) {
           for (int db = 0; db < S::DB; ++db) {
             uint4* vrow =
                 reinterpret_cast<uint4*>(base_ptr + S::OFF_V + (j % KS) * S::KV_STAGE + db * S::TILE + row * 128);
@@ -327,16 +352,18 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_addr(&p_full));
     }
-    // ---- O / l -> global
+    // ---- O / l -> global: the row's sum is the two halves' sums
     if (ok && n_tiles > 0) {
       mbar_wait(smem_addr(&o_ready), (uint32_t)(n_tiles - 1) & 1u, status, &abort_flag);
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      row_max[hsel][row] = l;                            // (the exchange buffer is free: every maximum was read)
+      asm volatile("bar.sync 1, 256;" ::: "memory");
       if (!abort_flag) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
-        __nv_bfloat16* dst = out + (int64_t)(tok_begin + t0 + tl) * out_stride + (int64_t)(h0 + g) * D;
+        const float l_row = l + row_max[hsel ^ 1][row];
+        const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+        __nv_bfloat16* dst = out + (int64_t)(tok_begin + t0 + tl) * out_stride + (int64_t)(h0 + g) * D + hsel * HD;
 #pragma unroll 1
-        for (int c = 0; c < D; c += 32) {
+        for (int c = 0; c < HD; c += 32) {
           float v[32];
           tmem_ld32(tmem_o + (uint32_t)c, v);            // every lane takes part in the load
           if (row_ok) {
