@@ -182,10 +182,11 @@ __global__ void add_rmsnorm_kernel(const T* __restrict__ branch, const float* __
 
 // The same with 8 columns per access and the row kept in registers (up to MAXC chunks of 8 per thread;
 // the launcher picks the smallest MAXC that holds a row, since registers decide how many rows an SM has
-// in flight).  The branch is a tensor here, never unsummed splits.  The norm's weight does not depend on
+// in flight).  The norm's weight does not depend on
 // the kernel before this one and is fetched before the dependency wait.
-template <typename T, int MAXC>
-__global__ void add_rmsnorm_wide_kernel(const T* __restrict__ branch, float* __restrict__ resid,
+template <typename T, int MAXC, bool PARTS>
+__global__ void add_rmsnorm_wide_kernel(const T* __restrict__ branch, const float* __restrict__ parts, int n_parts,
+                                        int64_t part_stride, float* __restrict__ resid,
                                         const float* __restrict__ weight, T* __restrict__ out,
                                         const int* __restrict__ rows, int n_rows, int hidden, float eps,
                                         int unit_offset) {
@@ -207,7 +208,20 @@ __global__ void add_rmsnorm_wide_kernel(const T* __restrict__ branch, float* __r
     const int c = (threadIdx.x + k * blockDim.x) * 8;
     if (c >= hidden) break;
     Vec8<float>::load(res + c, x[k]);
-    if (branch) {
+    if (PARTS) {                                          // unsummed splits, 8 columns of a split per load
+      float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      const float* src = parts + r * hidden + c;
+#pragma unroll 4
+      for (int p = 0; p < n_parts; ++p) {
+        float t[8];
+        Vec8<float>::load(src + (int64_t)p * part_stride, t);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) b[e] += t[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[k][e] += to_float(from_float<T>(b[e]));   // rounded as the product would be
+      if (!rows) Vec8<float>::store(res + c, x[k]);
+    } else if (branch) {
       float b[8];
       Vec8<T>::load(branch + r * hidden + c, b);
 #pragma unroll
@@ -231,7 +245,7 @@ __global__ void add_rmsnorm_wide_kernel(const T* __restrict__ branch, float* __r
   }
 }
 
-// The same for a few rows whose branch arrives as unsummed splits (decoding): a cluster of blocks
+// The same for rows whose branch arrives as unsummed splits (decoding, short portions): a cluster of blocks
 // shares one row, each block sums, adds and squares its stretch of columns, the blocks exchange
 // their sums of squares through distributed shared memory (added in rank order) and each
 // normalises its own stretch.  A row of a handful of tokens is then read through many SMs' ports
@@ -294,22 +308,35 @@ static int add_rmsnorm_launch(const T* branch, const float* parts, int n_parts, 
                               int unit_offset, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (n_parts > 16) return (int)cudaErrorInvalidValue;
-  // unsummed splits: many loads per column, so spread a row over as many threads as there are columns
-  if (!parts && hidden % 8 == 0 && aligned16(resid) && aligned16(weight) && aligned16(out) &&
-      (!branch || aligned16(branch))) {
+  // few rows of unsummed splits: a cluster of blocks per row (below)
+  const bool few_rows_of_parts = parts && !branch && n_rows <= 64 && hidden >= 1024 && hidden <= 8 * 4 * 256;
+  if (!few_rows_of_parts && hidden % 8 == 0 && aligned16(resid) && aligned16(weight) && aligned16(out) &&
+      (!branch || aligned16(branch)) && (!parts || (aligned16(parts) && part_stride % 4 == 0))) {
     const int chunks = hidden / 8;
     const int wide_threads = chunks >= 256 ? 256 : (chunks >= 128 ? 128 : (chunks >= 64 ? 64 : 32));
     // as few chunks per thread as the row needs: the kernel keeps them in registers, and the registers
     // decide how many rows an SM works on at a time
     if (chunks <= wide_threads)
-      return gllm_launch(add_rmsnorm_wide_kernel<T, 1>, dim3(n_rows), dim3(wide_threads), 0, stream, branch, resid,
-                         weight, out, rows, n_rows, hidden, eps, unit_offset);
+      return parts ? gllm_launch(add_rmsnorm_wide_kernel<T, 1, true>, dim3(n_rows), dim3(wide_threads), 0, stream,
+                                 branch, parts, n_parts, part_stride, resid, weight, out, rows, n_rows, hidden, eps,
+                                 unit_offset)
+                   : gllm_launch(add_rmsnorm_wide_kernel<T, 1, false>, dim3(n_rows), dim3(wide_threads), 0, stream,
+                                 branch, parts, n_parts, part_stride, resid, weight, out, rows, n_rows, hidden, eps,
+                                 unit_offset);
     if (chunks <= wide_threads * 2)
-      return gllm_launch(add_rmsnorm_wide_kernel<T, 2>, dim3(n_rows), dim3(wide_threads), 0, stream, branch, resid,
-                         weight, out, rows, n_rows, hidden, eps, unit_offset);
+      return parts ? gllm_launch(add_rmsnorm_wide_kernel<T, 2, true>, dim3(n_rows), dim3(wide_threads), 0, stream,
+                                 branch, parts, n_parts, part_stride, resid, weight, out, rows, n_rows, hidden, eps,
+                                 unit_offset)
+                   : gllm_launch(add_rmsnorm_wide_kernel<T, 2, false>, dim3(n_rows), dim3(wide_threads), 0, stream,
+                                 branch, parts, n_parts, part_stride, resid, weight, out, rows, n_rows, hidden, eps,
+                                 unit_offset);
     if (chunks <= wide_threads * 4)
-      return gllm_launch(add_rmsnorm_wide_kernel<T, 4>, dim3(n_rows), dim3(wide_threads), 0, stream, branch, resid,
-                         weight, out, rows, n_rows, hidden, eps, unit_offset);
+      return parts ? gllm_launch(add_rmsnorm_wide_kernel<T, 4, true>, dim3(n_rows), dim3(wide_threads), 0, stream,
+                                 branch, parts, n_parts, part_stride, resid, weight, out, rows, n_rows, hidden, eps,
+                                 unit_offset)
+                   : gllm_launch(add_rmsnorm_wide_kernel<T, 4, false>, dim3(n_rows), dim3(wide_threads), 0, stream,
+                                 branch, parts, n_parts, part_stride, resid, weight, out, rows, n_rows, hidden, eps,
+                                 unit_offset);
   }
   if (parts && !branch && n_rows <= 64 && hidden >= 1024 && hidden <= 8 * 4 * 256) {
     return gllm_launch_cluster(add_rmsnorm_cluster_kernel<T>, dim3(8, n_rows), dim3(256), 0, stream, 8u, parts,
@@ -510,8 +537,9 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const float* __restrict__
 // every head, moves 16 bytes at a time and writes the rotated k and the v straight to the cache.  The
 // position, the cache slot and so sine and cosine are step inputs: they are ready before the
 // dependency wait returns.  A thread's heads are all loaded before the first is stored.
-template <typename T>
-__global__ void rope_store_wide_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+template <typename T, bool PARTS>
+__global__ void rope_store_wide_kernel(T* __restrict__ qkv, const float* __restrict__ parts, int n_parts,
+                                       int64_t part_stride, const int* __restrict__ positions,
                                        const float* __restrict__ inv_freq, const int* __restrict__ slot_mapping,
                                        T* __restrict__ cache, int n_tokens, int hq, int hkv, int d, int rotary_dim,
                                        int block_size, int num_pages, int* __restrict__ status) {
@@ -543,6 +571,26 @@ __global__ void rope_store_wide_kernel(T* __restrict__ qkv, const int* __restric
     for (int e = 0; e < 8; ++e) sincosf(pos * inv_freq[my_chunk * 8 + e], &sn[e], &cs[e]);
   }
   pdl_wait();
+  // 8 columns of this token: from qkv, or the sum of the unsummed splits (8 columns of a split per load,
+  // rounded to T as the product would have been)
+  const float* prow = PARTS ? parts + (size_t)n * width : nullptr;
+  auto load8 = [&](int col, float* v) {
+    if (PARTS) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = 0.f;
+#pragma unroll 4
+      for (int p = 0; p < n_parts; ++p) {
+        float t[8];
+        Vec8<float>::load(prow + col + (int64_t)p * part_stride, t);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += t[e];
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = to_float(from_float<T>(v[e]));
+    } else {
+      Vec8<T>::load(row + col, v);
+    }
+  };
   // rotated part of q and k heads: (head, chunk of 8 pairs), two heads per turn
   if (chunks > 0) {
     const int step = blockDim.x / chunks;
@@ -552,11 +600,11 @@ __global__ void rope_store_wide_kernel(T* __restrict__ qkv, const int* __restric
       const int c0 = h * d + my_chunk * 8, c1 = c0 + half;
       const int e0 = h2 * d + my_chunk * 8, e1 = e0 + half;
       float a[8], b[8], a2[8], b2[8];
-      Vec8<T>::load(row + c0, a);
-      Vec8<T>::load(row + c1, b);
+      load8(c0, a);
+      load8(c1, b);
       if (two) {
-        Vec8<T>::load(row + e0, a2);
-        Vec8<T>::load(row + e1, b2);
+        load8(e0, a2);
+        load8(e1, b2);
       }
       auto finish = [&](int hh, int x0, int x1, float* u, float* v) {
         float ra[8], rb[8];
@@ -577,31 +625,37 @@ __global__ void rope_store_wide_kernel(T* __restrict__ qkv, const int* __restric
       if (two) finish(h2, e0, e1, a2, b2);
     }
   }
-  // everything that is not rotated and has to move: the tail of k heads past rotary_dim, and v, to the cache
-  if (cache_base < 0) return;
+  // everything that is not rotated and has to move: the tail of k heads past rotary_dim, and v, to the
+  // cache; with unsummed splits also the tails of the q heads, and all of it into qkv
+  if (cache_base < 0 && !PARTS) return;
   const int rot = chunks > 0 ? rotary_dim : 0;
   const int tail_chunks = (d - rot) / 8;
   const int v_chunks = d / 8;
-  const int plain_items = hkv * tail_chunks + hkv * v_chunks;
+  const int first_head = PARTS ? 0 : hq;                // q tails only when they have to be summed
+  const int tail_heads = hq + hkv - first_head;
+  const int plain_items = tail_heads * tail_chunks + hkv * v_chunks;
   for (int item = threadIdx.x; item < plain_items; item += blockDim.x) {
     int h, col_in_head;
-    if (item < hkv * tail_chunks) {
-      h = hq + item / tail_chunks;
+    if (item < tail_heads * tail_chunks) {
+      h = first_head + item / tail_chunks;
       col_in_head = rot + (item % tail_chunks) * 8;
     } else {
-      const int j = item - hkv * tail_chunks;
+      const int j = item - tail_heads * tail_chunks;
       h = hq + hkv + j / v_chunks;
       col_in_head = (j % v_chunks) * 8;
     }
     float v[8];
-    Vec8<T>::load(row + h * d + col_in_head, v);
-    const bool is_v = h >= hq + hkv;
-    const int kvh = is_v ? h - hq - hkv : h - hq;
-    Vec8<T>::store(cache + cache_base + (is_v ? v_plane : 0) + (int64_t)kvh * head_stride + col_in_head, v);
+    load8(h * d + col_in_head, v);
+    if (PARTS) Vec8<T>::store(row + h * d + col_in_head, v);
+    if (h >= hq && cache_base >= 0) {
+      const bool is_v = h >= hq + hkv;
+      const int kvh = is_v ? h - hq - hkv : h - hq;
+      Vec8<T>::store(cache + cache_base + (is_v ? v_plane : 0) + (int64_t)kvh * head_stride + col_in_head, v);
+    }
   }
 }
 
-// The same for a projection that arrives as unsummed splits, a few tokens at a time (decoding):
+// The same for a projection that arrives as unsummed splits (decoding, short portions):
 // one thread owns one pair of one head, sums the splits of its two elements, rotates them and
 // writes them to qkv and, for k and v, to the cache: no value makes a second trip through global
 // memory.  The position, the cache slot, the frequency and so the sine and cosine do not depend on
@@ -671,13 +725,19 @@ static int rope_store_launch(T* qkv, const float* parts, int n_parts, int64_t pa
   if (n_tokens <= 0) return 0;
   if (rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || n_parts > 16) return (int)cudaErrorInvalidValue;
   const int eff_rot = inv_freq ? rotary_dim : 0;
-  if (!parts && !interleaved && d % 8 == 0 && eff_rot % 16 == 0 && aligned16(qkv) &&
-      (!slot_mapping || aligned16(cache)) &&
+  // a few tokens of unsummed splits take the pair-per-thread kernel below (more blocks, less latency)
+  const bool few_tokens_of_parts = parts && n_tokens <= 64 && d % 2 == 0;
+  if (!few_tokens_of_parts && !interleaved && d % 8 == 0 && eff_rot % 16 == 0 && aligned16(qkv) &&
+      (!slot_mapping || aligned16(cache)) && (!parts || (aligned16(parts) && part_stride % 4 == 0)) &&
       (eff_rot == 0 || 128 % (eff_rot / 16) == 0)) {
-    return gllm_launch(rope_store_wide_kernel<T>, dim3(n_tokens), dim3(128), 0, stream, qkv, positions, inv_freq,
-                       slot_mapping, cache, n_tokens, hq, hkv, d, rotary_dim, block_size, num_pages, status);
+    return parts ? gllm_launch(rope_store_wide_kernel<T, true>, dim3(n_tokens), dim3(128), 0, stream, qkv, parts,
+                               n_parts, part_stride, positions, inv_freq, slot_mapping, cache, n_tokens, hq, hkv, d,
+                               rotary_dim, block_size, num_pages, status)
+                 : gllm_launch(rope_store_wide_kernel<T, false>, dim3(n_tokens), dim3(128), 0, stream, qkv, parts,
+                               n_parts, part_stride, positions, inv_freq, slot_mapping, cache, n_tokens, hq, hkv, d,
+                               rotary_dim, block_size, num_pages, status);
   }
-  if (parts && n_tokens <= 64 && d % 2 == 0) {
+  if (parts && n_tokens <= 65535 && d % 2 == 0) {   // few tokens, or sizes the wide kernel does not take
     const int items = (hq + 2 * hkv) * (d / 2);
     return gllm_launch(rope_store_parts_kernel<T>, dim3((items + 255) / 256, n_tokens), dim3(256), 0, stream, qkv,
                        parts, n_parts, part_stride, positions, inv_freq, slot_mapping, cache, n_tokens, hq, hkv, d,

@@ -301,7 +301,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           const int m = item.a_row0 + row, n0 = item.b_row0 + c;
           if (m < M && n0 < N) {
             if (splits > 1) {
-              for (int i = 0; i < 16 && n0 + i < N; ++i) mine[(int64_t)m * N + n0 + i] = v[i];
+              float* dst = mine + (int64_t)m * N + n0;
+              if (n0 + 16 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+              } else {
+                for (int i = 0; i < 16 && n0 + i < N; ++i) dst[i] = v[i];
+              }
             } else {
               OutT* dst = out + (int64_t)m * ldo + n0;
               if (n0 + 16 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
@@ -458,20 +465,26 @@ int umma_dispatch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int
 }
 }  // namespace
 
-// Splits along K for M tokens and an [N, K] weight.  It depends on (N, K) and on the bucket
-// M falls in (<= 16, <= 32, <= 64, more), never on M itself: enough items to keep every SM
-// streaming, as long as the fp32 partial tiles stay a small part of the weight's bytes.
+// Splits along K for M tokens and an [N, K] weight.  It depends on (N, K) and on the bucket M falls
+// in (<= 16, <= 32, <= 64, then multiples of 128), never on M itself: enough items to keep every SM
+// busy, as long as the fp32 partial tiles stay a small part of the weight's bytes.
 GLLM_API int gllm_gemm_bf16_splits(int M, int N, int K) {
-  if (M > 64) return 1;
-  const int bucket = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-  const int tiles = (N + BM - 1) / BM;
   const int num_kb = (K + BK - 1) / BK;
-  if (tiles >= 96) return 1;                    // wide enough to keep most SMs streaming without a cut
+  int tiles, limit;
+  if (M <= 64) {
+    const int bucket = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+    tiles = (N + BM - 1) / BM;                   // swapped orientation: 128 weight rows per tile
+    limit = K / (4 * bucket);
+  } else {
+    tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);   // 128 tokens x 256 weight rows per tile
+    limit = K / 512;
+  }
+  if (tiles >= 96) return 1;                    // wide enough to keep most SMs busy without a cut
   // as many splits as give every SM at most one item (one pipeline ramp per SM), each at least two
-  // k-blocks long, none empty, the partial tiles a small part of the weight's bytes
+  // k-blocks long, none empty
   int best = 1;
   for (int s = 2; s <= 16; ++s) {
-    if (tiles * s > 148 || s > K / (4 * bucket) || num_kb / s < 2) break;
+    if (tiles * s > 148 || s > limit || num_kb / s < 2) break;
     const int per = (num_kb + s - 1) / s;
     if (per * (s - 1) < num_kb) best = s;        // the last split is not empty
   }

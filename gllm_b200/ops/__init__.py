@@ -181,9 +181,10 @@ class SplitSum:
     def device(self):
         return self.parts.device
 
-    def tensor(self) -> torch.Tensor:
-        """The summed result as an ordinary tensor of ``dtype``."""
-        out = torch.empty(tuple(self.shape), dtype=self.dtype, device=self.parts.device)
+    def tensor(self, out: torch.Tensor | None = None) -> torch.Tensor:
+        """The summed result as an ordinary tensor of ``dtype`` (into ``out``, contiguous, when given)."""
+        if out is None:
+            out = torch.empty(tuple(self.shape), dtype=self.dtype, device=self.parts.device)
         f = _fn("elementwise", f"gllm_sum_parts_{_suffix(self.dtype)}")
         _check(f(self.parts.data_ptr(), self.parts.shape[0], self.parts.stride(0), out.data_ptr(), out.numel(),
                  _stream()), "sum_parts")

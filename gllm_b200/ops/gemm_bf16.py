@@ -84,6 +84,13 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
     n = weight.shape[0]
     splits = splits_of(m, n, k)
     partial, tickets = _device_scratch(x.device, splits * m * n if splits > 1 else 0, tiles_of(m, n))
+    if splits > 1 and out.is_contiguous():
+        # a second small kernel sums the splits: far quicker than the last CTA of a tile summing them
+        code = f(x.data_ptr(), weight.data_ptr(), None, int(out.dtype == torch.float32), m, n, k, x.stride(0),
+                 weight.stride(0), n, splits, partial.data_ptr(), tickets.data_ptr(), 0,
+                 ops.status_word(x.device).data_ptr(), ops._stream())
+        ops._check(code, "gemm_bf16")
+        return ops.SplitSum(partial[: splits * m * n].view(splits, m, n), out.dtype).tensor(out)
     code = f(x.data_ptr(), weight.data_ptr(), out.data_ptr(), int(out.dtype == torch.float32), m, n, k,
              x.stride(0), weight.stride(0), out.stride(0), splits, partial.data_ptr(), tickets.data_ptr(), 1,
              ops.status_word(x.device).data_ptr(), ops._stream())
