@@ -64,6 +64,8 @@ class StepRunner:
         self.cuda_graphs = bool(cuda_graphs) and torch.cuda.is_available()
         # portion sizes (the scheduler's full prefill portion) whose steps are captured as graphs too
         self.prefill_graph_tokens = tuple(int(n) for n in prefill_graph_tokens)
+        if not getattr(model, "graph_safe_portions", False):
+            self.prefill_graph_tokens = ()                 # some part reads the step's host-side description
         self._graphs: dict = {}
         self._graph_pool = None
         self.graph_replays = 0
@@ -94,7 +96,7 @@ class StepRunner:
         self.last_h2d_bytes = 0
 
     # ------------------------------------------------------------------ build
-    def build(self, entries: list[StepEntry], pad_to: int = 0, seq_bucket: int = 0):
+    def build(self, entries: list[StepEntry], pad_to: int = 0, seq_bucket: int = 0, pad_tokens_to: int = 0):
         """Reserve pages, lay the flat batch out on the host and upload it.
         Returns (tokens, StepContext, logit_rows).
 
@@ -102,7 +104,10 @@ class StepRunner:
         no request up to that many, so a captured graph sees fixed shapes; the
         padding rows use the cache's null row and null page and want logits
         like everybody else.  ``seq_bucket`` then stands in for the longest
-        sequence."""
+        sequence.  ``pad_tokens_to`` (a step that is one prompt portion): a
+        second portion that belongs to no request follows the real one and
+        brings the step to that many tokens; it writes into the null page and
+        attends over it, and nobody wants its logits."""
         cache = self.cache
         if not entries:
             raise ValueError("a step needs at least one entry")
@@ -146,8 +151,11 @@ class StepRunner:
 
         real_r = len(entries)
         pad = max(0, pad_to - real_r)
-        r = real_r + pad
-        n_total += pad
+        null_portion = max(0, pad_tokens_to - n_total)
+        if null_portion == 1 or (null_portion and pad):
+            raise ValueError("a null portion has at least two tokens and does not mix with padding rows")
+        r = real_r + pad + (1 if null_portion else 0)
+        n_total += pad + null_portion
         tokens = np.zeros(n_total, dtype=np.int32)
         positions = np.zeros(n_total, dtype=np.int32)
         token_row = np.full(n_total, cache.null_row, dtype=np.int32)
@@ -176,12 +184,21 @@ class StepRunner:
             off += n
             cu_q[i + 1] = off
         row_list = [x for i in sorted(rows_of) for x in rows_of[i]]
+        if null_portion:
+            positions[off:off + null_portion] = np.arange(null_portion, dtype=np.int32)
+            q_lens.append(null_portion)
+            n_prefill += null_portion
+            off += null_portion
+            cu_q[real_r + 1] = off
         for k in range(pad):
             q_lens.append(1)
             cu_q[real_r + k + 1] = off + k + 1
             row_list.append(off + k)
         logit_rows = np.asarray(row_list, dtype=np.int32)
         null_slots = np.full(pad, cache.null_page * cache.block_size, dtype=np.int32)
+        if null_portion:
+            null_slots = (cache.null_page * cache.block_size
+                          + np.arange(null_portion, dtype=np.int32) % cache.block_size).astype(np.int32)
 
         # pack everything into one pinned buffer, one copy to the device
         pinned = self._pinned[self._flip]
@@ -230,7 +247,7 @@ class StepRunner:
             },
             q_lens_host=tuple(q_lens),
             context_lens_host=tuple(int(c) for c in ctx_lens),
-            max_q_len=max(q_lens),
+            max_q_len=max(pad_tokens_to, max(q_lens)),
             max_seq_len=max(seq_bucket, max(int(c) + q for c, q in zip(ctx_lens, q_lens))),
             num_prefill_tokens=n_prefill,
             num_prefill_requests=sum(1 for n in q_lens if n > 1),
@@ -246,14 +263,17 @@ class StepRunner:
         """The key of the captured graph this step can run as, or None.
 
         ("decode", batch bucket, sequence bucket): every entry brings one token and wants its logits.
-        ("prefill", tokens, wanted rows): one request brings a portion of one of the sizes named in
-        ``prefill_graph_tokens``; what it has cached before does not enter the launch geometry of any
-        kernel (they read it from device memory), so one graph serves every context length."""
+        ("prefill", token bucket, wanted rows, padded): one request brings a portion of up to the
+        largest size named in ``prefill_graph_tokens``; the step is brought to the bucket's size by a null
+        portion (see ``build``).  Neither the portion's length nor what the request has cached before
+        enters the launch geometry of any kernel (they read both from device memory), so one graph
+        serves every length of the bucket and every context length."""
         if not self.cuda_graphs:
             return None
-        if (len(entries) == 1 and len(entries[0].tokens) in self.prefill_graph_tokens
-                and len(entries[0].tokens) > 1 and len(entries[0].tokens) <= self.max_tokens):
-            return ("prefill", len(entries[0].tokens), len(entries[0].want))
+        if len(entries) == 1 and len(entries[0].tokens) > 1 and self.prefill_graph_tokens:
+            bucket = self._prefill_bucket(len(entries[0].tokens))
+            if bucket:
+                return ("prefill", bucket, len(entries[0].want), bucket != len(entries[0].tokens))
         if not all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
             return None
         bucket = 1
@@ -270,6 +290,24 @@ class StepRunner:
         while seq_bucket < longest:
             seq_bucket *= 2
         return ("decode", bucket, min(seq_bucket, max(self.cache.max_seq_len, longest)))
+
+    def _prefill_bucket(self, n: int) -> int:
+        """The step size a lone portion of ``n`` tokens is padded to: multiples of 128 up to 1,024, of
+        256 beyond, with room for a null portion of at least two tokens unless ``n`` fits exactly;
+        0 when it is larger than the largest graphed portion or than a step may be."""
+        limit = min(max(self.prefill_graph_tokens), self.max_tokens)
+        if n > limit:
+            return 0
+        if n in self.prefill_graph_tokens:
+            return n
+        for need in (n, n + 2):
+            step = 128 if need <= 1024 else 256
+            bucket = -(-need // step) * step
+            if bucket == n or bucket >= n + 2:
+                # the null portion is a sequence of its own: it has to fit a block-table row
+                fits = bucket <= self.max_tokens and bucket - n <= self.cache.max_seq_len
+                return bucket if fits else 0
+        return 0
 
     def run(self, entries: list[StepEntry], check: bool = True, greedy: bool = False) -> torch.Tensor:
         """Run one step; returns fp32 logits ``[wanted, vocab]`` on the device,
@@ -293,7 +331,7 @@ class StepRunner:
             if key[0] == "decode":
                 tokens, ctx, rows = self.build(entries, pad_to=key[1], seq_bucket=key[2])
             else:
-                tokens, ctx, rows = self.build(entries)
+                tokens, ctx, rows = self.build(entries, pad_tokens_to=key[1])
             key = key + (bool(greedy),)
             record = self._graphs.get(key)
             if record is None:

@@ -58,6 +58,14 @@ class DecoderModel:
         self.embedding: torch.Tensor | None = None
         self.head: torch.Tensor | None = None
 
+    @property
+    def graph_safe_portions(self) -> bool:
+        """True when every part (the mixers' position encodings included) may have its prompt portions
+        captured in a CUDA graph (``Part.graph_safe_portions``)."""
+        parts = [self.final_norm] + [p for block in self.layers for p in [block] + block.parts()]
+        parts += [m.position for m in (b.mixer for b in self.layers) if getattr(m, "position", None) is not None]
+        return all(getattr(p, "graph_safe_portions", False) for p in parts)
+
     # ---------------------------------------------------------------- weights
     def expected_tensors(self) -> dict[str, TensorExpectation]:
         exp = {self.spec.embedding_name: TensorExpectation((self.spec.vocab_size, self.spec.hidden_size), "matrix")}

@@ -28,6 +28,8 @@ from gllm_b200.parts.base import (
 
 @register_mixer("attention")
 class Attention(Mixer):
+    graph_safe_portions = True
+
     def __init__(self, names, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position=None, window: int | None = None, scale: float | None = None):
         super().__init__(names)

@@ -121,6 +121,12 @@ class MixerCache:
 class Part:
     """Base of all parts: named tensors in, device tensors held."""
 
+    # True when ``forward`` takes everything that varies between steps of equal shape from device
+    # memory (positions, lengths, slots: the tensors of the StepContext), never from its host-side
+    # copies, and never waits for the device: such a part's prompt portions may be captured in a CUDA
+    # graph and replayed for other lengths and contexts.  Decode steps are captured either way.
+    graph_safe_portions = False
+
     def __init__(self, names: Mapping[str, str] | None = None):
         self.names = dict(names or {})
 

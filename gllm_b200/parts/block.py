@@ -14,6 +14,8 @@ from gllm_b200.parts.base import Block, register_block
 
 @register_block("prenorm")
 class PreNormBlock(Block):
+    graph_safe_portions = True
+
     def forward(self, branch, resid, ctx, cache):
         x = self.mixer_norm.forward(branch, resid, ctx.dtype)
         mixed = self.mixer.forward(x, ctx, cache)

@@ -15,6 +15,8 @@ from gllm_b200.parts.base import FeedForward, TensorExpectation, register_feed_f
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
+    graph_safe_portions = True
+
     def __init__(self, names, hidden_size: int, intermediate_size: int):
         super().__init__(names)
         self.hidden_size = int(hidden_size)

@@ -17,6 +17,8 @@ from gllm_b200.parts.base import Norm, TensorExpectation, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
+    graph_safe_portions = True
+
     def __init__(self, names, size: int, eps: float, unit_offset: bool = False):
         super().__init__(names)
         self.size = int(size)

@@ -50,6 +50,8 @@ def scaled_inverse_frequencies(
 
 @register_position_encoding("rotary")
 class RotaryEncoding(PositionEncoding):
+    graph_safe_portions = True
+
     def __init__(self, names=None, head_dim: int = 0, rotary_dim: int | None = None, theta: float = 10000.0,
                  scaling: dict | None = None, interleaved: bool = False):
         super().__init__(names)
@@ -73,6 +75,8 @@ class RotaryEncoding(PositionEncoding):
 @register_position_encoding("none")
 class NoPositionEncoding(PositionEncoding):
     """Positions do not enter the mixer (keys and values are stored as they are)."""
+
+    graph_safe_portions = True
 
     def __init__(self, names=None):
         super().__init__(names)
