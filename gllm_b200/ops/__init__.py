@@ -121,7 +121,14 @@ def _cuda(t: torch.Tensor, name: str, dtype: torch.dtype | None = None, contiguo
         raise ValueError(f"{name} must be contiguous")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
+    """The current CUDA stream's handle (every kernel is launched on it).  The raw getter costs a
+    fraction of a microsecond; building a ``torch.cuda.Stream`` object for every launch cost 15 us."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
