@@ -24,5 +24,11 @@ def load_model(folder: str, dtype: str | None = None, device: str | torch.device
     arch = architecture_for(config.architecture)
     spec = arch.build_spec(config)
     model = DecoderModel(spec, resolve_dtype(dtype, config), device)
+    if torch.device(device).type == "cuda":
+        # the kernels this model will ask for are compiled now, side by side, if they are not built yet
+        from gllm_b200 import ops
+
+        head_dims = {int(m.head_dim) for m in (b.mixer for b in model.layers) if hasattr(m, "head_dim")}
+        ops.prepare(model.dtype, head_dims)
     model.load(open_checkpoint(folder))
     return config, model

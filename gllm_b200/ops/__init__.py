@@ -93,6 +93,28 @@ def _error_string(code: int) -> str:
         return f"cudaError {code}"
 
 
+def modules_for(dtype: torch.dtype, head_dims=(), sampling: bool = False) -> list[str]:
+    """The kernel modules a model of this compute dtype with mixers of these head sizes will load."""
+    if dtype == torch.float32:
+        names = ["elementwise", "gemm_fp32", "attention_simt"]
+    else:
+        names = ["elementwise", "gemm_bf16", "attention_bf16", "attention_prefill_bf16"]
+        if any(d in (64, 128) for d in head_dims):
+            names += ["attention_prefill_tmem", "attention_decode_tma"]
+        if any(d not in (32, 64, 128) for d in head_dims):
+            names.append("attention_simt")
+    if sampling:
+        names.append("sampling")
+    return names
+
+
+def prepare(dtype: torch.dtype, head_dims=(), sampling: bool = False) -> None:
+    """Compile (side by side) whatever of ``modules_for`` is not built yet."""
+    from gllm_b200.ops.build import compile_modules
+
+    compile_modules(modules_for(dtype, head_dims, sampling))
+
+
 # number of kernel launches made through this module (benchmarks read it)
 launch_count = 0
 

@@ -186,6 +186,12 @@ def load_module(module: str) -> ctypes.CDLL:
 
 def build_all(verbose: bool = True) -> dict[str, Path]:
     """Compile every module whose source exists (in parallel)."""
+    return compile_modules([m for m in MODULES if (CSRC_DIR / MODULES[m]).is_file()], verbose=verbose)
+
+
+def compile_modules(names, verbose: bool = True) -> dict[str, Path]:
+    """Compile the named modules that are not built yet, side by side (a first call that needs six
+    modules then waits for the slowest of them, not for their sum)."""
     results: dict[str, Path] = {}
     errors: list[str] = []
 
@@ -195,7 +201,7 @@ def build_all(verbose: bool = True) -> dict[str, Path]:
         except ExtensionError as e:  # collected, raised together below
             errors.append(str(e))
 
-    threads = [threading.Thread(target=_one, args=(m,)) for m in MODULES if (CSRC_DIR / MODULES[m]).is_file()]
+    threads = [threading.Thread(target=_one, args=(m,)) for m in dict.fromkeys(names)]
     for t in threads:
         t.start()
     for t in threads:
