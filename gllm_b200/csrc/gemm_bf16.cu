@@ -450,6 +450,13 @@ int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M
                      reduce_in_kernel, status);
 }
 
+// Width of the weight tile for more than 64 tokens: 256 rows, or 64 for a single tile of tokens
+// (65 .. 128) times a narrow weight, where 256 would leave most SMs without a tile: more tiles, and
+// less to write and read back where the product is cut along K as well.
+static int normal_tile_rows(int M, int N, bool gated) {
+  return (!gated && M <= BM && (N + 255) / 256 < 64) ? 64 : 256;   // measured: wider is quicker from 129 tokens on
+}
+
 template <typename OutT, bool GATED>
 int umma_dispatch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int64_t ldx,
                   int64_t ldw, int64_t ldo, int splits, float* partial, int* tickets, int reduce_in_kernel, int* status,
@@ -460,6 +467,7 @@ int umma_dispatch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int
   if (M <= 16) GLLM_UMMA(16, true);
   if (M <= 32) GLLM_UMMA(32, true);
   if (M <= 64) GLLM_UMMA(64, true);
+  if (normal_tile_rows(M, N, GATED) == 64) GLLM_UMMA(64, false);
   GLLM_UMMA(256, false);
 #undef GLLM_UMMA
 }
@@ -476,7 +484,8 @@ GLLM_API int gllm_gemm_bf16_splits(int M, int N, int K) {
     tiles = (N + BM - 1) / BM;                   // swapped orientation: 128 weight rows per tile
     limit = K / (4 * bucket);
   } else {
-    tiles = ((M + BM - 1) / BM) * ((N + 255) / 256);   // 128 tokens x 256 weight rows per tile
+    const int bn = normal_tile_rows(M, N, false);
+    tiles = ((M + BM - 1) / BM) * ((N + bn - 1) / bn);   // 128 tokens x 256 (or 64) weight rows per tile
     limit = K / 512;
   }
   if (tiles >= 96) return 1;                    // wide enough to keep most SMs busy without a cut
@@ -494,7 +503,8 @@ GLLM_API int gllm_gemm_bf16_splits(int M, int N, int K) {
 // Output tiles of the launch (the ticket array needs this many zeroed ints when splits > 1).
 GLLM_API int gllm_gemm_bf16_tiles(int M, int N) {
   if (M <= 64) return (N + BM - 1) / BM;
-  return ((M + BM - 1) / BM) * ((N + 255) / 256);
+  const int bn = normal_tile_rows(M, N, false);
+  return ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
 }
 
 // out_is_f32: 0 = bf16 output, 1 = fp32 output.  Needs K % 8 == 0 and 16-byte aligned rows of X and W.
