@@ -98,7 +98,7 @@ def modules_for(dtype: torch.dtype, head_dims=(), sampling: bool = False) -> lis
     if dtype == torch.float32:
         names = ["elementwise", "gemm_fp32", "attention_simt"]
     else:
-        names = ["elementwise", "gemm_bf16", "attention_bf16", "attention_prefill_bf16"]
+        names = ["elementwise", "gemm_bf16", "gemm_bf16_pair", "attention_bf16", "attention_prefill_bf16"]
         if any(d in (64, 128) for d in head_dims):
             names += ["attention_prefill_tmem", "attention_decode_tma"]
         if any(d not in (32, 64, 128) for d in head_dims):

@@ -43,6 +43,7 @@ MODULES = {
     "attention_simt": "attention_simt.cu",
     "sampling": "sampling.cu",
     "gemm_bf16": "gemm_bf16.cu",
+    "gemm_bf16_pair": "gemm_bf16_pair.cu",
     "attention_bf16": "attention_bf16.cu",
     "attention_prefill_bf16": "attention_prefill_bf16.cu",
     "attention_prefill_tmem": "attention_prefill_tmem.cu",

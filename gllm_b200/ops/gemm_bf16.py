@@ -12,6 +12,7 @@ there, for comparisons.
 
 from __future__ import annotations
 
+import os
 from ctypes import c_int, c_int64, c_void_p
 
 import torch
@@ -70,6 +71,36 @@ def _device_scratch(device: torch.device, partial_floats: int, tickets: int):
     return s[name], s["tickets"]
 
 
+_pair = None
+# From this many tokens on, products that are not cut along K run on pairs of CTAs (cta_group::2).
+# (GLLM_B200_PAIR_MIN_TOKENS overrides the threshold: tests use 1 to run small steps through the kernel.)
+PAIR_MIN_TOKENS = int(os.environ.get("GLLM_B200_PAIR_MIN_TOKENS", 129))
+
+
+def _pair_fn():
+    global _pair
+    if _pair is None:
+        lib = load_module("gemm_bf16_pair")
+        f = lib.gllm_gemm_bf16_pair
+        f.argtypes = [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64, P, P]
+        f.restype = c_int
+        _pair = f
+    return _pair
+
+
+def linear_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False) -> torch.Tensor:
+    """``out = x @ weight.T`` (or its gated form, see ``linear_gated``) by the kernel in which two CTAs
+    of a cluster share every 256x256 tile.  Any number of tokens is right; few are slow."""
+    from gllm_b200 import ops
+
+    m, k = x.shape
+    code = _pair_fn()(x.data_ptr(), weight.data_ptr(), out.data_ptr(), int(out.dtype == torch.float32), int(gated), m,
+                      weight.shape[0], k, x.stride(0), weight.stride(0), out.stride(0),
+                      ops.status_word(x.device).data_ptr(), ops._stream())
+    ops._check(code, "gemm_bf16_pair")
+    return out
+
+
 def tensor_core_kernel_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
     k = x.shape[1]
     return (k % 8 == 0 and x.stride(1) == 1 and weight.stride(1) == 1 and x.stride(0) % 8 == 0
@@ -83,6 +114,8 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
     m, k = x.shape
     n = weight.shape[0]
     splits = splits_of(m, n, k)
+    if splits == 1 and m >= PAIR_MIN_TOKENS:
+        return linear_pair(x, weight, out)
     partial, tickets = _device_scratch(x.device, splits * m * n if splits > 1 else 0, tiles_of(m, n))
     if splits > 1 and out.is_contiguous():
         # a second small kernel sums the splits: far quicker than the last CTA of a tile summing them
@@ -140,6 +173,8 @@ def linear_gated(x: torch.Tensor, weight: torch.Tensor):
         return None
     m = x.shape[0]
     out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
+    if m >= PAIR_MIN_TOKENS:
+        return linear_pair(x, weight, out, gated=True)
     g = _umma_fns()[3]
     code = g(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), weight.stride(0), out.stride(0),
              ops.status_word(x.device).data_ptr(), ops._stream())

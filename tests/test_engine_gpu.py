@@ -84,6 +84,44 @@ def test_full_prefill_portions_replay_a_graph(dtype, tmp_path):
     plain_greedy_check(cfg, weights, prompt2, out2.token_ids, 1e-5 if dtype == "float32" else 0.05)
 
 
+def test_many_decoded_tokens_beside_full_prefill_portions(tmp_path, monkeypatch):
+    """40 requests with prompts of 1,040 tokens, admitted under a budget of 2,048 tokens a step: while
+    the last ones are prefilled in portions of 512, more than 32 others decode, so one step runs the
+    prefill attention kernel, the persistent decode kernel (which holds every SM), its merge and the
+    products on pairs of CTAs, each scheduled before the one ahead of it is done.  Every request's
+    tokens are the plain implementation's."""
+    from gllm_b200 import GenerationRequest, GeneratorParams, LLMEngine
+    from gllm_b200.config import load_config
+    from gllm_b200.ops import attention_bf16, gemm_bf16
+    from gllm_b200.weights import write_random_model
+
+    raw = dict(architectures=["LlamaForCausalLM"], hidden_size=512, head_dim=64, intermediate_size=1024,
+               hidden_act="silu", num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2,
+               rms_norm_eps=1e-5, eos_token_id=[0], torch_dtype="bfloat16", rope_theta=10000.0, vocab_size=1000,
+               tie_word_embeddings=False)
+    folder = write_random_model(str(tmp_path / "m"), load_config(raw), seed=21, std=0.03, norm_jitter=0.05,
+                                std_overrides={"q_proj": 0.06, "k_proj": 0.06})
+    cfg, weights = read_raw(folder, round_to_bf16=True)
+    calls = []
+    real_pair, real_decode = gemm_bf16.linear_pair, attention_bf16.decode_attention
+    monkeypatch.setattr(gemm_bf16, "linear_pair",
+                        lambda x, *a, **k: (calls.append(("pair", x.shape[0])), real_pair(x, *a, **k))[1])
+    monkeypatch.setattr(attention_bf16, "decode_attention",
+                        lambda q, *a, **k: (calls.append(("decode", q.shape[0])), real_decode(q, *a, **k))[1])
+    g = torch.Generator().manual_seed(15)
+    prompts = [torch.randint(1, cfg["vocab_size"], (1040,), generator=g).tolist() for _ in range(2)]
+    params = GeneratorParams(block_size=16, max_batch_size=40, max_seq_len=1280, model_dtype="bfloat16",
+                             max_num_batched_tokens=2048, prefill_chunk=512)
+    engine = LLMEngine(folder, params, device="cuda:0")
+    outs = engine.generate([GenerationRequest(prompt_token_ids=prompts[i % 2], max_new_tokens=32, temperature=0.0,
+                                              ignore_eos=True) for i in range(40)])
+    assert all(len(o.token_ids) == 32 for o in outs)
+    wide = [i for i, c in enumerate(calls) if c[0] == "decode" and c[1] >= 33]      # 33 x 9 spans: the stream kernel
+    assert wide and any(c[0] == "pair" and c[1] >= 129 + 33 for c in calls[wide[0]:wide[0] + 2])
+    for i in (0, 1, 20, 21, 38, 39):
+        plain_greedy_check(cfg, weights, prompts[i % 2], outs[i].token_ids[:2], 0.05)
+
+
 def test_long_decoding_and_first_tokens(tmp_path):
     from gllm_b200 import GenerationRequest, GeneratorParams, LLMEngine
 

@@ -401,6 +401,50 @@ def test_gemm_bf16_tensor_memory(ops, m, n, k, out_dtype):
         torch.testing.assert_close(alone[0].double(), got[m // 2].double(), rtol=1e-2, atol=1e-2)
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 130, 72), (129, 256, 64), (257, 777, 1000), (300, 3072, 2048), (2112, 2048, 2048)])
+def test_gemm_bf16_pair_of_ctas(ops, m, n, k):
+    """The product on pairs of CTAs (cta_group::2), called directly: tails in M, N and K (a pair's
+    second CTA may have no token row at all), both output types, twice in a row; then behind a
+    kernel that holds the GPU and a small one (so that it is scheduled early, its CTAs starting one
+    after the other as SMs come free), which must not change a bit."""
+    from gllm_b200.ops import gemm_bf16
+
+    g = torch.Generator().manual_seed(29)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(n, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).cuda()
+    want = x.double() @ w.double().T
+    for out_dtype, tol_ in ((torch.float32, 1e-4), (torch.bfloat16, 1e-2)):
+        for _ in range(2):
+            got = gemm_bf16.linear_pair(x, w, torch.full((m, n), float("nan"), dtype=out_dtype, device="cuda"))
+            ops.check_status()
+            torch.testing.assert_close(got.double(), want, rtol=tol_, atol=tol_)
+    first = gemm_bf16.linear_pair(x, w, torch.empty((m, n), dtype=torch.bfloat16, device="cuda"))
+    big_x = torch.randn(4096, 2048, generator=g).to(torch.bfloat16).cuda()
+    big_w = torch.randn(8192, 2048, generator=g).to(torch.bfloat16).cuda()
+    resid = torch.zeros(8, 2048).cuda()
+    for _ in range(3):
+        ops.linear(big_x, big_w)
+        ops.add_rmsnorm(None, resid, torch.ones(2048).cuda(), 1e-5, torch.bfloat16)
+        again = gemm_bf16.linear_pair(x, w, torch.empty((m, n), dtype=torch.bfloat16, device="cuda"))
+        assert torch.equal(first, again)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("m,inter,k", [(130, 192, 96), (513, 1024, 2048)])
+def test_gemm_bf16_pair_gated(ops, m, inter, k):
+    from gllm_b200.ops import gemm_bf16
+
+    g = torch.Generator().manual_seed(30)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+    wg = (torch.randn(inter, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).cuda()
+    wu = (torch.randn(inter, k, generator=g) / math.sqrt(k)).to(torch.bfloat16).cuda()
+    got = gemm_bf16.linear_pair(x, ops.interleave_gate_up(wg, wu),
+                                torch.full((m, inter), float("nan"), dtype=torch.bfloat16, device="cuda"), gated=True)
+    ops.check_status()
+    a, b = x.double() @ wg.double().T, x.double() @ wu.double().T
+    torch.testing.assert_close(got.double(), a * torch.sigmoid(a) * b, rtol=2e-2, atol=2e-2)
+
+
 def test_gemm_bf16_odd_inner_size_goes_to_the_library(ops):
     g = torch.Generator().manual_seed(10)
     x = torch.randn(5, 100, generator=g).to(torch.bfloat16).cuda()

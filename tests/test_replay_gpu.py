@@ -153,11 +153,15 @@ def test_replay_all_cuts(name, dtype, tmp_path):
     compare(results, index, plain, *tol)
 
 
-def test_replay_through_the_stream_decode_kernel(tmp_path, monkeypatch):
+@pytest.mark.parametrize("pair_gemm", [False, True])
+def test_replay_through_the_stream_decode_kernel(tmp_path, monkeypatch, pair_gemm):
     """The single tokens of tiny D (head size 64, one kv head, a window of 40 on one layer, pages of
     16) through the persistent TMA decode kernel, which steps this small would not pick by themselves:
-    the tail decoded token by token, and the mixed steps with pages used again."""
+    the tail decoded token by token, and the mixed steps with pages used again.  The second time every
+    product that is not cut along K also runs on pairs of CTAs, as in large mixed steps."""
     monkeypatch.setenv("GLLM_B200_STREAM_MIN_ITEMS", "1")
+    if pair_gemm:
+        monkeypatch.setenv("GLLM_B200_PAIR_MIN_TOKENS", "1")
     folder = write_tiny("D", str(tmp_path / "model"), sharp=False)
     cfg, weights = read_raw(folder, round_to_bf16=True)
     vocab = cfg["vocab_size"]
