@@ -74,6 +74,15 @@ __device__ __forceinline__ float sum_parts16(const float* __restrict__ p, int n_
 // returns only when every earlier kernel has completed and its writes are visible; and it calls
 // pdl_trigger() at once, which lets the kernel after it be scheduled early in turn.  Both are
 // no-ops for a kernel that was launched the ordinary way.
+// A block may touch another block's shared memory (or allocate tensor memory as a pair) only once that
+// block runs.  The blocks of a cluster usually start together, but microseconds apart when the kernel
+// is scheduled early and SMs come free one by one.  Every thread calls cluster_arrive_started() at the
+// kernel's top and cluster_wait_started() before the first such access: the wait is over as soon as
+// every block of the cluster has started, which by then it normally has.
+__device__ __forceinline__ void cluster_arrive_started() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_started() { asm volatile("barrier.cluster.wait.aligned;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -258,6 +258,7 @@ __global__ void add_rmsnorm_cluster_kernel(const float* __restrict__ parts, int 
   __shared__ float scratch[32];
   __shared__ float all_ss[16];
   pdl_trigger();
+  cluster_arrive_started();
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = (int)cluster.block_rank(), n_ranks = (int)cluster.num_blocks();
   const int cols_per = (hidden + n_ranks - 1) / n_ranks;
@@ -289,6 +290,7 @@ __global__ void add_rmsnorm_cluster_kernel(const float* __restrict__ parts, int 
   // every block pushes its sum into all blocks' slots: after one cluster barrier each reads only its
   // own shared memory, so none has to stay for the others
   const float mine = block_sum(ss, scratch);
+  cluster_wait_started();
   if (threadIdx.x < n_ranks) *cluster.map_shared_rank(&all_ss[rank], threadIdx.x) = mine;
   cluster.sync();
   float total = 0.f;

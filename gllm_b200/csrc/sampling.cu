@@ -361,6 +361,7 @@ argmax_kernel(const float* __restrict__ logits, int64_t row_stride, int V, int* 
   __shared__ float peer_v[ARGMAX_CLUSTER];
   __shared__ int peer_i[ARGMAX_CLUSTER];
   pdl_trigger();
+  cluster_arrive_started();
   cg::cluster_group cluster = cg::this_cluster();
   const int rank = (int)cluster.block_rank(), n_ranks = (int)cluster.num_blocks();
   const int row = blockIdx.y;
@@ -376,6 +377,7 @@ argmax_kernel(const float* __restrict__ logits, int64_t row_stride, int V, int* 
   }
   int arg;
   const float best = block_max_arg(vmax, imax, &arg, s);
+  cluster_wait_started();
   if (threadIdx.x == 0) {
     *cluster.map_shared_rank(&peer_v[rank], 0) = best;
     *cluster.map_shared_rank(&peer_i[rank], 0) = arg;
