@@ -72,9 +72,31 @@ def _device_scratch(device: torch.device, partial_floats: int, tickets: int):
 
 
 _pair = None
-# From this many tokens on, products that are not cut along K run on pairs of CTAs (cta_group::2).
-# (GLLM_B200_PAIR_MIN_TOKENS overrides the threshold: tests use 1 to run small steps through the kernel.)
+# From this many tokens on, products that are not cut along K run on pairs of CTAs (cta_group::2) where
+# a pair has enough to do (below).  GLLM_B200_PAIR_MIN_TOKENS overrides the threshold and drops the
+# second condition: tests use 1 to run small steps through the kernel.
 PAIR_MIN_TOKENS = int(os.environ.get("GLLM_B200_PAIR_MIN_TOKENS", 129))
+_PAIR_FORCED = "GLLM_B200_PAIR_MIN_TOKENS" in os.environ
+PAIR_MIN_BLOCKS = 64
+_sm_pairs = {}
+
+
+def pair_kernel_pays(x: torch.Tensor, n: int) -> bool:
+    """The cluster's start and its two barriers cost about 2 us more than the one-CTA kernel's start:
+    that is won back once a pair multiplies 64 blocks of 64 along K or more (measured at 2,048 tokens:
+    the o-projection, 32 blocks per pair, is 2 us slower on pairs; qkv, 64, the same; down, 128, and
+    gate/up, 224, quicker)."""
+    m, k = x.shape
+    if m < PAIR_MIN_TOKENS:
+        return False
+    if _PAIR_FORCED:
+        return True
+    dev = x.device.index or 0
+    if dev not in _sm_pairs:
+        _sm_pairs[dev] = max(1, torch.cuda.get_device_properties(dev).multi_processor_count // 2)
+    items = -(-m // 256) * -(-n // 256)
+    per_pair = -(-items // min(items, _sm_pairs[dev]))
+    return per_pair * -(-k // 64) >= PAIR_MIN_BLOCKS
 
 
 def _pair_fn():
@@ -114,7 +136,7 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
     m, k = x.shape
     n = weight.shape[0]
     splits = splits_of(m, n, k)
-    if splits == 1 and m >= PAIR_MIN_TOKENS:
+    if splits == 1 and pair_kernel_pays(x, n):
         return linear_pair(x, weight, out)
     partial, tickets = _device_scratch(x.device, splits * m * n if splits > 1 else 0, tiles_of(m, n))
     if splits > 1 and out.is_contiguous():
@@ -173,7 +195,7 @@ def linear_gated(x: torch.Tensor, weight: torch.Tensor):
         return None
     m = x.shape[0]
     out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
-    if m >= PAIR_MIN_TOKENS:
+    if pair_kernel_pays(x, n):
         return linear_pair(x, weight, out, gated=True)
     g = _umma_fns()[3]
     code = g(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), weight.stride(0), out.stride(0),

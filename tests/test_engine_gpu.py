@@ -103,6 +103,7 @@ def test_many_decoded_tokens_beside_full_prefill_portions(tmp_path, monkeypatch)
                                 std_overrides={"q_proj": 0.06, "k_proj": 0.06})
     cfg, weights = read_raw(folder, round_to_bf16=True)
     calls = []
+    monkeypatch.setattr(gemm_bf16, "_PAIR_FORCED", True)    # a model this narrow would keep to the one-CTA kernel
     real_pair, real_decode = gemm_bf16.linear_pair, attention_bf16.decode_attention
     monkeypatch.setattr(gemm_bf16, "linear_pair",
                         lambda x, *a, **k: (calls.append(("pair", x.shape[0])), real_pair(x, *a, **k))[1])
