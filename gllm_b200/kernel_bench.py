@@ -127,10 +127,43 @@ def linear(m=8, n=16384, k=2048, iters=5, peaks=None, out_fp32=False, gated=0, s
             "shape": dict(m=m, n=n, k=k)}
 
 
+def add_rmsnorm(rows=8, hidden=2048, splits=8, iters=5, peaks=None):
+    """resid += (sum of ``splits`` fp32 partial products, 0: a summed bf16 branch), then RMSNorm: the
+    kernel between two products of a layer."""
+    from gllm_b200 import ops
+
+    resid = torch.randn(rows, hidden, device="cuda")
+    weight = torch.ones(hidden, device="cuda")
+    parts = torch.randn(max(splits, 1), rows, hidden, device="cuda")
+    branch = ops.SplitSum(parts, torch.bfloat16) if splits else parts[0].to(torch.bfloat16)
+    out = torch.empty(rows, hidden, dtype=torch.bfloat16, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    us = _time(lambda: ops.add_rmsnorm(branch, resid, weight, 1e-5, torch.bfloat16, out=out), iters, flush)
+    nbytes = rows * hidden * ((4 * splits if splits else 2) + 4 + 4 + 2) + hidden * 4
+    gbs = nbytes / us / 1e3
+    return {"kernel": "add_rmsnorm", "us": round(us, 2), "bytes": nbytes, "achieved_gbs": round(gbs, 1),
+            "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4), "shape": dict(rows=rows, hidden=hidden, splits=splits)}
+
+
+def argmax(rows=8, vocab=128256, iters=5, peaks=None):
+    from gllm_b200 import ops
+
+    logits = torch.randn(rows, vocab, device="cuda")
+    out = torch.empty(rows, dtype=torch.int32, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    us = _time(lambda: ops.argmax(logits, out=out), iters, flush)
+    nbytes = rows * vocab * 4
+    gbs = nbytes / us / 1e3
+    return {"kernel": "argmax", "us": round(us, 2), "bytes": nbytes, "achieved_gbs": round(gbs, 1),
+            "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4), "shape": dict(rows=rows, vocab=vocab)}
+
+
 KERNELS = {
     "attention_decode": attention_decode,
     "attention_prefill": attention_prefill,
     "linear": linear,
+    "add_rmsnorm": add_rmsnorm,
+    "argmax": argmax,
 }
 
 
