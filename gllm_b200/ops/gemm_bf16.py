@@ -61,13 +61,22 @@ def _device_scratch(device: torch.device, partial_floats: int, tickets: int):
     buffers used in turn, so an unsummed result survives the next product) and
     the ticket counters (zeroed once; the kernel leaves them at zero)."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    s = _scratch.setdefault(idx, {"turn": 0})
+    s = _scratch.setdefault(idx, {"turn": 0, "retired": []})
+
+    def grow(name, numel, make):
+        # a buffer that is outgrown stays allocated: a captured graph may hold its address, and memory
+        # given back to the allocator would be handed to somebody else while the graph still writes it
+        if name in s:
+            s["retired"].append(s[name])
+        s[name] = make(numel)
+
     if "tickets" not in s or s["tickets"].numel() < tickets:
-        s["tickets"] = torch.zeros(max(tickets, 4096), dtype=torch.int32, device=device)
+        grow("tickets", max(tickets, 4096), lambda n: torch.zeros(n, dtype=torch.int32, device=device))
     s["turn"] ^= 1
     name = f"partial{s['turn']}"
     if name not in s or s[name].numel() < partial_floats:
-        s[name] = torch.empty(max(partial_floats, 1 << 22), dtype=torch.float32, device=device)
+        # 148 items of 128 x 256 (the most a product is cut into) fit without growing
+        grow(name, max(partial_floats, 148 * 128 * 256), lambda n: torch.empty(n, dtype=torch.float32, device=device))
     return s[name], s["tickets"]
 
 

@@ -445,6 +445,21 @@ def test_gemm_bf16_pair_gated(ops, m, inter, k):
     torch.testing.assert_close(got.double(), a * torch.sigmoid(a) * b, rtol=2e-2, atol=2e-2)
 
 
+def test_gemm_scratch_that_is_outgrown_stays_allocated(ops):
+    """A captured graph holds the address of the split-K scratch it was captured with: when a later,
+    larger product makes the scratch grow, the old buffer must not go back to the allocator (the next
+    tensor would get its memory while the graph still writes partial sums there)."""
+    from gllm_b200.ops import gemm_bf16
+
+    dev = torch.device("cuda:0")
+    before = {gemm_bf16._device_scratch(dev, 16, 16)[0].data_ptr() for _ in range(2)}     # both turns
+    need = max(gemm_bf16._scratch[0][f"partial{t}"].numel() for t in (0, 1)) + 1
+    after = {gemm_bf16._device_scratch(dev, need, 16)[0].data_ptr() for _ in range(2)}
+    assert not (before & after)
+    kept = {t.data_ptr() for t in gemm_bf16._scratch[0]["retired"]}
+    assert before <= kept
+
+
 def test_gemm_bf16_odd_inner_size_goes_to_the_library(ops):
     g = torch.Generator().manual_seed(10)
     x = torch.randn(5, 100, generator=g).to(torch.bfloat16).cuda()
