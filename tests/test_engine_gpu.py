@@ -123,6 +123,43 @@ def test_many_decoded_tokens_beside_full_prefill_portions(tmp_path, monkeypatch)
         plain_greedy_check(cfg, weights, prompts[i % 2], outs[i].token_ids[:2], 0.05)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_random_crowd_over_a_small_pool(dtype, tmp_path):
+    """48 requests of random lengths, greedy and sampled, over 40 pages and 6 slots: admissions wait,
+    requests are preempted and computed again, decode steps replay graphs between mixed steps.  Every
+    request gets its tokens, no page is lost, and the greedy ones are the plain implementation's."""
+    import random
+
+    from gllm_b200 import GenerationRequest, GeneratorParams, LLMEngine
+
+    folder = write_tiny("D", str(tmp_path / "m"), sharp=(dtype == "float32"))
+    cfg, weights = read_raw(folder, round_to_bf16=(dtype == "bfloat16"))
+    rnd = random.Random(3)
+    g = torch.Generator().manual_seed(3)
+    reqs = []
+    for i in range(48):
+        n = rnd.choice([1, 2, 5, 17, 31, 64, 100, 150])
+        greedy = i % 3 != 2
+        reqs.append(GenerationRequest(
+            prompt_token_ids=torch.randint(1, cfg["vocab_size"], (n,), generator=g).tolist(),
+            max_new_tokens=rnd.choice([1, 2, 9, 30]), temperature=0.0 if greedy else 0.9, top_k=20, top_p=0.9, seed=i,
+            ignore_eos=True))
+    params = GeneratorParams(block_size=16, max_batch_size=6, max_seq_len=192, model_dtype=dtype, num_blocks=40,
+                             max_num_batched_tokens=96, prefill_chunk=32)
+    engine = LLMEngine(folder, params, device="cuda:0")
+    outs = engine.generate(reqs)
+    assert [len(o.token_ids) for o in outs] == [r.max_new_tokens for r in reqs]
+    engine.cache.check_invariants()
+    assert engine.cache.num_free_pages() == 40 and engine.counters["preemptions"] >= 1
+    assert engine.runner.graph_replays > 0
+    checked = 0
+    for r, o in zip(reqs, outs):
+        if r.temperature == 0.0 and checked < 10 and len(r.prompt_token_ids) + r.max_new_tokens <= 120:
+            plain_greedy_check(cfg, weights, r.prompt_token_ids, o.token_ids[:6], 1e-5 if dtype == "float32" else 0.05)
+            checked += 1
+    assert checked == 10
+
+
 def test_long_decoding_and_first_tokens(tmp_path):
     from gllm_b200 import GenerationRequest, GeneratorParams, LLMEngine
 
