@@ -54,3 +54,39 @@ def test_full_width_layers(full_width_model, dtype):
         assert float((got[0] - want[p + n - 1]).abs().max()) <= bound, p
         p += n
     assert dtype == "float32" or runner.graph_replays > 0
+
+
+def test_full_width_crowd_gives_each_request_the_logits_it_gets_alone(full_width_model):
+    """40 requests with 1,000 cached tokens each decode one token in the same step in which a 41st
+    request's portion of 300 tokens is prefilled (the persistent decode kernel, the tcgen05 prefill
+    kernel, products of 340 tokens on one CTA and on pairs of CTAs per tile, unsummed splits).  Each
+    sampled request's logits are those it gets when it runs alone, to bfloat16 rounding."""
+    from gllm_b200.engine.replay import build_runner
+    from gllm_b200.engine.step import StepEntry
+
+    folder, cfg, _, want = full_width_model
+    _, runner = build_runner(folder, "bfloat16", max_tokens=41 * 1024, max_live=41)
+    g = torch.Generator().manual_seed(7)
+    vocab = cfg["vocab_size"]
+    prompts = [torch.randint(0, vocab, (1000,), generator=g).tolist() for _ in range(40)]
+    nexts = torch.randint(0, vocab, (40,), generator=g).tolist()
+    late = torch.randint(0, vocab, (300,), generator=g).tolist()
+    sampled = [0, 13, 27, 39]
+    alone = {}
+    for i in sampled:
+        runner.run([StepEntry("alone", prompts[i], [])])
+        alone[i] = runner.run([StepEntry("alone", [nexts[i]], [0])]).float().cpu()[0]
+        runner.finish("alone")
+    alone["late"] = runner.run([StepEntry("alone", late, [299])]).float().cpu()[0]
+    runner.finish("alone")
+    for first in range(0, 40, 4):                        # four prompts a step
+        runner.run([StepEntry(f"r{i}", prompts[i], []) for i in range(first, first + 4)])
+    entries = [StepEntry("late", late, [299])] + [StepEntry(f"r{i}", [nexts[i]], [0]) for i in range(40)]
+    got = runner.run(entries).float().cpu()
+    scale = float(want.abs().max())
+    pairs = [("late", got[0])] + [(i, got[1 + i]) for i in sampled]
+    for key, row in pairs:
+        err = (row - alone[key]).abs()
+        assert float(err.max()) <= 5e-2 * scale and float(err.mean()) <= 5e-3 * scale, (key, float(err.max()))
+    # the 36 others are sane too: finite, and no two requests share a row
+    assert bool(got.isfinite().all()) and len({int(r.argmax()) for r in got}) > 20
