@@ -292,9 +292,11 @@ class StepRunner:
         return ("decode", bucket, min(seq_bucket, max(self.cache.max_seq_len, longest)))
 
     def _prefill_bucket(self, n: int) -> int:
-        """The step size a lone portion of ``n`` tokens is padded to: multiples of 128 up to 1,024, of
-        256 beyond, with room for a null portion of at least two tokens unless ``n`` fits exactly;
-        0 when it is larger than the largest graphed portion or than a step may be."""
+        """The step size a lone portion of ``n`` tokens is padded to: 16, 32, 64 (the token buckets of
+        the products for few tokens: a short prompt costs what a decode step of that many tokens
+        costs), then multiples of 128 up to 1,024, of 256 beyond, with room for a null portion of at
+        least two tokens unless ``n`` fits exactly; 0 when it is larger than the largest graphed
+        portion or than a step may be."""
         limit = min(max(self.prefill_graph_tokens), self.max_tokens)
         if n > limit:
             return 0
@@ -302,7 +304,7 @@ class StepRunner:
             return n
         for need in (n, n + 2):
             step = 128 if need <= 1024 else 256
-            bucket = -(-need // step) * step
+            bucket = next((b for b in (16, 32, 64) if need <= b), -(-need // step) * step)
             if bucket == n or bucket >= n + 2:
                 # the null portion is a sequence of its own: it has to fit a block-table row
                 fits = bucket <= self.max_tokens and bucket - n <= self.cache.max_seq_len

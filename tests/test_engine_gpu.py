@@ -160,6 +160,26 @@ def test_a_random_crowd_over_a_small_pool(dtype, tmp_path):
     assert checked == 10
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_short_prompts_run_as_graphs_of_few_tokens(dtype, tmp_path):
+    """Lone prompts of 2 .. 100 tokens are padded to 16, 32, 64 or 128 tokens by a null portion and
+    replayed as graphs: every bucket's edge and its neighbours give the plain implementation's tokens."""
+    from gllm_b200 import GenerationRequest, GeneratorParams, LLMEngine
+
+    folder = write_tiny("D", str(tmp_path / "m"), sharp=(dtype == "float32"))
+    cfg, weights = read_raw(folder, round_to_bf16=(dtype == "bfloat16"))
+    params = GeneratorParams(block_size=16, max_batch_size=2, max_seq_len=256, model_dtype=dtype, prefill_chunk=128)
+    engine = LLMEngine(folder, params, device="cuda:0")
+    g = torch.Generator().manual_seed(16)
+    for n in (2, 3, 14, 15, 16, 17, 30, 31, 32, 33, 62, 63, 64, 65, 100, 128):
+        prompt = torch.randint(1, cfg["vocab_size"], (n,), generator=g).tolist()
+        out = engine.generate([GenerationRequest(prompt_token_ids=prompt, max_new_tokens=2, temperature=0.0,
+                                                 ignore_eos=True)])[0]
+        plain_greedy_check(cfg, weights, prompt, out.token_ids, 1e-5 if dtype == "float32" else 0.05)
+    buckets = {k[1] for k in engine.runner._graphs if k[0] == "prefill"}
+    assert buckets == {16, 32, 64, 128}
+
+
 def test_long_decoding_and_first_tokens(tmp_path):
     from gllm_b200 import GenerationRequest, GeneratorParams, LLMEngine
 
