@@ -61,11 +61,15 @@ decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride,
   const int c0 = max(split * S::CHUNK, kstart);
   const int c1 = min((split + 1) * S::CHUNK, qpos + 1);
   float* my_ml = part_ml + (((int64_t)n * hq + h0) * num_chunks + split) * 2;
-  // Nothing of this chunk is visible: the merge kernel reads only the chunks of kstart .. qpos, so this
-  // CTA has nothing to write, and it leaves at once: waiting here would hold its shared memory, and a
-  // grid sized for the sequence bucket would keep CTAs with keys from starting (and from requesting
-  // their keys) until the kernel before this one is done.
-  if (c0 >= c1) return;
+  if (c0 >= c1) {                                       // nothing of this chunk is visible
+    pdl_wait();
+    if (threadIdx.x < heads) {
+      float* ml = my_ml + (int64_t)threadIdx.x * num_chunks * 2;
+      ml[0] = -INFINITY;
+      ml[1] = 0.f;
+    }
+    return;
+  }
   const int* bt = block_table + (int64_t)token_row[n] * bt_stride;
   const int64_t head_elems = (int64_t)block_size * D;
   const int64_t page_elems = 2 * (int64_t)hkv * head_elems;
