@@ -12,7 +12,8 @@ A "step" is one decode step of the whole batch (forward + greedy sampling).
 wall-clock around K ``LLMEngine.step()`` calls, each of which copies the step's
 metadata from pinned host memory and reads the sampled tokens back.  The model
 (2.47 GB of weights) is larger than the 126 MB L2, so every step streams its
-inputs from HBM; no explicit L2 flush is used.
+inputs from HBM; no explicit L2 flush is used.  The prefill is one step of 2,048 prompt
+tokens, timed on the device (the host's share of the step overlaps a spin kernel).
 """
 
 from __future__ import annotations
@@ -227,6 +228,10 @@ def time_prefill(engine, tokens: int, repeats: int, warmup: int):
         engine.scheduler.add(st)
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        # the GPU spins for about a millisecond first, so that the host's share of the step (schedule,
+        # metadata, launch) is over when the start event fires: the events bracket the device's time for
+        # the step, its copy of the metadata included
+        torch.cuda._sleep(3_000_000)
         start.record()
         engine.step()
         end.record()
