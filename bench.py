@@ -112,12 +112,9 @@ class ClockSampler:
 
 def make_model_folder(tmp: str, num_layers: int | None) -> str:
     from gllm_b200.config import load_config
-    from gllm_b200.config.presets import load_preset
     from gllm_b200.weights import write_random_model
 
-    raw = load_preset("llama-3.2-1b")
-    if num_layers is not None:
-        raw["num_hidden_layers"] = num_layers
+    raw = raw_model_config(num_layers)
     folder = os.path.join(tmp, "llama-3.2-1b-random")
     write_random_model(folder, load_config(raw), seed=0, std=0.02)
     return folder
@@ -167,9 +164,7 @@ def fill_engine(engine, batch: int, context: int, seed: int = 0):
             prompt_token_ids=torch.randint(0, vocab, (context,), generator=g).tolist(),
             max_new_tokens=engine.max_seq_len - context, temperature=0.0, ignore_eos=True,
         )
-        st = engine._make_state(req)
-        engine.scheduler.add(st)
-        states.append(st)
+        states.append(engine.submit(req))
     while any(s.num_computed < len(s.prompt_token_ids) for s in states):
         engine.step()
     return states
@@ -177,60 +172,68 @@ def fill_engine(engine, batch: int, context: int, seed: int = 0):
 
 def drain(engine, states):
     for s in states:
-        engine.scheduler.abort(s.id)
+        engine.abort(s.id)
 
 
-def time_decode(engine, batch: int, context: int, steps: int, warmup: int):
-    """Returns (device ms per step, wall ms per step, launches per step, h2d, d2h)."""
+def time_decode(engine, batch: int, context: int, steps: int, warmup: int, reps: int = 5):
+    """``reps`` repetitions of: fill the engine with ``batch`` requests of ``context`` cached tokens, ``warmup``
+    untimed steps, then ``steps`` timed ones.  Device time (CUDA events) and wall time (host clock, a
+    synchronize on both sides) are taken around the SAME loop of ``LLMEngine.step()`` calls, each of which
+    copies the step's metadata from pinned host memory and reads the sampled tokens of the step before it.
+    Returns the medians: (device ms per step, wall ms per step, launches per step, h2d, d2h)."""
     import torch
 
     from gllm_b200 import ops
 
-    states = fill_engine(engine, batch, context)
-    for _ in range(warmup):
-        engine.step()
-    torch.cuda.synchronize()
-    # device-timed
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches0 = ops.launch_count
-    start.record()
-    for _ in range(steps):
-        engine.step()
-    end.record()
-    torch.cuda.synchronize()
-    dev_ms = start.elapsed_time(end) / steps
-    launches = (ops.launch_count - launches0) / steps
-    # end to end (wall clock around the public step call, host tokens in and out)
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        engine.step()
-    torch.cuda.synchronize()
-    wall_ms = (time.perf_counter() - t0) * 1000 / steps
-    h2d = engine.runner.last_h2d_bytes
-    d2h = engine.runner.sampled.numel() * 4 + 4      # the sampled-token snapshot and the status word
-    drain(engine, states)
-    return dev_ms, wall_ms, launches, h2d, d2h
+    dev, wall = [], []
+    launches = h2d = d2h = 0
+    for _ in range(reps):
+        states = fill_engine(engine, batch, context)
+        for _ in range(warmup):
+            engine.step()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = ops.launch_count
+        t0 = time.perf_counter()
+        start.record()
+        for _ in range(steps):
+            engine.step()
+        end.record()
+        torch.cuda.synchronize()
+        wall.append((time.perf_counter() - t0) * 1000 / steps)
+        dev.append(start.elapsed_time(end) / steps)
+        launches = (ops.launch_count - launches0) / steps
+        h2d = engine.runner.last_h2d_bytes
+        d2h = engine.runner.sampled.numel() * 4 + 4      # the sampled-token snapshot and the status word
+        drain(engine, states)
+    dev.sort()
+    wall.sort()
+    return dev[len(dev) // 2], wall[len(wall) // 2], launches, h2d, d2h
 
 
 def time_prefill(engine, tokens: int, repeats: int, warmup: int):
+    """One request of ``tokens`` prompt tokens and one generated token, ``repeats`` times.  Returns the
+    medians (device ms, end-to-end ms).  Device: events around the step, behind a spin kernel of about a
+    millisecond so that the host's share of the step (schedule, metadata, launch) is over when the start
+    event fires; it holds the copy of the metadata.  End to end: the host clock from ``submit`` to the
+    sampled token in host memory, no spin kernel."""
     import torch
 
     from gllm_b200 import GenerationRequest
 
     g = torch.Generator().manual_seed(1)
     vocab = engine.config.vocab_size
-    times = []
+
+    def request():
+        return GenerationRequest(prompt_token_ids=torch.randint(0, vocab, (tokens,), generator=g).tolist(),
+                                 max_new_tokens=1, temperature=0.0, ignore_eos=True)
+
+    dev, e2e = [], []
     for it in range(warmup + repeats):
-        req = GenerationRequest(prompt_token_ids=torch.randint(0, vocab, (tokens,), generator=g).tolist(),
-                                max_new_tokens=1, temperature=0.0, ignore_eos=True)
-        st = engine._make_state(req)
-        engine.scheduler.add(st)
+        req = request()
         torch.cuda.synchronize()
+        st = engine.submit(req)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        # the GPU spins for about a millisecond first, so that the host's share of the step (schedule,
-        # metadata, launch) is over when the start event fires: the events bracket the device's time for
-        # the step, its copy of the metadata included
         torch.cuda._sleep(3_000_000)
         start.record()
         engine.step()
@@ -239,9 +242,57 @@ def time_prefill(engine, tokens: int, repeats: int, warmup: int):
         engine.step()          # greedy steps are pipelined: this call reads the timed step's token
         assert st.is_finished, "the prefill step did not finish the one-token request"
         if it >= warmup:
-            times.append(start.elapsed_time(end))
-    times.sort()
-    return times[len(times) // 2]
+            dev.append(start.elapsed_time(end))
+    for it in range(warmup + repeats):
+        req = request()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        st = engine.submit(req)
+        while not st.is_finished:
+            engine.step()
+        ms = (time.perf_counter() - t0) * 1000
+        if it >= warmup:
+            e2e.append(ms)
+    dev.sort()
+    e2e.sort()
+    return dev[len(dev) // 2], e2e[len(e2e) // 2]
+
+
+BENCH_SIZES = dict(context=2048, max_seq_len=4096, block_size=16, prefill_tokens=2048, full_layers=16)
+
+
+def bench_config(raw: dict, batch: int, peaks: dict, sampling: str) -> dict:
+    """The flat ``config`` record both arms print."""
+    return {
+        "model": "llama-3.2-1b sizes",
+        "layers": raw["num_hidden_layers"],
+        "layers_of_full_model": BENCH_SIZES["full_layers"],
+        "hidden": raw["hidden_size"],
+        "heads": raw["num_attention_heads"],
+        "kv_heads": raw["num_key_value_heads"],
+        "head_dim": raw["head_dim"],
+        "intermediate": raw["intermediate_size"],
+        "vocab": raw["vocab_size"],
+        "global_batch": batch,
+        "seq_len": BENCH_SIZES["context"],
+        "max_seq_len": BENCH_SIZES["max_seq_len"],
+        "block_size": BENCH_SIZES["block_size"],
+        "prefill_tokens": BENCH_SIZES["prefill_tokens"],
+        "parallelism": "single GPU",
+        "l2": "inputs larger than L2 (2.47 GB of weights per step)",
+        "sampling": sampling,
+        "peaks": peaks["source"],
+        "repetitions": "median of 5",
+    }
+
+
+def raw_model_config(num_layers: int | None) -> dict:
+    from gllm_b200.config.presets import load_preset
+
+    raw = load_preset("llama-3.2-1b")
+    if num_layers is not None:
+        raw["num_hidden_layers"] = num_layers
+    return raw
 
 
 def run_ours(args) -> dict:
@@ -250,12 +301,12 @@ def run_ours(args) -> dict:
     from gllm_b200 import GeneratorParams, LLMEngine
 
     peaks = load_peaks()
-    context, max_seq_len, block_size, prefill_tokens = 2048, 4096, 16, 2048
-    full_layers = 16
-    layers = args.layers or full_layers
+    context, max_seq_len = BENCH_SIZES["context"], BENCH_SIZES["max_seq_len"]
+    block_size, prefill_tokens = BENCH_SIZES["block_size"], BENCH_SIZES["prefill_tokens"]
+    layers = args.layers or BENCH_SIZES["full_layers"]
     tmp = tempfile.mkdtemp(prefix="gllm_b200_bench_")
     try:
-        folder = make_model_folder(tmp, layers if layers != full_layers else None)
+        folder = make_model_folder(tmp, layers if layers != BENCH_SIZES["full_layers"] else None)
         params = GeneratorParams(block_size=block_size, max_batch_size=64, max_seq_len=max_seq_len,
                                  model_dtype="bfloat16", max_num_batched_tokens=8192, prefill_chunk=2048)
         engine = LLMEngine(folder, params, device="cuda:0")
@@ -264,30 +315,40 @@ def run_ours(args) -> dict:
     cfg = engine.config
     wbytes = weight_bytes(engine)
     kv_per_token = engine.cache.bytes_per_token()
+    steps = args.steps
+    reps = 5
 
-    points = {}
+    def step_bytes(b):
+        return wbytes + b * (context + args.warmup + steps // 2) * kv_per_token
+
+    points, points_ms, rooflines, e2e_points = {}, {}, {}, {}
     for b in (1, 64):
-        dev_ms, _, _, _, _ = time_decode(engine, b, context, max(8, args.steps // 4), args.warmup)
+        dev_ms, wall_ms, _, _, _ = time_decode(engine, b, context, steps, args.warmup, reps)
         points[f"decode_b{b}"] = round(b * 1000.0 / dev_ms, 1)
+        points_ms[f"decode_b{b}"] = round(dev_ms, 4)
+        e2e_points[f"decode_b{b}"] = round(b * 1000.0 / wall_ms, 1)
+        rooflines[f"decode_b{b}"] = round(step_bytes(b) / (dev_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
 
-    prefill_ms = time_prefill(engine, prefill_tokens, repeats=5, warmup=max(3, args.warmup))
+    prefill_ms, prefill_e2e_ms = time_prefill(engine, prefill_tokens, repeats=5, warmup=max(3, args.warmup))
     pf_flops = prefill_flops(cfg, prefill_tokens)
 
     sampler = ClockSampler(0)
     sampler.start()
     batch = 8
-    dev_ms, wall_ms, launches, h2d, d2h = time_decode(engine, batch, context, args.steps, args.warmup)
+    dev_ms, wall_ms, launches, h2d, d2h = time_decode(engine, batch, context, steps, args.warmup, reps)
     clocks = sampler.stop()
 
-    step_bytes = wbytes + batch * (context + args.warmup + args.steps // 2) * kv_per_token
-    achieved = step_bytes / (dev_ms * 1e-3) / 1e9
+    achieved = step_bytes(batch) / (dev_ms * 1e-3) / 1e9
     value = batch * 1000.0 / dev_ms
+    rooflines["decode_b8"] = round(achieved / peaks["hbm_gbs"], 4)
+    points_ms["decode_b8"] = round(dev_ms, 4)
+    e2e_points["decode_b8"] = round(batch * 1000.0 / wall_ms, 1)
     record = {
         "metric": "decode tok/s at batch 8 (Llama 3.2 1B sizes, random bf16 weights, 2,048 cached tokens)",
         "value": round(value, 1),
         "unit": "tokens/s",
         "n_gpus": 1,
-        "steps": args.steps,
+        "steps": steps,
         "warmup": args.warmup,
         "ms_per_step": round(dev_ms, 4),
         "higher_is_better": True,
@@ -295,39 +356,22 @@ def run_ours(args) -> dict:
         "vs_baseline": None,
         "dtype": "bf16",
         "data": "synthetic: uniform random token ids, random N(0,0.02) weights (seed 0)",
-        "config": {
-            "model": "llama-3.2-1b sizes",
-            "layers": cfg.num_hidden_layers,
-            "layers_of_full_model": full_layers,
-            "hidden": cfg.hidden_size,
-            "heads": cfg.num_attention_heads,
-            "kv_heads": cfg.num_key_value_heads,
-            "head_dim": cfg.head_dim,
-            "intermediate": cfg.intermediate_size,
-            "vocab": cfg.vocab_size,
-            "global_batch": batch,
-            "seq_len": context,
-            "max_seq_len": max_seq_len,
-            "block_size": block_size,
-            "prefill_tokens": prefill_tokens,
-            "parallelism": "single GPU",
-            "l2": "inputs larger than L2 (2.47 GB of weights per step)",
-            "sampling": "greedy, inside the step",
-            "peaks": peaks["source"],
-        },
+        "config": bench_config(cfg.to_dict(), batch, peaks, "greedy, inside the step"),
         "e2e": {
             "value": round(batch * 1000.0 / wall_ms, 1),
             "unit": "tokens/s",
             "h2d_bytes_per_step": int(h2d),
             "d2h_bytes_per_step": int(d2h),
         },
-        "gpu_launches": int(round(launches * args.steps)),
+        "gpu_launches": int(round(launches * steps)),
         "clocks": clocks,
         "prefill": {
             "value": round(prefill_tokens * 1000.0 / prefill_ms, 1),
             "tokens": prefill_tokens,
             "ms": round(prefill_ms, 4),
             "frac": round(pf_flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4),
+            "e2e_ms": round(prefill_e2e_ms, 4),
+            "e2e_value": round(prefill_tokens * 1000.0 / prefill_e2e_ms, 1),
         },
         "roofline": {
             "bound": "hbm",
@@ -337,18 +381,29 @@ def run_ours(args) -> dict:
             "frac": round(achieved / peaks["hbm_gbs"], 4),
         },
         "points": points,
+        "points_ms_per_step": points_ms,
+        "points_e2e": e2e_points,
+        "points_roofline_frac": rooflines,
     }
     return record
 
 
 def run_reference(args) -> dict:
-    return {
-        "impl": "reference",
-        "unavailable": (
-            "pip install of the reference into baseline/_ref installs no modules (its setup.py uses find_packages() "
-            "and the tree has no __init__.py), and its engine downloads a gated checkpoint from the hub at construction"
-        ),
-    }
+    sys.path.insert(0, ROOT)
+    from baseline import reference_arm
+    from gllm_b200.config import load_config
+
+    raw = raw_model_config(args.layers)
+    args.prefill_flops = prefill_flops(load_config(dict(raw)), BENCH_SIZES["prefill_tokens"])
+    args.warmup_prefill = 3
+    peaks = load_peaks()
+    try:
+        return reference_arm.run(args, peaks, raw, ClockSampler, BENCH_SIZES, bench_config)
+    except Exception as e:      # noqa: BLE001 - the arm reports why it has no number instead of failing the run
+        import traceback
+
+        traceback.print_exc()
+        return {"impl": "reference", "unavailable": f"{type(e).__name__}: {e}"[:300]}
 
 
 def main() -> int:
@@ -367,13 +422,15 @@ def main() -> int:
         overrides = {k: int(v) for k, v in (kv.split("=") for kv in args.shape.split(",") if kv)}
         print(json.dumps(kernel_bench.run(args.kernel, load_peaks(), overrides)))
         return 0
-    if args.impl == "reference":
-        print(json.dumps(run_reference(args)))
-        return 0
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: this engine does not run on {args.gpus} GPUs")
         return 2
     args.warmup = max(3, args.warmup)
+    # a repetition's context grows from `context + warmup` to `context + warmup + steps` tokens
+    args.steps = max(1, min(args.steps, BENCH_SIZES["max_seq_len"] - BENCH_SIZES["context"] - args.warmup - 2))
+    if args.impl == "reference":
+        print(json.dumps(run_reference(args)))
+        return 0
     print(json.dumps(run_ours(args)))
     return 0
 

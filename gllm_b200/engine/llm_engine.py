@@ -244,13 +244,36 @@ class LLMEngine(LLMEngineBase):
         """Run ``reqs`` to completion; results in the order of ``reqs``.  More
         requests than ``max_batch_size`` are fine: the surplus waits its turn."""
         states = [self._make_state(r) for r in reqs]
-        for s in states:
-            self.scheduler.add(s)
-        while not all(s.is_finished for s in states):
-            self.step()
-            if not self.scheduler.has_work and self._pending is None:
-                break
+        added = []
+        try:
+            for s in states:
+                self.scheduler.add(s)
+                added.append(s)
+            while not all(s.is_finished for s in states):
+                self.step()
+                if not self.scheduler.has_work and self._pending is None:
+                    break
+        except BaseException:
+            # a refused request, or a step that raised: nothing of this call stays queued or holds pages
+            for s in added:
+                self.scheduler.abort(s.id)
+            if not self.scheduler.has_work:
+                self._pending = None
+            raise
         return [self._create_result(s) for s in states]
+
+    def submit(self, req: GenerationRequest) -> RequestState:
+        """Queue one request without running anything; ``step()`` runs it.  Returns its state
+        (``id``, ``generated_token_ids``, ``is_finished``).  Raises ValueError for a request that can
+        never run."""
+        state = self._make_state(req)
+        self.scheduler.add(state)
+        return state
+
+    def abort(self, request_id) -> bool:
+        """End a waiting or running request now: its pages and its slot are free at once, a token
+        of it that is still in flight is dropped.  False when no such request is live."""
+        return self.scheduler.abort(request_id)
 
     # --------------------------------------------------- continuous batching
     def enqueue_request(self, req: GenerationRequest) -> asyncio.Future:
@@ -298,6 +321,7 @@ class LLMEngine(LLMEngineBase):
         """The serving loop (call it on a thread of its own): admit what was
         enqueued, run a step, resolve the futures of finished requests."""
         self.alive = True
+        error: BaseException | None = None
         try:
             while self.alive:
                 self._drain_queue(blocking=not self.scheduler.has_work and self._pending is None)
@@ -307,8 +331,32 @@ class LLMEngine(LLMEngineBase):
                     if state.future is not None:
                         fut, loop = state.future
                         self._resolve(fut, loop, result=self._create_result(state))
+        except BaseException as e:
+            error = e
+            raise
         finally:
             self.alive = False
+            self._fail_outstanding(error)
+
+    def _fail_outstanding(self, error: BaseException | None) -> None:
+        """The serving loop has ended (``stop()`` or an exception): every request that is still
+        queued, waiting or running gets the error on its future (nobody awaits for ever), and
+        gives back its pages and its slot."""
+        reason = error if isinstance(error, Exception) else RuntimeError("the engine was stopped")
+        self._pending = None
+        while True:
+            try:
+                _, fut, loop = self.request_queue.get_nowait()
+            except queue.Empty:
+                break
+            self._resolve(fut, loop, error=reason)
+        for state in list(self.scheduler.waiting) + list(self.scheduler.running):
+            self.scheduler.abort(state.id)
+            if state.future is not None:
+                fut, loop = state.future
+                self._resolve(fut, loop, error=reason)
 
     def stop(self) -> None:
+        """Ends ``run()`` after the step it is in; requests that are not finished by then get a
+        RuntimeError on their futures."""
         self.alive = False
