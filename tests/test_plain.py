@@ -1,9 +1,12 @@
 """The plain implementation itself (no GPU): against the outputs of the
-reference's own model code on tiny model A (tests/golden, made by
+reference's own model code on the tiny models A and B (tests/golden, made by
 tests/golden/make_golden.py), and its parts against known values.
 
-llama3 frequency scaling and the untied head are absent from the reference, so
-they rest on their published formulas; everything else of tiny A is anchored."""
+A is anchored whole, token by token from the reference's cache, and for requests
+that arrive beside decoding neighbours.  B is anchored in everything but the two
+things the reference lacks: the llama3 scaling rule (the reference ran with a
+table of angles made from the plain frequencies) and the choice of an untied head
+matrix; those two are held by the property tests below."""
 
 import json
 import math
@@ -38,6 +41,73 @@ def test_plain_equals_the_reference_model_code(tmp_path):
         for t in meta["greedy"][i]:
             assert int(plain_forward(cfg, weights, tokens, torch.float64)[-1].argmax()) == t
             tokens.append(t)
+
+
+def _golden(name):
+    with open(os.path.join(GOLDEN, f"{name}.json")) as f:
+        meta = json.load(f)
+    return load_file(os.path.join(GOLDEN, f"{name}.safetensors")), meta
+
+
+def test_plain_equals_the_reference_decoding_token_by_token_and_mixed_arrival(tmp_path):
+    golden, meta = _golden("tiny_a_reference")
+    cfg, weights = read_raw(write_tiny("A", str(tmp_path / "m")))
+    prompts, conts = meta["prompts"], meta["continuations"]
+    # the reference decoded the continuation of prompt 2 one token at a time from its cache
+    whole = plain_forward(cfg, weights, prompts[2] + conts[2], torch.float32)
+    want = golden["decode_2"]
+    assert want.shape[0] == len(conts[2])
+    assert float((whole[len(prompts[2]):] - want).abs().max()) < 5e-6
+    # arrivals: request i joins at step i with its whole prompt, then brings its fixed tokens one by one
+    fed = [0, 0, 0]
+    for s, active in enumerate(meta["mixed_schedule"]):
+        for i in active:
+            n_prompt = len(prompts[i])
+            seq = prompts[i] + conts[i][:fed[i]]
+            logits = plain_forward(cfg, weights, seq, torch.float32)
+            want = golden[f"mixed_{s}_{i}"]
+            got = logits if fed[i] == 0 else logits[-1:]
+            assert got.shape == want.shape and (fed[i] > 0 or got.shape[0] == n_prompt)
+            assert float((got - want).abs().max()) < 5e-6, (s, i)
+            fed[i] += 1
+
+
+def test_plain_equals_the_reference_on_tiny_b_with_its_table_and_head_put_in(tmp_path):
+    golden, meta = _golden("tiny_b_reference")
+    cfg, weights = read_raw(write_tiny("B", str(tmp_path / "m")))
+    assert cfg["rope_scaling"]["rope_type"] == "llama3" and not cfg["tie_word_embeddings"]
+    for i, prompt in enumerate(meta["prompts"]):
+        got = plain_forward(cfg, weights, prompt, torch.float32)
+        want = golden[f"logits_{i}"]
+        assert got.shape == want.shape
+        assert float((got - want).abs().max()) < 1e-5, i
+    seq = meta["prompts"][3] + meta["continuation"]
+    got = plain_forward(cfg, weights, seq, torch.float32)[len(meta["prompts"][3]):]
+    assert float((got - golden["decode_3"]).abs().max()) < 1e-5
+    assert float(golden["decode_3"].abs().max()) > 0.1              # the comparison is not of zeros
+
+
+def test_llama3_rule_is_continuous_monotone_and_has_the_stated_limits():
+    """The rule's published meaning, checked as properties over a dense sweep of
+    wavelengths instead of the few frequencies a head size gives: short waves
+    untouched, long waves slowed by ``factor``, a straight blend in between
+    that meets both ends, and a larger factor never speeds a frequency up."""
+    for factor, low, high, orig in ((8.0, 1.0, 4.0, 64.0), (32.0, 1.0, 4.0, 8192.0)):
+        d = 4096
+        cfg = dict(head_dim=d, hidden_size=d, num_attention_heads=1, rope_theta=500000.0,
+                   rope_scaling=dict(rope_type="llama3", factor=factor, low_freq_factor=low, high_freq_factor=high,
+                                     original_max_position_embeddings=orig))
+        f = plain_inverse_frequencies(cfg)
+        base = plain_inverse_frequencies({k: v for k, v in cfg.items() if k != "rope_scaling"})
+        wl = 2 * math.pi / base
+        ratio = f / base
+        assert torch.equal(ratio[wl < orig / high], torch.ones_like(ratio[wl < orig / high]))
+        torch.testing.assert_close(ratio[wl > orig / low], torch.full_like(ratio[wl > orig / low], 1 / factor))
+        assert (ratio[1:] <= ratio[:-1] + 1e-12).all()                # longer waves are slowed at least as much
+        assert float((ratio[1:] - ratio[:-1]).abs().max()) < 0.01     # no jump at either edge of the blend
+        mid = (wl >= orig / high) & (wl <= orig / low)
+        smooth = (orig / wl[mid] - low) / (high - low)                # 1 at the short edge, 0 at the long edge
+        torch.testing.assert_close(ratio[mid], (1 - smooth) / factor + smooth)
 
 
 def test_llama3_frequencies_hit_all_three_branches():
