@@ -374,14 +374,20 @@ GLLM_API int gllm_attention_decode_bf16_noalloc(const __nv_bfloat16* q, int64_t 
                                                 int block_size, int num_pages, int num_chunks, float scale,
                                                 int window, int* status, cudaStream_t stream) {
   if (num_queries <= 0) return 0;
-  if (hq <= 0 || d <= 0 || num_chunks <= 0) return (int)cudaErrorInvalidValue;
+  // Bound every factor before multiplying, and test the limit by division: the product of
+  // unchecked arguments could wrap around and pass.
+  if ((d != 32 && d != 64 && d != 128) || hq <= 0 || hkv <= 0 || hq % hkv || num_chunks <= 0 ||
+      num_queries > 65535)
+    return (int)cudaErrorInvalidValue;
+  const int64_t per_chunk = (int64_t)num_queries * hq * (d + 2);          // <= 65535 * 2^31 * 130 < 2^63
+  if ((int64_t)num_chunks > (int64_t)GLLM_DECODE_NOALLOC_MAX_FLOATS / per_chunk) return (int)cudaErrorInvalidValue;
   const int64_t o_floats = (int64_t)num_queries * hq * num_chunks * d;
-  const int64_t ml_floats = (int64_t)num_queries * hq * num_chunks * 2;
-  if (o_floats + ml_floats > (int64_t)GLLM_DECODE_NOALLOC_MAX_FLOATS) return (int)cudaErrorInvalidValue;
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
   if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return (int)cudaErrorInvalidDevice;
+  // The cache is written without a lock: two threads that race here both look the address up and
+  // both store the same value.
   if (!g_decode_noalloc_ptr[dev]) {
     float* p = nullptr;
     e = cudaGetSymbolAddress((void**)&p, g_decode_noalloc_scratch);

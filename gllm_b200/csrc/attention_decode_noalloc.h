@@ -6,10 +6,9 @@
 //
 // Who needs it: code that runs where cudaMalloc is not an option.  Examples are
 // a host callback or a plugin inside someone else's runtime that owns all
-// device memory and forbids further allocations, a region of code that is
-// being recorded into a CUDA graph or runs right after a device-wide memory
-// budget was fixed, and a latency-critical loop in which an allocation (which
-// may synchronise the whole device) is not acceptable.  The ordinary entry
+// device memory and forbids further allocations, code that runs after a
+// device-wide memory budget was fixed, and a latency-critical loop in which an
+// allocation (which may synchronise the whole device) is not acceptable.  The ordinary entry
 // point, gllm_attention_decode_bf16, asks its caller for two scratch buffers
 // for the per-chunk partial results; such callers have nowhere to get them from.
 //
@@ -24,9 +23,12 @@
 //    that loads this library holds that much until the process exits.
 //    A call needs  num_queries * hq * num_chunks * (d + 2)  floats;
 //    a call that needs more returns cudaErrorInvalidValue (1) and launches nothing.
+//  * The device that ``stream`` belongs to must be the current device of the
+//    calling thread: the array's address is looked up, and remembered, for the
+//    current device.
 //  * The first call on a device looks up the array's device address
-//    (cudaGetSymbolAddress) with that device current.  Make that first call
-//    before any stream capture begins.
+//    (cudaGetSymbolAddress).  Make that first call before any stream capture
+//    begins.
 //  * All calls share the one array and it keeps the previous call's contents.
 //    Nothing in it has to start at zero: every entry a call reads was written by
 //    that call first.  Two calls whose kernels overlap on the GPU (different

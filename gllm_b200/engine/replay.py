@@ -7,8 +7,17 @@ import json
 import os
 import sys
 
-REPLAY_PAGE_TOKENS = 16      # tokens per cache page; divides the 64-token rounding of --max-tokens
+REPLAY_PAGE_TOKENS = 16      # default tokens per cache page; divides the 64-token rounding of --max-tokens
 MAX_LIVE_REQUESTS = 4
+
+
+def check_block_size(block_size: int) -> int:
+    """``--max-tokens`` counts every request rounded up to 64 tokens (to the page, for larger pages):
+    the pool of ``max_tokens // block_size`` pages holds that exactly when the page divides 64 or is a
+    multiple of it."""
+    if block_size <= 0 or (64 % block_size and block_size % 64):
+        raise ValueError(f"--block-size {block_size}: a page must divide 64 tokens or be a multiple of 64")
+    return block_size
 
 
 def build_runner(model_dir: str, dtype: str, max_tokens: int, block_size: int = REPLAY_PAGE_TOKENS,
@@ -21,6 +30,7 @@ def build_runner(model_dir: str, dtype: str, max_tokens: int, block_size: int = 
 
     if not torch.cuda.is_available():
         raise RuntimeError("no CUDA device: this engine runs on a GPU only")
+    check_block_size(block_size)
     config, model = load_model(model_dir, dtype, device)
     num_blocks = max(1, max_tokens // block_size)
     cache = CacheManager(
@@ -43,12 +53,18 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", required=True, type=int,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
+    ap.add_argument("--block-size", type=int, default=REPLAY_PAGE_TOKENS,
+                    help="tokens per cache page (default 16); divides 64 or is a multiple of it")
     args = ap.parse_args(argv)
+    try:
+        check_block_size(args.block_size)
+    except ValueError as e:
+        ap.error(str(e))
 
     from gllm_b200.engine.step import StepEntry
 
     os.makedirs(args.out, exist_ok=True)
-    _, runner = build_runner(args.model, args.dtype, args.max_tokens)
+    _, runner = build_runner(args.model, args.dtype, args.max_tokens, block_size=args.block_size)
     for line in sys.stdin:
         line = line.strip()
         if not line:

@@ -119,8 +119,9 @@ def plain_mlp(x, w, prefix):
 
 
 # ---------------------------------------------------------------------- model
-def plain_forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, plan=None) -> torch.Tensor:
-    """Logits [T, V] of one whole sequence.
+def plain_forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, plan=None, rows=None) -> torch.Tensor:
+    """Logits [T, V] of one whole sequence (with ``rows``: only at those positions, [len(rows), V];
+    the sequence is still run whole).
 
     x = E[tokens]  (gllm/model/model.py:175-182); per layer
     x = x + attn(norm_in(x)); x = x + mlp(norm_post(x))  (the deferred adds of
@@ -152,6 +153,8 @@ def plain_forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, plan=No
         x = x + a
         h = plain_rmsnorm(x, w[f"{p}.post_attention_layernorm.weight"], eps)
         x = x + plain_mlp(h, w, f"{p}.mlp")
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long)]
     x = plain_rmsnorm(x, w["model.norm.weight"], eps)
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return x @ head.T

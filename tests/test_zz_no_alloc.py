@@ -1,6 +1,8 @@
 """The decode attention entry point for callers that cannot allocate device memory
 (gllm_b200/csrc/attention_decode_noalloc.h), called through its exported C symbol and
-compared with the ordinary entry point, which takes its scratch from the caller.
+compared with the ordinary entry point, which takes its scratch from the caller, and
+with a plain float64 attention over the same pages (a fault both entry points share
+would pass the first comparison).
 
 Such callers (a plugin inside a runtime that owns all device memory, code between the
 fixing of a memory budget and the end of the process, a loop that cannot afford an
@@ -52,6 +54,21 @@ def _case(seed, batch, context, hq, hkv, d, block_size):
     return pool, table, q, positions, rows
 
 
+def _plain(pool, table, q, positions, hq, hkv, d, scale):
+    """Plain attention of each query over keys 0 .. its position, gathered page by page."""
+    pool, table, q = pool.double().cpu(), table.cpu().long(), q.double().cpu()
+    out = []
+    for b in range(q.shape[0]):
+        n = int(positions[b]) + 1
+        k = pool[table[b], 0].permute(0, 2, 1, 3).reshape(-1, hkv, d)[:n]      # [tokens, hkv, d]
+        v = pool[table[b], 1].permute(0, 2, 1, 3).reshape(-1, hkv, d)[:n]
+        k = k.repeat_interleave(hq // hkv, 1)
+        v = v.repeat_interleave(hq // hkv, 1)
+        scores = torch.einsum("hd,khd->hk", q[b, : hq * d].view(hq, d), k) * scale
+        out.append(torch.einsum("hk,khd->hd", scores.softmax(-1), v).reshape(hq * d))
+    return torch.stack(out)
+
+
 def test_no_alloc_entry_point_equals_the_ordinary_one_twice_in_a_row():
     noalloc, ordinary, chunk_of = _library()
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -79,6 +96,8 @@ def test_no_alloc_entry_point_equals_the_ordinary_one_twice_in_a_row():
         assert not got.float().isnan().any()
         torch.testing.assert_close(got.float(), want.float(), rtol=2e-2, atol=2e-2)
         assert torch.equal(got, want)            # the same kernels: in fact bit for bit
+        plain = _plain(pool, table, q, positions, hq, pool.shape[2], d, scale)
+        torch.testing.assert_close(got.double().cpu(), plain, rtol=2e-2, atol=2e-2)
 
 
 def test_no_alloc_entry_point_refuses_what_does_not_fit():
@@ -91,5 +110,12 @@ def test_no_alloc_entry_point_refuses_what_does_not_fit():
                    table.shape[1], positions.data_ptr(), rows.data_ptr(), 2, 4, 2, 64, 16, pool.shape[0],
                    too_many_chunks, 0.125, 0, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
     assert code == 1                             # cudaErrorInvalidValue: nothing was launched
+    # sizes whose product wraps around 64 bits must not slip under the limit
+    for nq, heads, chunks, hd in [(65535, 1024, 2 ** 31 - 1, 128), (2 ** 31 - 1, 2 ** 31 - 2, 2 ** 31 - 1, 64),
+                                  (2, 4, 1, 2 ** 30), (2, 2 ** 31 - 2, 2 ** 31 - 1, 128)]:
+        code = noalloc(q.data_ptr(), q.shape[1], out.data_ptr(), out.shape[1], pool.data_ptr(), table.data_ptr(),
+                       table.shape[1], positions.data_ptr(), rows.data_ptr(), nq, heads, 2, hd, 16, pool.shape[0],
+                       chunks, 0.125, 0, status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert code == 1, (nq, heads, chunks, hd)
     torch.cuda.synchronize()
     assert float(out.float().abs().sum()) == 0
