@@ -12,8 +12,10 @@ The reference has one pool for all layers, sized so it can never run short,
 and keeps block tables in the runner (gllm/model/kv_cache/paged_kv_cache.py:30-57,
 gllm/llm/llm.py:71-82,163-231).
 
-Pool layout per group: ``[cache_layers, pages, 2 (k|v), kv_heads, block_size,
-head_dim]``: one (page, head) is one contiguous chunk.
+Pool layout per group: ``[cache_layers, pages, block_size * elements per
+token]``; inside a page the tensors a mixer declared lie one after the other,
+each ``[heads, block_size, width]`` (for attention: ``[2 (k|v), kv_heads,
+block_size, head_dim]``, one (page, head) being one contiguous chunk).
 """
 
 from __future__ import annotations
@@ -35,7 +37,7 @@ class CacheGroup:
     allocator: BlockAllocator
     # plan entries that own a pool layer in this group, in plan order
     owner_entries: list[int] = field(default_factory=list)
-    pool: torch.Tensor | None = None           # [layers, pages, 2, hkv, bs, d]
+    pool: torch.Tensor | None = None           # [layers, pages + 1, block_size * elements_per_token]
     block_table: torch.Tensor | None = None    # device [max_batch, max_blocks] int32
     block_table_host: np.ndarray | None = None
     dirty_rows: set = field(default_factory=set)
@@ -121,7 +123,7 @@ class CacheManager:
             # Rows that pad a batch to a fixed size store there and read from there.
             if allocate_pools:
                 g.pool = torch.zeros(
-                    (len(g.owner_entries), self.num_blocks + 1, 2, r.num_kv_heads, self.block_size, r.head_dim),
+                    (len(g.owner_entries), self.num_blocks + 1, self.block_size * r.elements_per_token),
                     dtype=dtype, device=self.device,
                 )
             # One row more than there are state slots: the *null row* (index max_batch_size),
@@ -144,9 +146,7 @@ class CacheManager:
     # ------------------------------------------------------------- accounting
     def bytes_per_token(self) -> int:
         item = torch.empty((), dtype=self.dtype).element_size()
-        return sum(
-            2 * g.requirement.num_kv_heads * g.requirement.head_dim * item * len(g.owner_entries) for g in self.groups
-        )
+        return sum(g.requirement.elements_per_token * item * len(g.owner_entries) for g in self.groups)
 
     def num_free_pages(self, group: int = 0) -> int:
         return self.groups[group].allocator.num_free if self.groups else 0
@@ -174,6 +174,11 @@ class CacheManager:
 
     def pages_for_tokens(self, n_tokens: int) -> int:
         return -(-n_tokens // self.block_size)
+
+    def pages_for_admission(self, n_tokens: int) -> dict[int, int]:
+        """Pages each group needs for the first ``n_tokens`` tokens of a request that holds nothing yet
+        (a window group gives pages back only after the step that stored them)."""
+        return {g.index: -(-n_tokens // g.block_size) for g in self.groups}
 
     def can_append(self, request_id, n_new: int) -> bool:
         rc = self.requests[request_id]
@@ -294,7 +299,9 @@ class CacheManager:
             pages = None
             if g is not None and self.groups[g].pool is not None:
                 pages = self.groups[g].pool[self._entry_layer[idx]]
-            out.append(MixerCache(group=g, pages=pages, writes=self._entry_writes[idx], state=self._states[idx]))
+            out.append(MixerCache(group=g, pages=pages, writes=self._entry_writes[idx], state=self._states[idx],
+                                  requirement=None if g is None else self.groups[g].requirement,
+                                  block_size=self.block_size))
         return out
 
     # ---------------------------------------------------------------- checking

@@ -54,7 +54,7 @@ static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const int* __restrict__ sampled,
                                  const int* __restrict__ token_row, const T* __restrict__ table,
-                                 float* __restrict__ resid, int n_tokens, int hidden, int vocab,
+                                 float* __restrict__ resid, int n_tokens, int hidden, int vocab, float scale,
                                  int* __restrict__ status) {
   pdl_trigger();
   pdl_wait();
@@ -66,14 +66,14 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const int* __re
   if (!ok && threadIdx.x == 0) atomicOr(status, GLLM_STATUS_TOKEN_RANGE);
   const T* row = table + (size_t)(ok ? tok : 0) * hidden;
   float* dst = resid + (size_t)n * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? to_float(row[i]) : 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = ok ? to_float(row[i]) * scale : 0.f;
 }
 
 template <typename T>
 __global__ void embedding_wide_kernel(const int* __restrict__ tokens, const int* __restrict__ sampled,
                                       const int* __restrict__ token_row, const T* __restrict__ table,
                                       float* __restrict__ resid, int n_tokens, int hidden, int vocab,
-                                      int* __restrict__ status) {
+                                      float scale, int* __restrict__ status) {
   pdl_trigger();
   pdl_wait();
   const int n = blockIdx.x;
@@ -86,37 +86,57 @@ __global__ void embedding_wide_kernel(const int* __restrict__ tokens, const int*
   for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
     float v[8];
     Vec8<T>::load(row + c, v);
-    if (!ok) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = 0.f;
-    }
+    for (int i = 0; i < 8; ++i) v[i] = ok ? v[i] * scale : 0.f;
     Vec8<float>::store(dst + c, v);
   }
 }
 
 template <typename T>
 static int embedding_launch(const int* tokens, const int* sampled, const int* token_row, const T* table,
-                            float* resid, int n_tokens, int hidden, int vocab, int* status,
+                            float* resid, int n_tokens, int hidden, int vocab, float scale, int* status,
                             cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
   if (hidden % 8 == 0 && aligned16(table) && aligned16(resid))
     return gllm_launch(embedding_wide_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, tokens, sampled,
-                       token_row, table, resid, n_tokens, hidden, vocab, status);
+                       token_row, table, resid, n_tokens, hidden, vocab, scale, status);
   return gllm_launch(embedding_kernel<T>, dim3(n_tokens), dim3(threads), 0, stream, tokens, sampled, token_row,
-                     table, resid, n_tokens, hidden, vocab, status);
+                     table, resid, n_tokens, hidden, vocab, scale, status);
 }
 
+// `scale` multiplies every looked-up row (1 for an architecture without an embedding multiplier).
 GLLM_API int gllm_embedding_f32(const int* tokens, const int* sampled, const int* token_row, const float* table,
-                                float* resid, int n_tokens, int hidden, int vocab, int* status,
+                                float* resid, int n_tokens, int hidden, int vocab, float scale, int* status,
                                 cudaStream_t stream) {
-  return embedding_launch<float>(tokens, sampled, token_row, table, resid, n_tokens, hidden, vocab, status, stream);
+  return embedding_launch<float>(tokens, sampled, token_row, table, resid, n_tokens, hidden, vocab, scale, status,
+                                 stream);
 }
 GLLM_API int gllm_embedding_bf16(const int* tokens, const int* sampled, const int* token_row,
                                  const __nv_bfloat16* table, float* resid, int n_tokens, int hidden, int vocab,
-                                 int* status, cudaStream_t stream) {
-  return embedding_launch<__nv_bfloat16>(tokens, sampled, token_row, table, resid, n_tokens, hidden, vocab, status,
-                                         stream);
+                                 float scale, int* status, cudaStream_t stream) {
+  return embedding_launch<__nv_bfloat16>(tokens, sampled, token_row, table, resid, n_tokens, hidden, vocab, scale,
+                                         status, stream);
+}
+
+// ------------------------------------------------- logit scale and soft cap
+// x = x * scale; then, with cap > 0, x = cap * tanh(x / cap).  fp32, in place, over n values.
+__global__ void scale_softcap_kernel(float* __restrict__ x, int64_t n, float scale, float cap) {
+  pdl_trigger();
+  pdl_wait();
+  const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float v = x[i] * scale;
+    if (cap > 0.f) v = cap * tanhf(v * inv_cap);
+    x[i] = v;
+  }
+}
+GLLM_API int gllm_scale_softcap_f32(float* x, int64_t n, float scale, float cap, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int threads = 256;
+  const int64_t blocks = (n + threads - 1) / threads;
+  return gllm_launch(scale_softcap_kernel, dim3((unsigned)(blocks < 4096 ? blocks : 4096)), dim3(threads), 0, stream,
+                     x, n, scale, cap);
 }
 
 // ------------------------------------------------------ add + RMSNorm (fused)

@@ -74,10 +74,10 @@ class Scheduler:
             raise ValueError("max_new_tokens must be > 0.")
         req.max_new_tokens = min(allowed, req.max_new_tokens)
         worst = n_prompt + req.max_new_tokens
-        if self.cache.pages_for_tokens(worst) > self.cache.num_blocks:
+        worst_pages = max(self.cache.pages_for_admission(worst).values(), default=0)
+        if worst_pages > self.cache.num_blocks:
             raise ValueError(
-                f"the request may grow to {worst} tokens = {self.cache.pages_for_tokens(worst)} pages, "
-                f"the pool has {self.cache.num_blocks}"
+                f"the request may grow to {worst} tokens = {worst_pages} pages, the pool has {self.cache.num_blocks}"
             )
         req.status = RequestStatus.WAITING
         req.arrival = self._arrivals
@@ -175,7 +175,7 @@ class Scheduler:
             if self.cache.slots.num_free - new_slots <= 0:
                 break
             n = min(req.num_tokens, self.params.prefill_chunk, budget)
-            need = {g: self.cache.pages_for_tokens(n) for g in groups}
+            need = self.cache.pages_for_admission(n)
             if not fits(need):
                 break
             promise(req, need)

@@ -17,17 +17,24 @@ from gllm_b200.parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, build_part
 from gllm_b200.parts.base import Block, MixerCache, Norm, StepContext, TensorExpectation
 
 
+_TABLE_OF_KIND = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS}
+
+
 def _build_layer(layer_spec) -> Block:
+    """The registered block of ``layer_spec.block`` with the parts it declares, each built from the
+    spec of the same name."""
     try:
         block_cls = BLOCKS[layer_spec.block]
     except KeyError:
         raise KeyError(f"no block of kind {layer_spec.block!r} is registered; known: {sorted(BLOCKS)}") from None
-    return block_cls(
-        build_part(MIXERS, layer_spec.mixer),
-        build_part(FEED_FORWARDS, layer_spec.feed_forward),
-        build_part(NORMS, layer_spec.mixer_norm),
-        build_part(NORMS, layer_spec.feed_forward_norm),
-    )
+    declared = block_cls.part_kinds
+    missing = [n for n in declared if n not in layer_spec.parts]
+    extra = [n for n in layer_spec.parts if n not in declared]
+    if missing or extra:
+        raise ValueError(f"block {layer_spec.block!r} declares parts {list(declared)}: the layer lacks {missing} "
+                         f"and names {extra} beyond them")
+    return block_cls(**{name: build_part(_TABLE_OF_KIND[kind], layer_spec.parts[name])
+                        for name, kind in declared.items()})
 
 
 def expected_tensors_of_spec(spec: ModelSpec) -> dict[str, TensorExpectation]:
@@ -63,7 +70,7 @@ class DecoderModel:
         """True when every part (the mixers' position encodings included) may have its prompt portions
         captured in a CUDA graph (``Part.graph_safe_portions``)."""
         parts = [self.final_norm] + [p for block in self.layers for p in [block] + block.parts()]
-        parts += [m.position for m in (b.mixer for b in self.layers) if getattr(m, "position", None) is not None]
+        parts += [p.position for p in list(parts) if getattr(p, "position", None) is not None]
         return all(getattr(p, "graph_safe_portions", False) for p in parts)
 
     # ---------------------------------------------------------------- weights
@@ -93,9 +100,21 @@ class DecoderModel:
         reads_cache_of | None)."""
         out = []
         for entry in self.spec.plan:
-            mixer = self.layers[entry.layer].mixer
-            out.append((mixer.kv_requirement(), mixer.state_requirement(), entry.reads_cache_of))
+            mixer = self.layers[entry.layer].cache_mixer()
+            if mixer is None:
+                out.append((None, None, entry.reads_cache_of))
+            else:
+                out.append((mixer.kv_requirement(), mixer.state_requirement(), entry.reads_cache_of))
         return out
+
+    def kernel_needs(self) -> dict:
+        """Union of what the parts will ask of the kernel modules (``Part.kernel_needs``)."""
+        needs: dict = {}
+        parts = [self.final_norm] + [p for block in self.layers for p in block.parts()]
+        for part in parts:
+            for key, values in part.kernel_needs().items():
+                needs.setdefault(key, set()).update(values)
+        return needs
 
     # ---------------------------------------------------------------- forward
     def forward(
@@ -107,11 +126,16 @@ class DecoderModel:
         logits_out: torch.Tensor | None = None,
     ) -> torch.Tensor:
         """Logits ``[len(logit_rows), vocab]`` fp32 of the flat batch ``tokens``."""
-        resid = ops.embedding(tokens, self.embedding, sampled=ctx.sampled, token_row=ctx.token_row)
+        resid = ops.embedding(tokens, self.embedding, sampled=ctx.sampled, token_row=ctx.token_row,
+                              scale=1.0 if self.spec.embedding_scale is None else self.spec.embedding_scale)
         branch = None
         for entry_idx, entry in enumerate(self.spec.plan):
             branch, resid = self.layers[entry.layer].forward(branch, resid, ctx, caches[entry_idx])
         if logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         final = self.final_norm.forward(branch, resid, self.dtype, rows=logit_rows)
-        return ops.linear(final, self.head, out_dtype=torch.float32, out=logits_out)
+        logits = ops.linear(final, self.head, out_dtype=torch.float32, out=logits_out)
+        if self.spec.logit_scale is not None or self.spec.logit_softcap is not None:
+            ops.scale_softcap(logits, 1.0 if self.spec.logit_scale is None else self.spec.logit_scale,
+                              self.spec.logit_softcap)
+        return logits

@@ -13,7 +13,7 @@ from __future__ import annotations
 
 from dataclasses import asdict
 
-from gllm_b200.config.model_config import LlamaConfig
+from gllm_b200.config.llama_config import LlamaConfig
 from gllm_b200.config.registry import register_architecture
 from gllm_b200.models.spec import LayerSpec, ModelSpec, PartSpec, PlanEntry
 
@@ -61,13 +61,12 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
         )
         norm = dict(size=cfg.hidden_size, eps=cfg.rms_norm_eps)
         layers.append(
-            LayerSpec(
-                block="prenorm",
-                mixer=mixer,
-                feed_forward=ffn,
+            LayerSpec("prenorm", dict(
                 mixer_norm=PartSpec("rmsnorm", norm, {"weight": f"{p}.input_layernorm.weight"}),
+                mixer=mixer,
                 feed_forward_norm=PartSpec("rmsnorm", norm, {"weight": f"{p}.post_attention_layernorm.weight"}),
-            )
+                feed_forward=ffn,
+            ))
         )
     return ModelSpec(
         hidden_size=cfg.hidden_size,

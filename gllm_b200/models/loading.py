@@ -28,7 +28,6 @@ def load_model(folder: str, dtype: str | None = None, device: str | torch.device
         # the kernels this model will ask for are compiled now, side by side, if they are not built yet
         from gllm_b200 import ops
 
-        head_dims = {int(m.head_dim) for m in (b.mixer for b in model.layers) if hasattr(m, "head_dim")}
-        ops.prepare(model.dtype, head_dims)
+        ops.prepare(model.dtype, model.kernel_needs().get("attention_head_dims", ()))
     model.load(open_checkpoint(folder))
     return config, model

@@ -29,13 +29,22 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: how its parts are arranged (``block``) and the parts."""
+    """One layer: how its parts are arranged (``block``, a registered block
+    kind) and the parts, by the names that block kind declares
+    (``Block.part_kinds``).  The built-in pre-norm block declares ``mixer_norm``,
+    ``mixer``, ``feed_forward_norm`` and ``feed_forward``; a block with one
+    shared norm, with norms after its branches or without a feed-forward
+    declares other names and needs no change here."""
 
     block: str
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    parts: dict[str, PartSpec] = field(default_factory=dict)
+
+    def __getattr__(self, name: str) -> PartSpec:
+        # spec.mixer, spec.feed_forward_norm ...: the part of that name
+        parts = object.__getattribute__(self, "parts")
+        if name in parts:
+            return parts[name]
+        raise AttributeError(name)
 
 
 @dataclass(frozen=True)
@@ -64,6 +73,12 @@ class ModelSpec:
     embedding_name: str
     head_name: str | None
     eos_token_ids: tuple[int, ...] = ()
+    # Optional constants around the layer stack (none of them is Llama's): the looked-up embedding
+    # rows are multiplied by ``embedding_scale``; the logits are multiplied by ``logit_scale`` and
+    # then capped softly, ``cap * tanh(logits / cap)``.
+    embedding_scale: float | None = None
+    logit_scale: float | None = None
+    logit_softcap: float | None = None
     # Tensor names that a checkpoint may hold and the model does not read
     # (for instance a stored head beside tied embeddings).
     ignorable_names: tuple[str, ...] = ()

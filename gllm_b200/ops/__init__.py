@@ -22,6 +22,7 @@ __all__ = [
     "ExtensionError",
     "build_all",
     "embedding",
+    "scale_softcap",
     "add_rmsnorm",
     "silu_mul",
     "rope_store",
@@ -40,7 +41,8 @@ __all__ = [
 P = c_void_p
 _SIGNATURES = {
     "elementwise": {
-        "gllm_embedding_{t}": [P, P, P, P, P, c_int, c_int, c_int, P, P],
+        "gllm_embedding_{t}": [P, P, P, P, P, c_int, c_int, c_int, c_float, P, P],
+        "gllm_scale_softcap_f32": [P, c_int64, c_float, c_float, P],
         "gllm_add_rmsnorm_{t}": [P, P, c_int, c_int64, P, P, P, P, c_int, c_int, c_float, c_int, P],
         "gllm_sum_parts_{t}": [P, c_int, c_int64, P, c_int64, P],
         "gllm_silu_mul_{t}": [P, P, c_int, c_int, c_int, P],
@@ -195,12 +197,29 @@ class SplitSum:
     """The result of a product that was cut along K and whose ``splits`` fp32
     partial results ``parts [splits, rows, cols]`` were left unsummed: the
     kernel that consumes it (``add_rmsnorm``, ``rope_store``) adds them in
-    ascending order, which saves a reduction pass.  ``parts`` lives in shared
-    scratch: consume a SplitSum before the next product runs."""
+    ascending order, which saves a reduction pass.  ``parts`` lives in one of
+    two scratch buffers that the products take in turn: it survives the next
+    product and is overwritten by the one after.  Consume a SplitSum (or call
+    ``as_tensor`` on it) before two more products have run; reading it later
+    raises."""
 
-    def __init__(self, parts: torch.Tensor, dtype: torch.dtype):
+    def __init__(self, parts: torch.Tensor, dtype: torch.dtype, generation: int | None = None):
         self.parts = parts
         self.dtype = dtype
+        # the count of scratch-taking products on the device when this one ran (None: the parts are
+        # the caller's own memory)
+        self.generation = generation
+
+    def check_alive(self) -> None:
+        if self.generation is None:
+            return
+        from gllm_b200.ops import gemm_bf16
+
+        now = gemm_bf16.scratch_generation(self.parts.device)
+        if now - self.generation > 1:
+            raise RuntimeError(
+                f"an unsummed product was read after {now - self.generation} further products: its partial sums "
+                "have been overwritten (sum it with ops.as_tensor before running two more products)")
 
     @property
     def shape(self):
@@ -212,6 +231,7 @@ class SplitSum:
 
     def tensor(self, out: torch.Tensor | None = None) -> torch.Tensor:
         """The summed result as an ordinary tensor of ``dtype`` (into ``out``, contiguous, when given)."""
+        self.check_alive()
         if out is None:
             out = torch.empty(tuple(self.shape), dtype=self.dtype, device=self.parts.device)
         f = _fn("elementwise", f"gllm_sum_parts_{_suffix(self.dtype)}")
@@ -227,14 +247,17 @@ def as_tensor(x):
 
 def _parts_args(x):
     if isinstance(x, SplitSum):
+        x.check_alive()
         return x.parts.data_ptr(), x.parts.shape[0], x.parts.stride(0)
     return None, 0, 0
 
 
 # ---------------------------------------------------------------- embedding
 def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None,
-              sampled: torch.Tensor | None = None, token_row: torch.Tensor | None = None) -> torch.Tensor:
-    """fp32 residual rows ``table[tokens]`` (gllm/model/model.py:175-182).
+              sampled: torch.Tensor | None = None, token_row: torch.Tensor | None = None,
+              scale: float = 1.0) -> torch.Tensor:
+    """fp32 residual rows ``table[tokens] * scale`` (gllm/model/model.py:175-182; the reference has
+    no multiplier).
 
     With ``sampled`` and ``token_row``: a negative token id stands for
     ``sampled[token_row[i]]``, the token the previous step's argmax left on the
@@ -252,8 +275,17 @@ def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor | Non
         _cuda(out, "out", torch.float32)
     f = _fn("elementwise", f"gllm_embedding_{_suffix(table.dtype)}")
     _check(f(tokens.data_ptr(), _ptr(sampled), _ptr(token_row) if sampled is not None else None, table.data_ptr(),
-             out.data_ptr(), n, hidden, vocab, status_word(table.device).data_ptr(), _stream()), "embedding")
+             out.data_ptr(), n, hidden, vocab, float(scale), status_word(table.device).data_ptr(), _stream()),
+           "embedding")
     return out
+
+
+def scale_softcap(logits: torch.Tensor, scale: float = 1.0, cap: float | None = None) -> torch.Tensor:
+    """In place on fp32 ``logits``: multiply by ``scale``, then with ``cap``: ``cap * tanh(x / cap)``."""
+    _cuda(logits, "logits", torch.float32)
+    f = _fn("elementwise", "gllm_scale_softcap_f32")
+    _check(f(logits.data_ptr(), logits.numel(), float(scale), float(cap or 0.0), _stream()), "scale_softcap")
+    return logits
 
 
 # ------------------------------------------------------------- add + RMSNorm

@@ -6,8 +6,7 @@ aligned and whose inner size is a multiple of 8; decode steps (M <= 64) run it
 with the weight as the 128-row operand and split along K.  Anything else (odd
 inner sizes) goes to the library product (cuBLAS through ``torch.matmul``),
 which is what the reference uses for every projection
-(gllm/model/layers/linear.py:20).  ``set_backend("library")`` sends everything
-there, for comparisons.
+(gllm/model/layers/linear.py:20).
 """
 
 from __future__ import annotations
@@ -22,20 +21,8 @@ from gllm_b200.ops.build import load_module
 P = c_void_p
 FEW_TOKENS = 64
 
-_BACKEND = "tcgen05"
 _umma = None
 _scratch: dict[int, dict[str, torch.Tensor]] = {}
-
-
-def set_backend(name: str) -> None:
-    global _BACKEND
-    if name not in ("tcgen05", "library"):
-        raise ValueError("backend must be 'tcgen05' or 'library'")
-    _BACKEND = name
-
-
-def get_backend() -> str:
-    return _BACKEND
 
 
 def _umma_fns():
@@ -61,7 +48,8 @@ def _device_scratch(device: torch.device, partial_floats: int, tickets: int):
     buffers used in turn, so an unsummed result survives the next product) and
     the ticket counters (zeroed once; the kernel leaves them at zero)."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    s = _scratch.setdefault(idx, {"turn": 0, "retired": []})
+    s = _scratch.setdefault(idx, {"turn": 0, "retired": [], "generation": 0})
+    s["generation"] += 1
 
     def grow(name, numel, make):
         # a buffer that is outgrown stays allocated: a captured graph may hold its address, and memory
@@ -78,6 +66,15 @@ def _device_scratch(device: torch.device, partial_floats: int, tickets: int):
         # 148 items of 128 x 256 (the most a product is cut into) fit without growing
         grow(name, max(partial_floats, 148 * 128 * 256), lambda n: torch.empty(n, dtype=torch.float32, device=device))
     return s[name], s["tickets"]
+
+
+def scratch_generation(device: torch.device) -> int:
+    """How many products have taken a scratch buffer on ``device`` so far.  An unsummed result
+    (``ops.SplitSum``) lives in the buffer of the product that made it, which the product after the
+    next one overwrites: a SplitSum remembers the generation it was made in and refuses to be read
+    once two more products have run."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    return _scratch.get(idx, {}).get("generation", 0)
 
 
 _pair = None
@@ -154,7 +151,8 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
                  weight.stride(0), n, splits, partial.data_ptr(), tickets.data_ptr(), 0,
                  ops.status_word(x.device).data_ptr(), ops._stream())
         ops._check(code, "gemm_bf16")
-        return ops.SplitSum(partial[: splits * m * n].view(splits, m, n), out.dtype).tensor(out)
+        return ops.SplitSum(partial[: splits * m * n].view(splits, m, n), out.dtype,
+                            scratch_generation(x.device)).tensor(out)
     code = f(x.data_ptr(), weight.data_ptr(), out.data_ptr(), int(out.dtype == torch.float32), m, n, k,
              x.stride(0), weight.stride(0), out.stride(0), splits, partial.data_ptr(), tickets.data_ptr(), 1,
              ops.status_word(x.device).data_ptr(), ops._stream())
@@ -167,7 +165,7 @@ def linear_split(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype):
     when it would not (or does not take these operands)."""
     from gllm_b200 import ops
 
-    if _BACKEND != "tcgen05" or not tensor_core_kernel_takes(x, weight):
+    if not tensor_core_kernel_takes(x, weight):
         return None
     f, splits_of, tiles_of, _ = _umma_fns()
     m, k = x.shape
@@ -180,11 +178,11 @@ def linear_split(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype):
              weight.stride(0), n, splits, partial.data_ptr(), tickets.data_ptr(), 0,
              ops.status_word(x.device).data_ptr(), ops._stream())
     ops._check(code, "gemm_bf16")
-    return ops.SplitSum(partial[: splits * m * n].view(splits, m, n), out_dtype)
+    return ops.SplitSum(partial[: splits * m * n].view(splits, m, n), out_dtype, scratch_generation(x.device))
 
 
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    if _BACKEND == "tcgen05" and tensor_core_kernel_takes(x, weight):
+    if tensor_core_kernel_takes(x, weight):
         return linear_tcgen05(x, weight, out)
     if out.dtype == torch.bfloat16:
         torch.matmul(x, weight.t(), out=out)
@@ -200,7 +198,7 @@ def linear_gated(x: torch.Tensor, weight: torch.Tensor):
     from gllm_b200 import ops
 
     n, k = weight.shape
-    if _BACKEND != "tcgen05" or not tensor_core_kernel_takes(x, weight) or n % 128:
+    if not tensor_core_kernel_takes(x, weight) or n % 128:
         return None
     m = x.shape[0]
     out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)

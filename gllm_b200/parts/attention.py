@@ -49,7 +49,10 @@ class Attention(Mixer):
         self.w_o: torch.Tensor | None = None
 
     def kv_requirement(self):
-        return KVPageRequirement(self.num_kv_heads, self.head_dim, self.window)
+        return KVPageRequirement.keys_and_values(self.num_kv_heads, self.head_dim, self.window)
+
+    def kernel_needs(self):
+        return {"attention_head_dims": {self.head_dim}}
 
     def expected_tensors(self):
         qd, kd = self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
@@ -78,13 +81,14 @@ class Attention(Mixer):
             qkv = ops.as_tensor(qkv)
             self.position.apply(qkv, ctx, self.num_heads, self.num_kv_heads, self.head_dim)
         inv_freq, rotary_dim, interleaved = rotary if rotary is not None else (None, 0, False)
+        pages = cache.kv_pages()
         qkv = ops.rope_store(
             qkv, ctx.positions, inv_freq,
             view.slot_mapping if cache.writes else None,
-            cache.pages, self.num_heads, self.num_kv_heads, self.head_dim, rotary_dim, interleaved,
+            pages, self.num_heads, self.num_kv_heads, self.head_dim, rotary_dim, interleaved,
         )
         attn = ops.paged_attention(
-            qkv, cache.pages, view.block_table, ctx.positions, ctx.token_row, self.num_heads, self.scale,
+            qkv, pages, view.block_table, ctx.positions, ctx.token_row, self.num_heads, self.scale,
             window=self.window, batch=ctx,
         )
         return ops.linear(attn, self.w_o, split_ok=True)

@@ -44,12 +44,30 @@ class TensorExpectation:
 # ------------------------------------------------- what mixers ask of the cache
 @dataclass(frozen=True)
 class KVPageRequirement:
-    """Keys and values of every token (or of a trailing window of tokens)."""
+    """What a mixer keeps in cache pages for every token (or for a trailing
+    window of tokens): a tuple of tensors, each ``(heads, width)`` elements per
+    token.  Attention keeps two of equal shape (keys and values,
+    ``keys_and_values``); a mixer that caches one latent vector per token
+    declares ``((1, width),)``; keys and values of different widths are two
+    entries of different shape.  Inside a page the tensors lie one after the
+    other, each as ``[heads, block_size, width]``."""
 
-    num_kv_heads: int
-    head_dim: int
+    tensors: tuple[tuple[int, int], ...]
     # None: all tokens stay.  w: a token at position p needs positions > p - w.
     window: int | None = None
+
+    def __post_init__(self):
+        if not self.tensors or any(len(t) != 2 or t[0] <= 0 or t[1] <= 0 for t in self.tensors):
+            raise ValueError("a page requirement names at least one (heads, width) tensor of positive sizes")
+
+    @classmethod
+    def keys_and_values(cls, num_kv_heads: int, head_dim: int, window: int | None = None) -> "KVPageRequirement":
+        shape = (int(num_kv_heads), int(head_dim))
+        return cls((shape, shape), window)
+
+    @property
+    def elements_per_token(self) -> int:
+        return sum(h * w for h, w in self.tensors)
 
 
 @dataclass(frozen=True)
@@ -112,14 +130,40 @@ class MixerCache:
     """What one plan entry's mixer may touch of the cache."""
 
     group: int | None = None              # key into StepContext.groups
-    pages: torch.Tensor | None = None     # [pages, 2, kv_heads, block_size, head_dim]
+    pages: torch.Tensor | None = None     # [pages, block_size * elements_per_token]: this entry's pool layer
     writes: bool = True                   # False: attends over another entry's pages
     state: torch.Tensor | None = None     # [max_batch_size + 1, *StateRequirement.shape]; last row: padding rows
+    requirement: KVPageRequirement | None = None
+    block_size: int = 0
+
+    def tensor(self, index: int) -> torch.Tensor:
+        """The ``index``-th tensor the mixer declared, as a view ``[pages, heads, block_size, width]``
+        of the pool (token ``t`` of a page is ``[:, :, t]``)."""
+        before = sum(h * w for h, w in self.requirement.tensors[:index]) * self.block_size
+        heads, width = self.requirement.tensors[index]
+        return self.pages.as_strided(
+            (self.pages.shape[0], heads, self.block_size, width),
+            (self.pages.stride(0), self.block_size * width, width, 1),
+            self.pages.storage_offset() + before,
+        )
+
+    def kv_pages(self) -> torch.Tensor:
+        """``[pages, 2 (k|v), kv_heads, block_size, head_dim]`` for a mixer that declared
+        ``KVPageRequirement.keys_and_values``."""
+        t = self.requirement.tensors
+        if len(t) != 2 or t[0] != t[1]:
+            raise ValueError("this cache does not hold keys and values of equal shape")
+        return self.pages.view(self.pages.shape[0], 2, t[0][0], self.block_size, t[0][1])
 
 
 # ------------------------------------------------------------------ part bases
 class Part:
     """Base of all parts: named tensors in, device tensors held."""
+
+    def kernel_needs(self) -> dict:
+        """What the part will ask of the kernel modules, so that they can be compiled side by side
+        before the first step: ``{"attention_head_dims": {64}}`` for an attention mixer."""
+        return {}
 
     # True when ``forward`` takes everything that varies between steps of equal shape from device
     # memory (positions, lengths, slots: the tensors of the StepContext), never from its host-side
@@ -182,17 +226,35 @@ class FeedForward(Part):
 class Block(Part):
     """Arrangement of a layer's parts.  ``forward`` gets the previous layer's
     not yet added branch output and the fp32 residual stream, and returns its
-    own last branch output with the (updated in place) residual stream."""
+    own last branch output with the (updated in place) residual stream.
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+    A block kind declares the parts it is made of in ``part_kinds``: part name
+    -> "mixer" | "feed_forward" | "norm", in the order they are loaded.  The
+    decoder builds exactly those from a ``LayerSpec`` and hands them to the
+    constructor by name; each becomes an attribute.  A block holds at most one
+    mixer that asks for a cache (the plan gives every entry one cache)."""
+
+    part_kinds: dict[str, str] = {}
+
+    def __init__(self, **parts: Part):
         super().__init__()
-        self.mixer = mixer
-        self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+        missing = [n for n in self.part_kinds if n not in parts]
+        extra = [n for n in parts if n not in self.part_kinds]
+        if missing or extra:
+            raise ValueError(f"block {type(self).__name__}: missing parts {missing}, unexpected parts {extra}")
+        self._part_names = list(self.part_kinds)
+        for name in self._part_names:
+            setattr(self, name, parts[name])
 
     def parts(self) -> list[Part]:
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        return [getattr(self, n) for n in self._part_names]
+
+    def cache_mixer(self) -> "Mixer | None":
+        """The mixer whose cache requirement the plan entry serves (None: the block keeps nothing)."""
+        mixers = [p for p in self.parts() if isinstance(p, Mixer)]
+        if len(mixers) > 1:
+            raise ValueError("a block holds at most one mixer")
+        return mixers[0] if mixers else None
 
     def forward(self, branch, resid, ctx: StepContext, cache: MixerCache):
         raise NotImplementedError

@@ -15,6 +15,7 @@ from gllm_b200.parts.base import Block, register_block
 @register_block("prenorm")
 class PreNormBlock(Block):
     graph_safe_portions = True
+    part_kinds = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
 
     def forward(self, branch, resid, ctx, cache):
         x = self.mixer_norm.forward(branch, resid, ctx.dtype)

@@ -11,11 +11,11 @@ from gllm_b200.parts.base import KVPageRequirement, StateRequirement
 
 
 def manager(num_blocks=12, block_size=4, max_batch=3, window=None, two_groups=False, max_seq_len=None):
-    reqs = [(KVPageRequirement(2, 16, None), None, None), (KVPageRequirement(2, 16, None), None, None)]
+    reqs = [(KVPageRequirement.keys_and_values(2, 16, None), None, None), (KVPageRequirement.keys_and_values(2, 16, None), None, None)]
     if window is not None:
-        reqs.append((KVPageRequirement(2, 16, window), None, None))
+        reqs.append((KVPageRequirement.keys_and_values(2, 16, window), None, None))
     if two_groups:
-        reqs.append((KVPageRequirement(1, 32, None), None, None))
+        reqs.append((KVPageRequirement.keys_and_values(1, 32, None), None, None))
     return CacheManager(reqs, block_size, num_blocks, max_batch, max_seq_len or num_blocks * block_size,
                         torch.float32, "cpu", allocate_pools=False)
 
@@ -52,12 +52,13 @@ def test_layers_with_equal_needs_share_a_group():
     assert m.groups[0].owner_entries == [0, 1] and m.groups[1].window == 6
     caches = m.mixer_caches()
     assert [c.group for c in caches] == [0, 0, 1, 2]
-    m2 = CacheManager([(KVPageRequirement(2, 16), None, None), (KVPageRequirement(2, 16), None, 0)],
+    m2 = CacheManager([(KVPageRequirement.keys_and_values(2, 16), None, None), (KVPageRequirement.keys_and_values(2, 16), None, 0)],
                       4, 8, 2, 32, torch.float32, "cpu")
     c = m2.mixer_caches()
     assert c[1].group == 0 and not c[1].writes and c[0].writes
     assert c[1].pages.data_ptr() == c[0].pages.data_ptr()     # reads the other entry's pages
-    assert m2.groups[0].pool.shape == (1, 8 + 1, 2, 2, 4, 16)    # + the null page
+    assert m2.groups[0].pool.shape == (1, 8 + 1, 4 * 2 * 2 * 16)    # + the null page
+    assert c[0].kv_pages().shape == (8 + 1, 2, 2, 4, 16)
 
 
 def test_append_commit_free_and_slot_mapping():
@@ -120,7 +121,7 @@ def test_window_group_gives_pages_back_early():
 
 
 def test_state_slots_are_zeroed_and_stay_put():
-    reqs = [(None, StateRequirement((3,), torch.float32), None), (KVPageRequirement(1, 16), None, None)]
+    reqs = [(None, StateRequirement((3,), torch.float32), None), (KVPageRequirement.keys_and_values(1, 16), None, None)]
     m = CacheManager(reqs, 4, 8, 2, 32, torch.float32, "cpu")
     caches = m.mixer_caches()
     assert caches[0].state.shape == (2 + 1, 3) and caches[0].pages is None and caches[1].state is None

@@ -25,7 +25,7 @@ from gllm_b200.parts.base import KVPageRequirement
 def host_engine(step):
     params = GeneratorParams(block_size=4, max_batch_size=4, max_seq_len=32, num_blocks=16,
                              max_num_batched_tokens=16, prefill_chunk=8)
-    cache = CacheManager([(KVPageRequirement(1, 16), None, None)], 4, 16, 4, 32, torch.float32, "cpu",
+    cache = CacheManager([(KVPageRequirement.keys_and_values(1, 16), None, None)], 4, 16, 4, 32, torch.float32, "cpu",
                          allocate_pools=False)
     eng = object.__new__(LLMEngine)
     eng.gen_params = params

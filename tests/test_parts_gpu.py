@@ -113,7 +113,7 @@ def test_attention_part_in_portions(dtype, window):
     attn = build_part(MIXERS, spec)
     attn.load(getter(w, dtype), dtype, "cuda")
     req = attn.kv_requirement()
-    assert (req.num_kv_heads, req.head_dim, req.window) == (2, 32, window) and attn.state_requirement() is None
+    assert (req.tensors, req.window) == (((2, 32), (2, 32)), window) and attn.state_requirement() is None
     cache, runner = context_for([(req, None, None)], None, dtype)
     caches = cache.mixer_caches()
     xs = {"a": torch.randn(57, 96, generator=g).to(dtype), "b": torch.randn(31, 96, generator=g).to(dtype)}

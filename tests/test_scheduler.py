@@ -16,7 +16,7 @@ from gllm_b200.sampling import SamplingParams
 def setup(block_size=4, max_batch=4, max_seq_len=64, num_blocks=32, budget=16, chunk=8):
     params = GeneratorParams(block_size=block_size, max_batch_size=max_batch, max_seq_len=max_seq_len,
                              num_blocks=num_blocks, max_num_batched_tokens=budget, prefill_chunk=chunk)
-    cache = CacheManager([(KVPageRequirement(1, 16), None, None)], block_size, num_blocks, max_batch, max_seq_len,
+    cache = CacheManager([(KVPageRequirement.keys_and_values(1, 16), None, None)], block_size, num_blocks, max_batch, max_seq_len,
                          torch.float32, "cpu", allocate_pools=False)
     return params, cache, Scheduler(params, cache)
 

@@ -87,8 +87,10 @@ def register_toy():
                                           position=PartSpec("rotary", dict(head_dim=cfg.head_dim, theta=10000.0))),
                         {n: f"layers.1.self_attn.{n}_proj.weight" for n in "qkvo"})
         layers = (
-            LayerSpec("prenorm", toy, ffn("layers.0"), norm("layers.0.n1.weight"), norm("layers.0.n2.weight")),
-            LayerSpec("prenorm", attn, ffn("layers.1"), norm("layers.1.n1.weight"), norm("layers.1.n2.weight")),
+            LayerSpec("prenorm", dict(mixer=toy, feed_forward=ffn("layers.0"), mixer_norm=norm("layers.0.n1.weight"),
+                                      feed_forward_norm=norm("layers.0.n2.weight"))),
+            LayerSpec("prenorm", dict(mixer=attn, feed_forward=ffn("layers.1"), mixer_norm=norm("layers.1.n1.weight"),
+                                      feed_forward_norm=norm("layers.1.n2.weight"))),
         )
         return ModelSpec(hidden_size=h, vocab_size=cfg.vocab_size, layers=layers,
                          plan=(PlanEntry(0), PlanEntry(1), PlanEntry(0)),      # the toy layer runs twice: two states

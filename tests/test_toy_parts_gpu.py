@@ -106,8 +106,10 @@ def register_toys():
         dense = PartSpec("swiglu", dict(hidden_size=h, intermediate_size=cfg.intermediate_size),
                          {n: f"layers.1.mlp.{n}_proj.weight" for n in ("gate", "up", "down")})
         layers = (   # different feed-forwards in different layers of one model
-            LayerSpec("prenorm", attn("layers.0"), routed, norm("layers.0.n1.weight"), norm("layers.0.n2.weight")),
-            LayerSpec("prenorm", attn("layers.1"), dense, norm("layers.1.n1.weight"), norm("layers.1.n2.weight")),
+            LayerSpec("prenorm", dict(mixer=attn("layers.0"), feed_forward=routed, mixer_norm=norm("layers.0.n1.weight"),
+                                      feed_forward_norm=norm("layers.0.n2.weight"))),
+            LayerSpec("prenorm", dict(mixer=attn("layers.1"), feed_forward=dense, mixer_norm=norm("layers.1.n1.weight"),
+                                      feed_forward_norm=norm("layers.1.n2.weight"))),
         )
         return ModelSpec(hidden_size=h, vocab_size=cfg.vocab_size, layers=layers, plan=(PlanEntry(0), PlanEntry(1)),
                          final_norm=norm("norm.weight"), embedding_name="embed.weight", head_name="head.weight")
