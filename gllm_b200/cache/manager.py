@@ -40,7 +40,8 @@ class CacheGroup:
     pool: torch.Tensor | None = None           # [layers, pages + 1, block_size * elements_per_token]
     block_table: torch.Tensor | None = None    # device [max_batch, max_blocks] int32
     block_table_host: np.ndarray | None = None
-    dirty_rows: set = field(default_factory=set)
+    # (slot, first column, end column) ranges of block_table_host that the device copy lacks
+    dirty: list = field(default_factory=list)
 
     @property
     def window(self) -> int | None:
@@ -213,7 +214,7 @@ class CacheManager:
                 new = group.allocator.allocate(n)
                 blocks.extend(new)
                 group.block_table_host[rc.slot, first:first + n] = new
-                group.dirty_rows.add(rc.slot)
+                group.dirty.append((rc.slot, first, first + n))
             table = np.asarray(blocks, dtype=np.int64)
             pages = table[positions // self.block_size]
             if (pages < 0).any():
@@ -239,9 +240,9 @@ class CacheManager:
                     release.append(blocks[b])
                     blocks[b] = -1
                     group.block_table_host[rc.slot, b] = -1
+                    group.dirty.append((rc.slot, b, b + 1))
             if release:
                 group.allocator.free(release)
-                group.dirty_rows.add(rc.slot)
 
     def free_request(self, request_id) -> None:
         rc = self.requests.pop(request_id, None)
@@ -253,7 +254,7 @@ class CacheManager:
             n = len(rc.blocks[group.index])
             if n:
                 group.block_table_host[rc.slot, :n] = -1
-                group.dirty_rows.add(rc.slot)
+                group.dirty.append((rc.slot, 0, n))
         self.slots.free(rc.slot)
 
     def rollback(self, request_id, n_tokens_before: int) -> None:
@@ -268,27 +269,34 @@ class CacheManager:
                 group.allocator.free(extra)
             if len(blocks) > keep:
                 group.block_table_host[rc.slot, keep:len(blocks)] = -1
+                group.dirty.append((rc.slot, keep, len(blocks)))
                 del blocks[keep:]
-                group.dirty_rows.add(rc.slot)
 
     # ------------------------------------------------------------ device side
-    def flush_block_tables(self) -> int:
-        """Copy the rows that changed since the last flush to the device;
-        returns the bytes copied."""
-        copied = 0
+    def take_table_updates(self) -> dict[int, tuple[np.ndarray, np.ndarray]]:
+        """What the device copies of the block tables lack, per group: (flat indices ``slot *
+        max_blocks + column``, page ids), both int32, each entry once with its newest value.  The step
+        function uploads them with the step's metadata and scatters them on the device, so the host never
+        waits for a copy; the lists are cleared."""
+        out = {}
         for group in self.groups:
-            if not group.dirty_rows:
+            if not group.dirty:
                 continue
-            rows = sorted(group.dirty_rows)
-            group.dirty_rows.clear()
-            host = torch.from_numpy(group.block_table_host)
-            if len(rows) > 8:
-                group.block_table.copy_(host, non_blocking=False)
-                copied += host.numel() * 4
-            else:
-                for r in rows:
-                    group.block_table[r].copy_(host[r], non_blocking=False)
-                    copied += host.shape[1] * 4
+            width = self.max_blocks_per_request
+            spans = [np.arange(slot * width + a, slot * width + b, dtype=np.int32) for slot, a, b in group.dirty]
+            group.dirty.clear()
+            idx = np.unique(np.concatenate(spans))
+            out[group.index] = (idx, group.block_table_host.reshape(-1)[idx])
+        return out
+
+    def flush_block_tables(self) -> int:
+        """Bring the device copies of the block tables up to date with a blocking copy of the changed
+        entries (for callers without a step function); returns the bytes copied."""
+        copied = 0
+        for g, (idx, values) in self.take_table_updates().items():
+            table = self.groups[g].block_table.view(-1)
+            table[torch.from_numpy(idx.astype(np.int64)).to(table.device)] = torch.from_numpy(values).to(table.device)
+            copied += 8 * idx.size
         return copied
 
     def mixer_caches(self) -> list[MixerCache]:

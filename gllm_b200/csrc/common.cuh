@@ -87,6 +87,20 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 #include <stdlib.h>
+// Streaming multiprocessors of the current device (asked once; grid sizes and split counts follow it).
+static inline int gllm_sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0, count = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && count > 0)
+      n = count;
+    else
+      return 1;
+  }
+  return n;
+}
+
 static inline bool gllm_pdl_enabled() {
   static int on = -1;
   if (on < 0) {

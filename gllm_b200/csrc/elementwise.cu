@@ -119,6 +119,29 @@ GLLM_API int gllm_embedding_bf16(const int* tokens, const int* sampled, const in
                                          status, stream);
 }
 
+// ------------------------------------------------------------ int32 scatter
+// dst[idx[i]] = val[i] (block-table entries that changed since the last step; indices are distinct).
+__global__ void scatter_i32_kernel(int* __restrict__ dst, int64_t dst_size, const int* __restrict__ idx,
+                                   const int* __restrict__ val, int n, int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int64_t at = idx[i];
+    if (at < 0 || at >= dst_size) {
+      atomicOr(status, GLLM_STATUS_PAGE_RANGE);
+      continue;
+    }
+    dst[at] = val[i];
+  }
+}
+GLLM_API int gllm_scatter_i32(int* dst, int64_t dst_size, const int* idx, const int* val, int n, int* status,
+                              cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const int blocks = (n + 255) / 256;
+  return gllm_launch(scatter_i32_kernel, dim3(blocks < 1024 ? blocks : 1024), dim3(256), 0, stream, dst, dst_size,
+                     idx, val, n, status);
+}
+
 // ------------------------------------------------- logit scale and soft cap
 // x = x * scale; then, with cap > 0, x = cap * tanh(x / cap).  fp32, in place, over n values.
 __global__ void scale_softcap_kernel(float* __restrict__ x, int64_t n, float scale, float cap) {
@@ -406,7 +429,7 @@ static int sum_parts_launch(const float* parts, int n_parts, int64_t part_stride
                             cudaStream_t stream) {
   if (n <= 0) return 0;
   int blocks = (int)((n + 255) / 256);
-  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks > gllm_sm_count() * 8) blocks = gllm_sm_count() * 8;
   return gllm_launch(sum_parts_kernel<T>, dim3(blocks), dim3(256), 0, stream, parts, n_parts, part_stride, out, n);
 }
 GLLM_API int gllm_sum_parts_f32(const float* parts, int n_parts, int64_t part_stride, float* out, int64_t n,
@@ -468,13 +491,13 @@ static int silu_mul_launch(const T* gate_up, T* out, int n_rows, int inter, int 
   if (inter % 8 == 0 && block % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
     const size_t chunks = (size_t)n_rows * (inter / 8);
     int wide_blocks = (int)((chunks + 255) / 256);
-    if (wide_blocks > 148 * 16) wide_blocks = 148 * 16;
+    if (wide_blocks > gllm_sm_count() * 16) wide_blocks = gllm_sm_count() * 16;
     return gllm_launch(silu_mul_wide_kernel<T>, dim3(wide_blocks), dim3(256), 0, stream, gate_up, out, n_rows, inter,
                        block);
   }
   const size_t total = (size_t)n_rows * inter;
   int blocks = (int)((total + 255) / 256);
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > gllm_sm_count() * 16) blocks = gllm_sm_count() * 16;
   return gllm_launch(silu_mul_kernel<T>, dim3(blocks), dim3(256), 0, stream, gate_up, out, n_rows, inter, block);
 }
 GLLM_API int gllm_silu_mul_f32(const float* gate_up, float* out, int n_rows, int inter, int block,

@@ -413,15 +413,7 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int64_t ld
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-  }
-  return n;
-}
+int sm_count() { return gllm_sm_count(); }
 
 template <int BN, bool SWAPPED, typename OutT, bool GATED>
 int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int64_t ldx,
@@ -493,7 +485,7 @@ GLLM_API int gllm_gemm_bf16_splits(int M, int N, int K) {
   // k-blocks long, none empty
   int best = 1;
   for (int s = 2; s <= 16; ++s) {
-    if (tiles * s > 148 || s > limit || num_kb / s < 2) break;
+    if (tiles * s > gllm_sm_count() || s > limit || num_kb / s < 2) break;
     const int per = (num_kb + s - 1) / s;
     if (per * (s - 1) < num_kb) best = s;        // the last split is not empty
   }

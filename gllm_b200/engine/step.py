@@ -75,6 +75,8 @@ class StepRunner:
         self.max_tokens = int(max_tokens_per_step)
         n_groups = len(cache.groups)
         cap = _align4(self.max_tokens) * (5 + n_groups) + 4 * _align4(cache.max_batch_size + 1) + 64
+        # room for every entry of every block table (index and page id): the most a step can change
+        cap += 2 * n_groups * _align4((cache.max_batch_size + 1) * cache.max_blocks_per_request)
         self._capacity = cap
         self._pinned = [torch.empty(cap, dtype=torch.int32).pin_memory() if torch.cuda.is_available()
                         else torch.empty(cap, dtype=torch.int32) for _ in range(2)]
@@ -226,8 +228,16 @@ class StepRunner:
         put("row_slots", row_owner)
         for g in cache.groups:
             put(f"slotmap{g.index}", np.concatenate(slot_maps[g.index] + [null_slots]))
+        # block-table entries that changed since the last step ride along and are scattered on the device
+        table_updates = cache.take_table_updates()
+        for g, (idx, values) in table_updates.items():
+            put(f"table_idx{g}", idx)
+            put(f"table_val{g}", values)
         self._meta[:cursor].copy_(pinned[:cursor], non_blocking=True)
-        self.last_h2d_bytes = cursor * 4 + cache.flush_block_tables()
+        self.last_h2d_bytes = cursor * 4
+        for g in table_updates:
+            (i0, n), (v0, _) = views.pop(f"table_idx{g}"), views.pop(f"table_val{g}")
+            ops.scatter_int32(cache.groups[g].block_table, self._meta[i0:i0 + n], self._meta[v0:v0 + n])
 
         def dev(name):
             start, n = views[name]
@@ -313,7 +323,8 @@ class StepRunner:
 
     def run(self, entries: list[StepEntry], check: bool = True, greedy: bool = False) -> torch.Tensor:
         """Run one step; returns fp32 logits ``[wanted, vocab]`` on the device,
-        in the order of the entries and of their ``want`` lists.  With
+        in the order of the entries and of their ``want`` lists; they may lie in
+        a buffer that the next ``run`` overwrites (copy what has to outlive it).  With
         ``greedy`` the argmax of every wanted row is written to
         ``self.sampled[state slot of the row's request]`` (see ``snapshot``).
 
@@ -336,9 +347,14 @@ class StepRunner:
                 tokens, ctx, rows = self.build(entries, pad_tokens_to=key[1])
             key = key + (bool(greedy),)
             record = self._graphs.get(key)
+            # every graph writes its logits into the one workspace buffer (kept, not freed, when it is
+            # outgrown): a buffer of its own per captured key would add up to gigabytes at a large
+            # vocabulary
+            vocab = self.model.spec.vocab_size
+            logits_out = self.workspace.get("graph_logits", rows.numel() * vocab, torch.float32).view(-1, vocab)
             if record is None:
                 # first time: run it plainly (this is the step's result), then capture for later
-                logits = self.model.forward(tokens, ctx, self.mixer_caches, rows)
+                logits = self.model.forward(tokens, ctx, self.mixer_caches, rows, logits_out=logits_out)
                 if greedy:
                     ops.argmax(logits, out=self.sampled, scatter_index=self._row_slots)
                 torch.cuda.synchronize(self.device)
@@ -347,7 +363,7 @@ class StepRunner:
                     self._graph_pool = torch.cuda.graph_pool_handle()
                 launches_before = ops.launch_count
                 with torch.cuda.graph(graph, pool=self._graph_pool):
-                    g_logits = self.model.forward(tokens, ctx, self.mixer_caches, rows)
+                    g_logits = self.model.forward(tokens, ctx, self.mixer_caches, rows, logits_out=logits_out)
                     if greedy:
                         ops.argmax(g_logits, out=self.sampled, scatter_index=self._row_slots)
                 launches = ops.launch_count - launches_before

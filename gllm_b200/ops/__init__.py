@@ -23,6 +23,7 @@ __all__ = [
     "build_all",
     "embedding",
     "scale_softcap",
+    "scatter_int32",
     "add_rmsnorm",
     "silu_mul",
     "rope_store",
@@ -43,6 +44,7 @@ _SIGNATURES = {
     "elementwise": {
         "gllm_embedding_{t}": [P, P, P, P, P, c_int, c_int, c_int, c_float, P, P],
         "gllm_scale_softcap_f32": [P, c_int64, c_float, c_float, P],
+        "gllm_scatter_i32": [P, c_int64, P, P, c_int, P, P],
         "gllm_add_rmsnorm_{t}": [P, P, c_int, c_int64, P, P, P, P, c_int, c_int, c_float, c_int, P],
         "gllm_sum_parts_{t}": [P, c_int, c_int64, P, c_int64, P],
         "gllm_silu_mul_{t}": [P, P, c_int, c_int, c_int, P],
@@ -278,6 +280,19 @@ def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor | Non
              out.data_ptr(), n, hidden, vocab, float(scale), status_word(table.device).data_ptr(), _stream()),
            "embedding")
     return out
+
+
+def scatter_int32(dst: torch.Tensor, index: torch.Tensor, values: torch.Tensor) -> None:
+    """``dst.view(-1)[index[i]] = values[i]`` for int32 tensors (indices are distinct); an index
+    outside ``dst`` sets a status bit and is skipped."""
+    _cuda(dst, "dst", torch.int32)
+    _cuda(index, "index", torch.int32)
+    _cuda(values, "values", torch.int32)
+    if index.numel() != values.numel():
+        raise ValueError("index and values differ in length")
+    f = _fn("elementwise", "gllm_scatter_i32")
+    _check(f(dst.data_ptr(), dst.numel(), index.data_ptr(), values.data_ptr(), index.numel(),
+             status_word(dst.device).data_ptr(), _stream()), "scatter_int32")
 
 
 def scale_softcap(logits: torch.Tensor, scale: float = 1.0, cap: float | None = None) -> torch.Tensor:

@@ -63,8 +63,9 @@ def _device_scratch(device: torch.device, partial_floats: int, tickets: int):
     s["turn"] ^= 1
     name = f"partial{s['turn']}"
     if name not in s or s[name].numel() < partial_floats:
-        # 148 items of 128 x 256 (the most a product is cut into) fit without growing
-        grow(name, max(partial_floats, 148 * 128 * 256), lambda n: torch.empty(n, dtype=torch.float32, device=device))
+        # one item of 128 x 256 per SM (the most a product is cut into) fits without growing
+        sms = torch.cuda.get_device_properties(idx).multi_processor_count
+        grow(name, max(partial_floats, sms * 128 * 256), lambda n: torch.empty(n, dtype=torch.float32, device=device))
     return s[name], s["tickets"]
 
 
