@@ -93,6 +93,18 @@ class DecoderModel:
                 part.load(get, self.dtype, self.device)
         self.final_norm.load(get, self.dtype, self.device)
         self.head = self.embedding if self.spec.head_name is None else get(self.spec.head_name, "matrix")
+        if self.dtype == torch.bfloat16 and self.device.type == "cuda":
+            from gllm_b200.ops import gemm_bf16
+
+            gemm_bf16.set_weight_order(self.streamed_weights())
+
+    def streamed_weights(self) -> list:
+        """Every matrix a step multiplies by, in running order (``Part.streamed_weights``), the head last."""
+        out = []
+        for entry in self.spec.plan:
+            for part in self.layers[entry.layer].parts():
+                out += part.streamed_weights()
+        return out + [self.head]
 
     # ------------------------------------------------------------------ cache
     def cache_requirements(self):
@@ -133,7 +145,7 @@ class DecoderModel:
             branch, resid = self.layers[entry.layer].forward(branch, resid, ctx, caches[entry_idx])
         if logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
-        final = self.final_norm.forward(branch, resid, self.dtype, rows=logit_rows)
+        final = self.final_norm.forward(None if branch is ops.ADDED else branch, resid, self.dtype, rows=logit_rows)
         logits = ops.linear(final, self.head, out_dtype=torch.float32, out=logits_out)
         if self.spec.logit_scale is not None or self.spec.logit_softcap is not None:
             ops.scale_softcap(logits, 1.0 if self.spec.logit_scale is None else self.spec.logit_scale,

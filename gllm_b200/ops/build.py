@@ -58,6 +58,13 @@ class ExtensionError(RuntimeError):
     """A CUDA module could not be compiled or loaded."""
 
 
+def _flags() -> list[str]:
+    """NVCC_FLAGS plus what ``GLLM_B200_NVCC_EXTRA`` adds (for instance ``-DNAME=value`` of a tuning
+    constant a source file exposes); the library's name follows the flags."""
+    extra = os.environ.get("GLLM_B200_NVCC_EXTRA", "").split()
+    return NVCC_FLAGS + extra
+
+
 def _nvcc() -> str:
     cand = os.environ.get("GLLM_B200_NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.isfile(cand):
@@ -71,7 +78,7 @@ def _headers() -> list[Path]:
 
 def _digest(source: Path) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(_flags()).encode())
     for p in [source] + _headers():
         h.update(p.name.encode())
         h.update(p.read_bytes())
@@ -124,7 +131,7 @@ def compile_module(module: str, verbose: bool = True) -> Path:
     out_dir = _writable_dir()
     out = out_dir / f"gllm_{module}.{_digest(source)}.so"
     tmp_out = out_dir / f".{out.name}.{os.getpid()}.tmp"
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC_DIR), "-o", str(tmp_out), str(source)]
+    cmd = [_nvcc(), *_flags(), "-I", str(CSRC_DIR), "-o", str(tmp_out), str(source)]
     t0 = time.time()
     if verbose:
         print(f"[gllm_b200] compiling {source.name} for sm_100a ...", file=sys.stderr, flush=True)
@@ -157,7 +164,7 @@ def compile_module(module: str, verbose: bool = True) -> Path:
     os.replace(tmp_out, out)
     # libraries of older versions of this module's source are of no use any more
     for old in out_dir.glob(f"gllm_{module}.*.so"):
-        if old != out:
+        if old != out and not os.environ.get("GLLM_B200_NVCC_EXTRA"):
             try:
                 old.unlink()
             except OSError:

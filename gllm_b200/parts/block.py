@@ -9,6 +9,7 @@ the norm kernel that follows it.
 
 from __future__ import annotations
 
+from gllm_b200 import ops
 from gllm_b200.parts.base import Block, register_block
 
 
@@ -17,8 +18,20 @@ class PreNormBlock(Block):
     graph_safe_portions = True
     part_kinds = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
 
+    @staticmethod
+    def _normed(norm, part, branch, resid, ctx):
+        """norm(resid + branch) for ``part``: lazily (for the part's first product to fuse) when the
+        part takes that and nothing is left to add, else by the norm kernel."""
+        if branch is ops.ADDED:
+            branch = None
+        x = norm.forward_lazy(branch, resid, ctx.dtype) if part.accepts_lazy_input else None
+        return x if x is not None else norm.forward(branch, resid, ctx.dtype)
+
     def forward(self, branch, resid, ctx, cache):
-        x = self.mixer_norm.forward(branch, resid, ctx.dtype)
+        ctx.residual_sink = resid
+        x = self._normed(self.mixer_norm, self.mixer, branch, resid, ctx)
         mixed = self.mixer.forward(x, ctx, cache)
-        x = self.feed_forward_norm.forward(mixed, resid, ctx.dtype)
-        return self.feed_forward.forward(x, ctx), resid
+        x = self._normed(self.feed_forward_norm, self.feed_forward, mixed, resid, ctx)
+        out = self.feed_forward.forward(x, ctx)
+        ctx.residual_sink = None
+        return out, resid
