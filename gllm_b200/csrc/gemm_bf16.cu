@@ -27,17 +27,10 @@
 // status bit, stops issuing work, lets its copies in flight land (bounded
 // again), frees its tensor memory and returns.
 //
-// Two fusions for steps of few tokens (the few-token orientation only):
-//  * NORMED: the token operand is not read by TMA but built by the epilogue warps from the fp32
-//    residual stream: B = bf16(resid * norm_weight), written into shared memory in the layout TMA
-//    would have produced (rows of 128 bytes, 128-byte swizzle); the same warps sum each row's
-//    squares while the weight streams, and the epilogue scales token m's column by
-//    rsqrt(mean(resid[m]^2) + eps).  Since the product is linear this equals
-//    RMSNorm(resid) @ W^T and the norm kernel before the product disappears.
-//  * accumulate: the epilogue adds its (partial) tile into an fp32 matrix with red.global.add,
-//    so a product that ends a branch adds itself to the residual stream: no partial sums are
-//    written, and the norm after it reads the residual alone.  The order of these additions is
-//    not fixed, so results may differ in the last fp32 bit between runs.
+// accumulate (the few-token orientation only): the epilogue adds its (partial) tile into an fp32
+// matrix with red.global.add, so a product that ends a branch adds itself to the residual stream: no
+// partial sums are written, and the norm after it reads the residual alone.  The order of these
+// additions is not fixed, so results may differ in the last fp32 bit between runs.
 //
 // No TMA load here uses cluster multicast; every CTA fetches its own tiles.
 #include "umma_utils.cuh"
@@ -65,10 +58,6 @@ struct Shape {
   static constexpr int STAGES = (SMEM_BUDGET / STAGE) > GLLM_GEMM_MAX_STAGES ? GLLM_GEMM_MAX_STAGES : (SMEM_BUDGET / STAGE);
   static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;                // two accumulators; a power of two >= 32
   static constexpr int SMEM = STAGES * STAGE + 1024;                         // + slack to align the base
-  // NORMED: the token operand of a CTA's whole K range lives behind the ring, one tile per k-block
-  static constexpr int X_TILE = BN * BK * 2;
-  static constexpr int X_MAX_KB = 32;                                        // k-blocks of one CTA's K range
-  static constexpr int SMEM_NORMED = SMEM + X_MAX_KB * X_TILE;
 };
 
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
@@ -95,30 +84,17 @@ __device__ __forceinline__ Item item_of(int w, int tiles_a, int splits) {
 // GATED: the weight rows come in blocks of 64 gate rows followed by the 64 up rows of the same
 // features; the epilogue writes silu(gate) * up, [M, N/2] (gllm/model/layers/mlp.py:44-47), instead
 // of the [M, N] product.  Only with splits == 1.
-// What the NORMED and accumulate variants need beyond the plain product.
-struct FusedArgs {
-  const float* resid;       // NORMED: [M, K] fp32, the rows to norm
-  const float* norm_weight; // NORMED: [K]
-  float eps;
-  int unit_offset;          // NORMED: the weight is an offset from one
-  int accumulate;           // the epilogue adds into `out` (fp32) instead of storing
-};
-
-template <int BN, bool SWAPPED, typename OutT, bool GATED, bool NORMED>
+template <int BN, bool SWAPPED, typename OutT, bool GATED>
 __global__ void __launch_bounds__(THREADS, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  OutT* __restrict__ out, int M, int N, int K, int64_t ldo, int splits, int kb_per_split,
                  int tiles_a, int num_items, float* __restrict__ partial, int* __restrict__ tickets,
-                 int reduce_in_kernel, int* __restrict__ status, const char* __restrict__ prefetch_ptr,
-                 unsigned long long prefetch_bytes, const FusedArgs fused) {
+                 int reduce_in_kernel, int* __restrict__ status, int accumulate) {
   using S = Shape<BN>;
-  static_assert(!NORMED || (SWAPPED && BN <= 16), "the normed variant is the few-token orientation with up to 16 tokens");
   extern __shared__ unsigned char smem_dyn[];
   __shared__ __align__(8) uint64_t full_bar[S::STAGES], empty_bar[S::STAGES], tmem_full_bar[2], tmem_empty_bar[2];
-  __shared__ __align__(8) uint64_t x_ready_bar;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag, is_last;
-  __shared__ float row_ss[4][NORMED ? BN : 1];
 
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -134,7 +110,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       mbar_init(smem_addr(&tmem_full_bar[b]), 1);
       mbar_init(smem_addr(&tmem_empty_bar[b]), 4);      // one arrival per epilogue warp
     }
-    mbar_init(smem_addr(&x_ready_bar), 1);
     abort_flag = 0;
     is_last = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -176,36 +151,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const uint32_t s = it % S::STAGES, round = it / S::STAGES;
             const uint32_t bar = smem_addr(&full_bar[s]);
             const uint32_t dst = tile_base + s * S::STAGE;
-            // NORMED: only the weight travels by TMA (the token operand is built in shared memory)
-            const uint32_t stage_bytes = NORMED ? (uint32_t)S::STAGE_A : (uint32_t)(S::STAGE_A + S::STAGE_B);
             if (pass == 0) {
               if (round > 0) { more = false; break; }
-              mbar_expect_tx(bar, stage_bytes);
+              mbar_expect_tx(bar, (uint32_t)(S::STAGE_A + S::STAGE_B));
               tma_load_2d(dst + off_w, map_w, kb * BK, row_w, bar);
             } else if (round == 0) {
-              if (!NORMED) tma_load_2d(dst + off_x, map_x, kb * BK, row_x, bar);
+              tma_load_2d(dst + off_x, map_x, kb * BK, row_x, bar);
             } else {
               ok = mbar_wait(smem_addr(&empty_bar[s]), (round & 1u) ^ 1u, status, &abort_flag);
               if (!ok) break;
-              mbar_expect_tx(bar, stage_bytes);
+              mbar_expect_tx(bar, (uint32_t)(S::STAGE_A + S::STAGE_B));
               tma_load_2d(dst + off_w, map_w, kb * BK, row_w, bar);
-              if (!NORMED) tma_load_2d(dst + off_x, map_x, kb * BK, row_x, bar);
+              tma_load_2d(dst + off_x, map_x, kb * BK, row_x, bar);
             }
           }
-        }
-      }
-      if (prefetch_bytes && !abort_flag) {
-        // Every load of this launch has been requested.  What the next product will stream (its weight,
-        // which depends on nothing) is asked into L2 now, each CTA a slice: the requests queue behind this
-        // CTA's own loads and are served while this kernel drains and the next one is handed over, a
-        // stretch in which the memory would otherwise idle.
-        constexpr unsigned long long CHUNK = 32 * 1024;
-        const unsigned long long per = (((prefetch_bytes + gridDim.x - 1) / gridDim.x) + 15ull) & ~15ull;
-        unsigned long long off = (unsigned long long)blockIdx.x * per;
-        const unsigned long long end = off + per < prefetch_bytes ? off + per : prefetch_bytes;
-        for (; off < end; off += CHUNK) {
-          const uint32_t size = (uint32_t)((end - off < CHUNK ? end - off : CHUNK) & ~15ull);
-          if (size) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(prefetch_ptr + off), "r"(size) : "memory");
         }
       }
       if (abort_flag) {
@@ -236,19 +195,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + acc * BN;
-        if (NORMED) {
-          // the epilogue warps have written this CTA's token tiles (one item per CTA: phase 0)
-          ok = mbar_wait(smem_addr(&x_ready_bar), 0u, status, &abort_flag);
-          if (!ok) break;
-        }
         for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const uint32_t s = it % S::STAGES;
           ok = mbar_wait(smem_addr(&full_bar[s]), (it / S::STAGES) & 1u, status, &abort_flag);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_addr = tile_base + s * S::STAGE;
-          const uint32_t b_addr = NORMED ? tile_base + S::STAGES * S::STAGE + (uint32_t)(kb - kb_begin) * S::X_TILE
-                                         : a_addr + S::STAGE_A;
+          const uint32_t b_addr = a_addr + S::STAGE_A;
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             umma_bf16(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
@@ -267,83 +220,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int row = quarter * 32 + lane;                 // row of the accumulator tile
     const int ep_thread = (warp - 2) * 32 + lane;        // 0 .. 127
     uint32_t n_used = 0;
-    float rstd[NORMED ? BN : 1];
-    if (NORMED) {
-      // Build the token operand of this CTA's K range, B[m][k] = bf16(resid[m][k] * w[k]), and sum every
-      // row's squares over the whole of K.  A thread takes chunks of 8 columns (16 bytes of bf16: one
-      // unit of the 128-byte swizzle), ep_thread, ep_thread + 128, ..., of every row, eight rows' loads
-      // in flight at a time.
-      const Item item = item_of<BN, SWAPPED>(blockIdx.x, tiles_a, splits);
-      const int kb_begin = item.split * kb_per_split;
-      const int kb_end = min(num_kb_total, kb_begin + kb_per_split);
-      const uint32_t x_base = tile_base + S::STAGES * S::STAGE;
-      const int chunks_per_row = K >> 3;
-      float ssq[BN];
-#pragma unroll
-      for (int r = 0; r < BN; ++r) ssq[r] = 0.f;
-      for (int c = ep_thread; c < chunks_per_row; c += 128) {
-        const int kb = c >> 3;
-        const bool mine = kb >= kb_begin && kb < kb_end;
-        float wv[8];
-        {
-          const float4 w0 = __ldg(reinterpret_cast<const float4*>(fused.norm_weight + c * 8));
-          const float4 w1 = __ldg(reinterpret_cast<const float4*>(fused.norm_weight + c * 8 + 4));
-          wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w; wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
-          if (fused.unit_offset) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) wv[i] += 1.0f;
-          }
-        }
-#pragma unroll
-        for (int rb = 0; rb < BN; rb += 8) {
-          float4 lo[8], hi[8];
-#pragma unroll
-          for (int r = 0; r < 8; ++r) {
-            if (rb + r < M) {
-              const float4* src = reinterpret_cast<const float4*>(fused.resid + (size_t)(rb + r) * K + c * 8);
-              lo[r] = __ldcg(src);
-              hi[r] = __ldcg(src + 1);
-            } else {
-              lo[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-              hi[r] = lo[r];
-            }
-          }
-#pragma unroll
-          for (int r = 0; r < 8; ++r) {
-            const float4 a = lo[r], b = hi[r];
-            ssq[rb + r] += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
-            if (mine) {
-              uint4 packed;
-              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
-              h[0] = __floats2bfloat162_rn(a.x * wv[0], a.y * wv[1]);
-              h[1] = __floats2bfloat162_rn(a.z * wv[2], a.w * wv[3]);
-              h[2] = __floats2bfloat162_rn(b.x * wv[4], b.y * wv[5]);
-              h[3] = __floats2bfloat162_rn(b.z * wv[6], b.w * wv[7]);
-              const int tr = rb + r;                   // row of the tile (token)
-              const uint32_t dst = x_base + (uint32_t)(kb - kb_begin) * S::X_TILE + (uint32_t)tr * 128u +
-                                   (uint32_t)(((c & 7) ^ (tr & 7)) << 4);
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed.x), "r"(packed.y),
-                           "r"(packed.z), "r"(packed.w)
-                           : "memory");
-            }
-          }
-        }
-      }
-      // the tiles are read by the tensor core (async proxy): make the generic-proxy stores visible to it
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-#pragma unroll
-      for (int r = 0; r < BN; ++r) {
-        const float t = warp_sum(ssq[r]);
-        if (lane == 0) row_ss[warp - 2][r] = t;
-      }
-      epilogue_sync();
-      if (ep_thread == 0) mbar_arrive(smem_addr(&x_ready_bar));
-#pragma unroll
-      for (int r = 0; r < BN; ++r) {
-        const float total = row_ss[0][r] + row_ss[1][r] + row_ss[2][r] + row_ss[3][r];
-        rstd[r] = 1.0f / sqrtf(total / (float)K + fused.eps);
-      }
-    }
     for (int w = blockIdx.x; w < num_items; w += gridDim.x) {
       const Item item = item_of<BN, SWAPPED>(w, tiles_a, splits);
       const int kb_begin = item.split * kb_per_split;
@@ -412,8 +288,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 for (int i = 0; i < 16; ++i) {
                   const int m = item.b_row0 + c + i;
                   if (m < M) {
-                    const float rs = NORMED ? rstd[i] : 1.0f;      // NORMED: BN = 16, so c = 0
-                    const float g = v[i] * rs, u = exch[row][c + i] * rs;
+                    const float g = v[i], u = exch[row][c + i];
                     out[(int64_t)m * ldo + f] = cast_out<OutT>(g / (1.0f + __expf(-g)) * u);
                   }
                 }
@@ -474,8 +349,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int i = 0; i < 16; ++i) {
               const int m = item.b_row0 + c + i;         // token
               if (m < M) {
-                const float val = NORMED ? v[i] * rstd[i] : v[i];      // NORMED: BN = 16, so c = 0
-                if (fused.accumulate) {
+                const float val = v[i];
+                if (accumulate) {
                   // every split adds its part into the fp32 matrix itself (a warp's 32 rows are contiguous)
                   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(reinterpret_cast<float*>(out) + (int64_t)m * ldo + n),
                                "f"(val)
@@ -497,7 +372,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (lane == 0) mbar_arrive(smem_addr(&tmem_empty_bar[acc]));
         ++n_used;
       }
-      if (splits > 1 && reduce_in_kernel && !fused.accumulate) {
+      if (splits > 1 && reduce_in_kernel && !accumulate) {
         // the CTA that draws the last ticket of this tile sums the splits in ascending order
         __threadfence();
         epilogue_sync();
@@ -558,26 +433,19 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int cols, int64_t ld
 
 int sm_count() { return gllm_sm_count(); }
 
-// What the next launch asks into L2 when its own loads are out (gllm_gemm_bf16_prefetch_next); used once.
-const char* g_prefetch_ptr = nullptr;
-unsigned long long g_prefetch_bytes = 0;
-
-template <int BN, bool SWAPPED, typename OutT, bool GATED, bool NORMED = false>
+template <int BN, bool SWAPPED, typename OutT, bool GATED>
 int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M, int N, int K, int64_t ldx,
                 int64_t ldw, int64_t ldo, int splits, float* partial, int* tickets, int reduce_in_kernel, int* status,
-                cudaStream_t stream, FusedArgs fused = FusedArgs{nullptr, nullptr, 0.f, 0, 0}) {
+                cudaStream_t stream, int accumulate = 0) {
   using S = Shape<BN>;
   CUtensorMap map_a, map_b;
-  // NORMED: there is no bf16 token matrix; the weight's map stands in for the unused one
-  const bool ok = SWAPPED ? (make_map(&map_a, W, N, K, ldw, BM) &&
-                             (NORMED ? make_map(&map_b, W, N, K, ldw, BN) : make_map(&map_b, X, M, K, ldx, BN)))
+  const bool ok = SWAPPED ? (make_map(&map_a, W, N, K, ldw, BM) && make_map(&map_b, X, M, K, ldx, BN))
                           : (make_map(&map_a, X, M, K, ldx, BM) && make_map(&map_b, W, N, K, ldw, BN));
   if (!ok) return (int)cudaErrorInvalidValue;
-  constexpr int smem = NORMED ? S::SMEM_NORMED : S::SMEM;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<BN, SWAPPED, OutT, GATED, NORMED>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(umma_gemm_kernel<BN, SWAPPED, OutT, GATED>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
@@ -587,15 +455,9 @@ int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M
   const int tiles_a = (a_rows + BM - 1) / BM, tiles_b = (b_rows + BN - 1) / BN;
   const int num_items = tiles_a * tiles_b * splits;
   const int grid = num_items < sm_count() ? num_items : sm_count();
-  // the normed variant builds its token tiles once: one item per CTA, its K range within the tile region
-  if (NORMED && (num_items > grid || kb_per_split > S::X_MAX_KB || K % BK)) return (int)cudaErrorInvalidValue;
-  const char* pf_ptr = g_prefetch_ptr;
-  const unsigned long long pf_bytes = g_prefetch_bytes;
-  g_prefetch_ptr = nullptr;
-  g_prefetch_bytes = 0;
-  return gllm_launch(umma_gemm_kernel<BN, SWAPPED, OutT, GATED, NORMED>, dim3(grid), dim3(THREADS), (size_t)smem, stream,
-                     map_a, map_b, out, M, N, K, ldo, splits, kb_per_split, tiles_a, num_items, partial, tickets,
-                     reduce_in_kernel, status, pf_ptr, pf_bytes, fused);
+  return gllm_launch(umma_gemm_kernel<BN, SWAPPED, OutT, GATED>, dim3(grid), dim3(THREADS), (size_t)S::SMEM, stream, map_a,
+                     map_b, out, M, N, K, ldo, splits, kb_per_split, tiles_a, num_items, partial, tickets,
+                     reduce_in_kernel, status, accumulate);
 }
 
 // Width of the weight tile for more than 64 tokens: 256 rows, or 64 for a single tile of tokens
@@ -655,16 +517,6 @@ GLLM_API int gllm_gemm_bf16_tiles(int M, int N) {
   return ((M + BM - 1) / BM) * ((N + bn - 1) / bn);
 }
 
-// The next product launched from this thread asks `bytes` bytes at `ptr` (16-byte aligned device memory
-// that stays allocated, typically the weight of the product after it) into L2 once its own loads are
-// out.  One launch consumes the hint.
-GLLM_API void gllm_gemm_bf16_prefetch_next(const void* ptr, unsigned long long bytes) {
-  if ((reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
-    g_prefetch_ptr = (const char*)ptr;
-    g_prefetch_bytes = bytes & ~15ull;
-  }
-}
-
 // out_is_f32: 0 = bf16 output, 1 = fp32 output.  Needs K % 8 == 0 and 16-byte aligned rows of X and W.
 // partial: splits * M * N floats of scratch when splits > 1, laid out [split][M][N].
 // reduce_in_kernel != 0: the kernel sums the splits itself into `out` (tickets: zeroed ints, left at
@@ -708,50 +560,11 @@ GLLM_API int gllm_gemm_bf16_accumulate(const __nv_bfloat16* X, const __nv_bfloat
   if (M > 64 || K <= 0 || K % 8 || ldx % 8 || ldw % 8 || splits < 1 || splits > 16 ||
       (reinterpret_cast<uintptr_t>(X) & 15) || (reinterpret_cast<uintptr_t>(W) & 15))
     return (int)cudaErrorInvalidValue;
-  const FusedArgs fused{nullptr, nullptr, 0.f, 0, 1};
 #define GLLM_ACC(BN) \
   return umma_launch<BN, true, float, false>(X, W, acc, M, N, K, ldx, ldw, ldo, splits, nullptr, nullptr, 0, status, \
-                                             stream, fused)
+                                             stream, 1)
   if (M <= 16) GLLM_ACC(16);
   if (M <= 32) GLLM_ACC(32);
   GLLM_ACC(64);
 #undef GLLM_ACC
-}
-
-// 1 when gllm_gemm_bf16_normed* take a product of these sizes with `splits` K ranges.
-GLLM_API int gllm_gemm_bf16_normed_takes(int M, int N, int K, int splits) {
-  if (M <= 0 || M > 16 || K <= 0 || K % BK || splits < 1) return 0;
-  const int num_kb = K / BK;
-  const int kb_per_split = (num_kb + splits - 1) / splits;
-  const int items = ((N + BM - 1) / BM) * splits;
-  return items <= sm_count() && kb_per_split <= Shape<16>::X_MAX_KB;
-}
-
-// RMSNorm fused into the product of up to 16 tokens: out = RMSNorm(resid; weight, eps) * W^T with
-// resid [M, K] fp32 (rows K apart), never rounded to a normed bf16 matrix in memory.  With splits > 1
-// the K ranges' parts go to `partial` [split][M][N] unsummed (out may be null), else out [M, N] bf16.
-GLLM_API int gllm_gemm_bf16_normed(const float* resid, const float* norm_weight, float eps, int unit_offset,
-                                   const __nv_bfloat16* W, __nv_bfloat16* out, int M, int N, int K, int64_t ldw,
-                                   int64_t ldo, int splits, float* partial, int* status, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (!gllm_gemm_bf16_normed_takes(M, N, K, splits) || ldw % 8 || (reinterpret_cast<uintptr_t>(W) & 15) ||
-      (reinterpret_cast<uintptr_t>(resid) & 15) || (reinterpret_cast<uintptr_t>(norm_weight) & 15) ||
-      (splits > 1 && !partial) || (splits == 1 && !out))
-    return (int)cudaErrorInvalidValue;
-  const FusedArgs fused{resid, norm_weight, eps, unit_offset, 0};
-  return umma_launch<16, true, __nv_bfloat16, false, true>(nullptr, W, out, M, N, K, 0, ldw, ldo, splits, partial,
-                                                           nullptr, 0, status, stream, fused);
-}
-
-// The same in front of the gated feed-forward product (see gllm_gemm_bf16_gated): out [M, N/2] bf16.
-GLLM_API int gllm_gemm_bf16_normed_gated(const float* resid, const float* norm_weight, float eps, int unit_offset,
-                                         const __nv_bfloat16* W, __nv_bfloat16* out, int M, int N, int K,
-                                         int64_t ldw, int64_t ldo, int* status, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (!gllm_gemm_bf16_normed_takes(M, N, K, 1) || N % 128 || ldw % 8 || (reinterpret_cast<uintptr_t>(W) & 15) ||
-      (reinterpret_cast<uintptr_t>(resid) & 15) || (reinterpret_cast<uintptr_t>(norm_weight) & 15))
-    return (int)cudaErrorInvalidValue;
-  const FusedArgs fused{resid, norm_weight, eps, unit_offset, 0};
-  return umma_launch<16, true, __nv_bfloat16, true, true>(nullptr, W, out, M, N, K, 0, ldw, ldo, 1, nullptr, nullptr,
-                                                          0, status, stream, fused);
 }

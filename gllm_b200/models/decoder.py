@@ -93,18 +93,6 @@ class DecoderModel:
                 part.load(get, self.dtype, self.device)
         self.final_norm.load(get, self.dtype, self.device)
         self.head = self.embedding if self.spec.head_name is None else get(self.spec.head_name, "matrix")
-        if self.dtype == torch.bfloat16 and self.device.type == "cuda":
-            from gllm_b200.ops import gemm_bf16
-
-            gemm_bf16.set_weight_order(self.streamed_weights())
-
-    def streamed_weights(self) -> list:
-        """Every matrix a step multiplies by, in running order (``Part.streamed_weights``), the head last."""
-        out = []
-        for entry in self.spec.plan:
-            for part in self.layers[entry.layer].parts():
-                out += part.streamed_weights()
-        return out + [self.head]
 
     # ------------------------------------------------------------------ cache
     def cache_requirements(self):

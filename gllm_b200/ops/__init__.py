@@ -35,7 +35,6 @@ __all__ = [
     "sample",
     "argmax",
     "SplitSum",
-    "NormedInput",
     "ADDED",
     "as_tensor",
     "linear_gated",
@@ -245,26 +244,6 @@ class SplitSum:
         return out
 
 
-class NormedInput:
-    """RMSNorm of the residual rows ``resid`` that has not been computed yet: a product that takes it
-    (``linear``, ``linear_gated``) fuses the norm into itself; ``tensor()`` runs the norm kernel
-    for everybody else.  ``resid`` must not change before it is consumed."""
-
-    def __init__(self, resid: torch.Tensor, weight: torch.Tensor, eps: float, unit_offset: bool, dtype: torch.dtype):
-        self.resid, self.weight, self.eps, self.unit_offset, self.dtype = resid, weight, float(eps), bool(unit_offset), dtype
-
-    @property
-    def shape(self):
-        return self.resid.shape
-
-    @property
-    def device(self):
-        return self.resid.device
-
-    def tensor(self) -> torch.Tensor:
-        return add_rmsnorm(None, self.resid, self.weight, self.eps, self.dtype, unit_offset=self.unit_offset)
-
-
 class _Added:
     """What a product returns when it has added its result into the matrix it was given
     (``linear(..., add_into=...)``): there is nothing left to add."""
@@ -277,8 +256,8 @@ ADDED = _Added()
 
 
 def as_tensor(x):
-    """``x`` itself, the summed tensor of a SplitSum, or the normed rows of a NormedInput."""
-    return x.tensor() if isinstance(x, (SplitSum, NormedInput)) else x
+    """``x`` itself, or the summed tensor of a SplitSum."""
+    return x.tensor() if isinstance(x, SplitSum) else x
 
 
 def _parts_args(x):
@@ -410,18 +389,10 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor, block: int = GATED_
     return stacked.reshape(2 * inter, hidden).contiguous()
 
 
-def linear_gated(x, weight: torch.Tensor) -> torch.Tensor:
+def linear_gated(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     """``silu(x @ Wg.T) * (x @ Wu.T)`` for a weight stacked by ``interleave_gate_up``: one kernel
     with the activation in the product's epilogue where the tensor-core kernel takes the operands,
-    the product and ``silu_mul`` otherwise.  ``x`` may be a NormedInput."""
-    if isinstance(x, NormedInput):
-        if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16:
-            from gllm_b200.ops import gemm_bf16
-
-            fused = gemm_bf16.linear_normed_gated(x, weight)
-            if fused is not None:
-                return fused
-        x = x.tensor()
+    the product and ``silu_mul`` otherwise."""
     _cuda(x, "x")
     _cuda(weight, "weight", x.dtype)
     if x.dtype == torch.bfloat16:
@@ -480,34 +451,20 @@ def rope_store(
 
 
 # ------------------------------------------------------------------- linear
-# Products of few tokens that end a branch add themselves into the residual stream (GLLM_B200_FUSE_ADD=0:
-# they leave their result to the norm kernel after them).  The norm fused into the product after it is
-# off unless GLLM_B200_FUSE_NORM=1: measured slower inside a step (the norm kernel is small enough to run
-# beside the product before and the product after it, whose weights stream in meanwhile; the fused
-# product is not).
-FUSE_SMALL_STEPS = os.environ.get("GLLM_B200_FUSE_NORM", "0") == "1"
+# Products of few tokens that end a branch add themselves into the residual stream
+# (GLLM_B200_FUSE_ADD=0: they leave their result to the norm kernel after them).
 ACCUMULATE_IN_PRODUCT = os.environ.get("GLLM_B200_FUSE_ADD", "1") != "0"
 
 
-def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
            out: torch.Tensor | None = None, split_ok: bool = False, add_into: torch.Tensor | None = None):
     """``x @ weight.T`` with ``weight`` stored ``[out, in]``
     (gllm/model/layers/linear.py:20).  fp32 inputs run the FFMA kernel (no
     tensor-core mode); bf16 inputs run the tensor-core kernels with fp32
     accumulation.  With ``split_ok`` the result may be a SplitSum (for callers
-    that hand it to ``add_rmsnorm`` or ``rope_store``).  ``x`` may be a
-    NormedInput (the norm then runs inside the product where the kernel takes
-    the sizes).  With ``add_into`` (fp32 ``[m, n]``, the residual stream) the
-    product may add itself there and return ``ADDED``; when it returns anything
-    else, nothing was added."""
-    if isinstance(x, NormedInput):
-        if x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and out is None and out_dtype in (None, x.dtype):
-            from gllm_b200.ops import gemm_bf16
-
-            fused = gemm_bf16.linear_normed(x, weight, split_ok)
-            if fused is not None:
-                return fused
-        x = x.tensor()
+    that hand it to ``add_rmsnorm`` or ``rope_store``).  With ``add_into``
+    (fp32 ``[m, n]``, the residual stream) the product may add itself there
+    and return ``ADDED``; when it returns anything else, nothing was added."""
     _cuda(x, "x")
     _cuda(weight, "weight", x.dtype)
     m, k = x.shape

@@ -12,8 +12,7 @@ which is what the reference uses for every projection
 from __future__ import annotations
 
 import os
-import weakref
-from ctypes import c_float, c_int, c_int64, c_uint64, c_void_p
+from ctypes import c_int, c_int64, c_void_p
 
 import torch
 
@@ -40,61 +39,22 @@ def _umma_fns():
         g = lib.gllm_gemm_bf16_gated
         g.argtypes = [P, P, P, c_int, c_int, c_int, c_int64, c_int64, c_int64, P, P]
         g.restype = c_int
-        lib.gllm_gemm_bf16_prefetch_next.argtypes = [P, c_uint64]
-        lib.gllm_gemm_bf16_prefetch_next.restype = None
-        _umma = (f, lib.gllm_gemm_bf16_splits, lib.gllm_gemm_bf16_tiles, g, lib.gllm_gemm_bf16_prefetch_next)
+        _umma = (f, lib.gllm_gemm_bf16_splits, lib.gllm_gemm_bf16_tiles, g)
     return _umma
 
 
-_fused = None
+_accumulate = None
 
 
-def _fused_fns():
-    """(accumulate, normed_takes, normed, normed_gated) of the few-token product."""
-    global _fused
-    if _fused is None:
+def _accumulate_fn():
+    global _accumulate
+    if _accumulate is None:
         lib = load_module("gemm_bf16")
         acc = lib.gllm_gemm_bf16_accumulate
         acc.argtypes = [P, P, P, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int, P, P]
         acc.restype = c_int
-        takes = lib.gllm_gemm_bf16_normed_takes
-        takes.argtypes = [c_int, c_int, c_int, c_int]
-        takes.restype = c_int
-        normed = lib.gllm_gemm_bf16_normed
-        normed.argtypes = [P, P, c_float, c_int, P, P, c_int, c_int, c_int, c_int64, c_int64, c_int, P, P, P]
-        normed.restype = c_int
-        gated = lib.gllm_gemm_bf16_normed_gated
-        gated.argtypes = [P, P, c_float, c_int, P, P, c_int, c_int, c_int, c_int64, c_int64, P, P]
-        gated.restype = c_int
-        _fused = (acc, takes, normed, gated)
-    return _fused
-
-
-# ---- the order in which weights are streamed
-# A decode step is a chain of products that each stream one weight from HBM, and between two of them
-# the memory idles while one kernel drains and the next is handed over.  A model that tells the order
-# of its weights (``set_weight_order``) lets every few-token product ask the head of the NEXT weight
-# into L2 once its own loads are out: that request depends on nothing, so it is served in the gap.
-PREFETCH_BYTES = int(float(os.environ.get("GLLM_B200_PREFETCH_MB", 32)) * (1 << 20))
-_next_weight: dict[int, weakref.ref] = {}
-
-
-def set_weight_order(weights) -> None:
-    """``weights``: the matrices a step multiplies by, in the order it does (the last is followed by
-    the first: the next step)."""
-    weights = [w for w in weights if w is not None and w.is_cuda]
-    for a, b in zip(weights, weights[1:] + weights[:1]):
-        if a.data_ptr() != b.data_ptr():
-            _next_weight[a.data_ptr()] = weakref.ref(b)
-
-
-def _hint_next_weight(weight: torch.Tensor, m: int) -> None:
-    if m > FEW_TOKENS or not PREFETCH_BYTES:
-        return
-    ref = _next_weight.get(weight.data_ptr())
-    nxt = ref() if ref is not None else None
-    if nxt is not None:
-        _umma_fns()[4](nxt.data_ptr(), min(nxt.numel() * nxt.element_size(), PREFETCH_BYTES))
+        _accumulate = acc
+    return _accumulate
 
 
 def _device_scratch(device: torch.device, partial_floats: int, tickets: int):
@@ -199,7 +159,6 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> 
     splits = splits_of(m, n, k)
     if splits == 1 and pair_kernel_pays(x, n):
         return linear_pair(x, weight, out)
-    _hint_next_weight(weight, m)
     partial, tickets = _device_scratch(x.device, splits * m * n if splits > 1 else 0, tiles_of(m, n))
     if splits > 1 and out.is_contiguous():
         # a second small kernel sums the splits: far quicker than the last CTA of a tile summing them
@@ -229,7 +188,6 @@ def linear_split(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype):
     splits = splits_of(m, n, k)
     if splits <= 1:
         return None
-    _hint_next_weight(weight, m)
     partial, tickets = _device_scratch(x.device, splits * m * n, 0)
     code = f(x.data_ptr(), weight.data_ptr(), None, int(out_dtype == torch.float32), m, n, k, x.stride(0),
              weight.stride(0), n, splits, partial.data_ptr(), tickets.data_ptr(), 0,
@@ -262,18 +220,13 @@ def linear_gated(x: torch.Tensor, weight: torch.Tensor):
     if pair_kernel_pays(x, n):
         return linear_pair(x, weight, out, gated=True)
     g = _umma_fns()[3]
-    _hint_next_weight(weight, m)
     code = g(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), weight.stride(0), out.stride(0),
              ops.status_word(x.device).data_ptr(), ops._stream())
     ops._check(code, "gemm_bf16_gated")
     return out
 
 
-# ---- fusions for steps of few tokens
-def _weight_ok(weight: torch.Tensor) -> bool:
-    return weight.stride(1) == 1 and weight.stride(0) % 8 == 0 and weight.data_ptr() % 16 == 0
-
-
+# ---- a product that adds itself into the residual stream
 def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, acc: torch.Tensor) -> bool:
     """``acc += x @ weight.T`` (``acc`` fp32 ``[m, n]``) inside the product's epilogue, for up to 64
     tokens; False when the kernel does not take the operands (nothing was launched)."""
@@ -285,58 +238,7 @@ def linear_accumulate(x: torch.Tensor, weight: torch.Tensor, acc: torch.Tensor) 
             or tuple(acc.shape) != (m, n) or acc.stride(1) != 1):
         return False
     splits = _umma_fns()[1](m, n, k)
-    _hint_next_weight(weight, m)
-    code = _fused_fns()[0](x.data_ptr(), weight.data_ptr(), acc.data_ptr(), m, n, k, x.stride(0), weight.stride(0),
-                           acc.stride(0), splits, ops.status_word(x.device).data_ptr(), ops._stream())
+    code = _accumulate_fn()(x.data_ptr(), weight.data_ptr(), acc.data_ptr(), m, n, k, x.stride(0), weight.stride(0),
+                            acc.stride(0), splits, ops.status_word(x.device).data_ptr(), ops._stream())
     ops._check(code, "gemm_bf16_accumulate")
     return True
-
-
-def linear_normed(nx, weight: torch.Tensor, split_ok: bool):
-    """``RMSNorm(resid) @ weight.T`` for a lazily normed input (``ops.NormedInput``), the norm fused
-    into the product; None when the kernel does not take the sizes."""
-    from gllm_b200 import ops
-
-    m, k = nx.shape
-    n = weight.shape[0]
-    if not _weight_ok(weight) or weight.shape[1] != k or nx.resid.data_ptr() % 16 or not nx.resid.is_contiguous():
-        return None
-    splits = _umma_fns()[1](m, n, k)
-    _, takes, normed, _ = _fused_fns()
-    if not takes(m, n, k, splits):
-        return None
-    _hint_next_weight(weight, m)
-    status = ops.status_word(weight.device).data_ptr()
-    if splits > 1:
-        partial, _ = _device_scratch(weight.device, splits * m * n, 0)
-        code = normed(nx.resid.data_ptr(), nx.weight.data_ptr(), nx.eps, int(nx.unit_offset), weight.data_ptr(), None,
-                      m, n, k, weight.stride(0), n, splits, partial.data_ptr(), status, ops._stream())
-        ops._check(code, "gemm_bf16_normed")
-        result = ops.SplitSum(partial[: splits * m * n].view(splits, m, n), nx.dtype, scratch_generation(weight.device))
-        return result if split_ok else result.tensor()
-    out = torch.empty((m, n), dtype=torch.bfloat16, device=weight.device)
-    code = normed(nx.resid.data_ptr(), nx.weight.data_ptr(), nx.eps, int(nx.unit_offset), weight.data_ptr(),
-                  out.data_ptr(), m, n, k, weight.stride(0), out.stride(0), 1, None, status, ops._stream())
-    ops._check(code, "gemm_bf16_normed")
-    return out
-
-
-def linear_normed_gated(nx, weight: torch.Tensor):
-    """The gated feed-forward product (``linear_gated``) of a lazily normed input; None when the kernel
-    does not take the sizes."""
-    from gllm_b200 import ops
-
-    m, k = nx.shape
-    n = weight.shape[0]
-    if not _weight_ok(weight) or weight.shape[1] != k or n % 128 or nx.resid.data_ptr() % 16 or not nx.resid.is_contiguous():
-        return None
-    _, takes, _, gated = _fused_fns()
-    if not takes(m, n, k, 1):
-        return None
-    _hint_next_weight(weight, m)
-    out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=weight.device)
-    code = gated(nx.resid.data_ptr(), nx.weight.data_ptr(), nx.eps, int(nx.unit_offset), weight.data_ptr(),
-                 out.data_ptr(), m, n, k, weight.stride(0), out.stride(0), ops.status_word(weight.device).data_ptr(),
-                 ops._stream())
-    ops._check(code, "gemm_bf16_normed_gated")
-    return out

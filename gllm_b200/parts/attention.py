@@ -29,7 +29,6 @@ from gllm_b200.parts.base import (
 @register_mixer("attention")
 class Attention(Mixer):
     graph_safe_portions = True
-    accepts_lazy_input = True
 
     def __init__(self, names, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position=None, window: int | None = None, scale: float | None = None):
@@ -51,9 +50,6 @@ class Attention(Mixer):
 
     def kv_requirement(self):
         return KVPageRequirement.keys_and_values(self.num_kv_heads, self.head_dim, self.window)
-
-    def streamed_weights(self):
-        return [self.w_qkv, self.w_o]
 
     def kernel_needs(self):
         return {"attention_head_dims": {self.head_dim}}

@@ -165,16 +165,6 @@ class MixerCache:
 class Part:
     """Base of all parts: named tensors in, device tensors held."""
 
-    # True when ``forward`` hands its input ``x`` straight to ``ops.linear`` / ``ops.linear_gated`` and
-    # does nothing else with it: the block may then pass an ``ops.NormedInput`` (a norm not computed
-    # yet, which the product fuses into itself) instead of a tensor.
-    accepts_lazy_input = False
-
-    def streamed_weights(self) -> list:
-        """The matrices ``forward`` multiplies by, in the order it does: a decode step streams each
-        from memory once, and a product may ask the head of the next one into the cache early."""
-        return []
-
     def kernel_needs(self) -> dict:
         """What the part will ask of the kernel modules, so that they can be compiled side by side
         before the first step: ``{"attention_head_dims": {64}}`` for an attention mixer."""
@@ -199,12 +189,6 @@ class Part:
 
 
 class Norm(Part):
-    def forward_lazy(self, branch, resid: torch.Tensor, dtype: torch.dtype):
-        """The same as ``forward`` without ``rows``, but the normed rows may come back as an
-        ``ops.NormedInput`` for a consumer that fuses the norm into its product; None when this norm
-        (or these sizes) cannot: the caller then calls ``forward``."""
-        return None
-
     def forward(self, branch, resid: torch.Tensor, dtype: torch.dtype,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
         """``resid += branch`` in place (fp32), return norm(resid) in ``dtype``.

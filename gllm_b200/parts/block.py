@@ -18,20 +18,12 @@ class PreNormBlock(Block):
     graph_safe_portions = True
     part_kinds = {"mixer_norm": "norm", "mixer": "mixer", "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
 
-    @staticmethod
-    def _normed(norm, part, branch, resid, ctx):
-        """norm(resid + branch) for ``part``: lazily (for the part's first product to fuse) when the
-        part takes that and nothing is left to add, else by the norm kernel."""
-        if branch is ops.ADDED:
-            branch = None
-        x = norm.forward_lazy(branch, resid, ctx.dtype) if part.accepts_lazy_input else None
-        return x if x is not None else norm.forward(branch, resid, ctx.dtype)
-
     def forward(self, branch, resid, ctx, cache):
+        # a part may add its result into the residual itself (its last product's epilogue) and say so
         ctx.residual_sink = resid
-        x = self._normed(self.mixer_norm, self.mixer, branch, resid, ctx)
+        x = self.mixer_norm.forward(None if branch is ops.ADDED else branch, resid, ctx.dtype)
         mixed = self.mixer.forward(x, ctx, cache)
-        x = self._normed(self.feed_forward_norm, self.feed_forward, mixed, resid, ctx)
+        x = self.feed_forward_norm.forward(None if mixed is ops.ADDED else mixed, resid, ctx.dtype)
         out = self.feed_forward.forward(x, ctx)
         ctx.residual_sink = None
         return out, resid

@@ -16,7 +16,6 @@ from gllm_b200.parts.base import FeedForward, TensorExpectation, register_feed_f
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
     graph_safe_portions = True
-    accepts_lazy_input = True
 
     def __init__(self, names, hidden_size: int, intermediate_size: int):
         super().__init__(names)
@@ -43,12 +42,10 @@ class SwiGLU(FeedForward):
             self.w_gate_up = torch.cat([gate, up], 0).contiguous()
         self.w_down = get(self.names["down"], "matrix").contiguous()
 
-    def streamed_weights(self):
-        return [self.w_gate_up, self.w_down]
-
     def forward(self, x, ctx):
+        sink = getattr(ctx, "residual_sink", None)
         if self.gated_blocks:
             hidden = ops.linear_gated(x, self.w_gate_up)
         else:
             hidden = ops.silu_mul(ops.linear(x, self.w_gate_up))
-        return ops.linear(hidden, self.w_down, split_ok=True, add_into=getattr(ctx, "residual_sink", None))
+        return ops.linear(hidden, self.w_down, split_ok=True, add_into=sink)

@@ -33,14 +33,5 @@ class RMSNorm(Norm):
     def load(self, get, dtype, device):
         self.weight = get(self.names["weight"], "vector")
 
-    # the product kernel that fuses the norm takes up to this many rows, of a width that is a multiple of 64
-    LAZY_MAX_ROWS = 16
-
-    def forward_lazy(self, branch, resid, dtype):
-        if (branch is not None or not ops.FUSE_SMALL_STEPS or dtype != torch.bfloat16
-                or resid.shape[0] > self.LAZY_MAX_ROWS or self.size % 64):
-            return None
-        return ops.NormedInput(resid, self.weight, self.eps, self.unit_offset, dtype)
-
     def forward(self, branch, resid, dtype, rows=None):
         return ops.add_rmsnorm(branch, resid, self.weight, self.eps, dtype, rows=rows, unit_offset=self.unit_offset)

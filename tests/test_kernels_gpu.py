@@ -531,74 +531,6 @@ def test_gemm_gated_epilogue(ops, m, inter, k):
     torch.testing.assert_close(unfused.double(), want, rtol=3e-2, atol=3e-2)
 
 
-def _plain_rmsnorm(resid, w, eps, unit_offset=False):
-    x = resid.double()
-    wd = w.double() + (1.0 if unit_offset else 0.0)
-    return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * wd
-
-
-@pytest.mark.parametrize("m", [1, 5, 8, 16])
-@pytest.mark.parametrize("n,k", [(200, 192), (3072, 2048), (130, 64), (2048, 4096)])
-@pytest.mark.parametrize("unit_offset", [False, True])
-def test_gemm_with_the_norm_fused_into_it(ops, m, n, k, unit_offset):
-    """RMSNorm(resid) @ W^T with the norm inside the product (the token operand is built from the
-    fp32 rows in shared memory, the row statistic scales the accumulator), cut along K or not,
-    against the plain formula; the rows are far from unit scale so that a missing scale shows."""
-    g = torch.Generator().manual_seed(m * 1000 + n + k)
-    resid = (torch.randn(m, k, generator=g) * 7.0 + 0.5).cuda()
-    nw = ((0.0 if unit_offset else 1.0) + 0.2 * torch.randn(k, generator=g)).cuda()
-    w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).cuda()
-    eps = 2e-5
-    want = _plain_rmsnorm(resid.cpu(), nw.cpu(), eps, unit_offset) @ w.double().cpu().T
-    lazy = ops.NormedInput(resid, nw, eps, unit_offset, torch.bfloat16)
-    before = resid.clone()
-    from gllm_b200.ops import gemm_bf16
-
-    fused = gemm_bf16.linear_normed(lazy, w, split_ok=True)
-    assert fused is not None, "the fused kernel refused sizes it is documented to take"
-    got = ops.as_tensor(fused).double().cpu()
-    ops.check_status()
-    assert torch.equal(resid, before)
-    scale = float(want.abs().max())
-    assert float((got - want).abs().max()) <= 2e-2 * scale
-    # and through the public entry point, which falls back to the norm kernel when it has to
-    got2 = ops.as_tensor(ops.linear(lazy, w, split_ok=True)).double().cpu()
-    assert float((got2 - want).abs().max()) <= 2e-2 * scale
-
-
-@pytest.mark.parametrize("m", [1, 8, 16])
-@pytest.mark.parametrize("inter,k", [(128, 64), (320, 192), (8192, 2048)])
-def test_gated_gemm_with_the_norm_fused_into_it(ops, m, inter, k):
-    g = torch.Generator().manual_seed(m + inter + k)
-    resid = (torch.randn(m, k, generator=g) * 3.0).cuda()
-    nw = (1.0 + 0.2 * torch.randn(k, generator=g)).cuda()
-    gate = (torch.randn(inter, k, generator=g) * 0.05).to(torch.bfloat16)
-    up = (torch.randn(inter, k, generator=g) * 0.05).to(torch.bfloat16)
-    w = ops.interleave_gate_up(gate.cuda(), up.cuda())
-    x = _plain_rmsnorm(resid.cpu(), nw.cpu(), 1e-5)
-    gd, ud = x @ gate.double().T, x @ up.double().T
-    want = gd * torch.sigmoid(gd) * ud
-    lazy = ops.NormedInput(resid, nw, 1e-5, False, torch.bfloat16)
-    from gllm_b200.ops import gemm_bf16
-
-    if inter % 64 == 0:
-        assert gemm_bf16.linear_normed_gated(lazy, w) is not None
-    got = ops.linear_gated(lazy, w).double().cpu()
-    ops.check_status()
-    assert float((got - want).abs().max()) <= 2e-2 * float(want.abs().max())
-
-
-def test_a_lazy_norm_of_sizes_the_fused_kernel_refuses_runs_the_norm_kernel(ops):
-    g = torch.Generator().manual_seed(3)
-    for m, n, k in [(17, 256, 128), (4, 96, 72), (8, 64, 64 * 40)]:       # too many rows; K no multiple of 64; K too long
-        resid = torch.randn(m, k, generator=g).cuda()
-        nw = torch.ones(k).cuda()
-        w = (torch.randn(n, k, generator=g) * 0.05).to(torch.bfloat16).cuda()
-        want = _plain_rmsnorm(resid.cpu(), nw.cpu(), 1e-5) @ w.double().cpu().T
-        got = ops.as_tensor(ops.linear(ops.NormedInput(resid, nw, 1e-5, False, torch.bfloat16), w, split_ok=True))
-        assert float((got.double().cpu() - want).abs().max()) <= 2e-2 * float(want.abs().max())
-
-
 @pytest.mark.parametrize("m", [1, 3, 16, 40, 64])
 @pytest.mark.parametrize("n,k", [(2048, 8192), (200, 136), (2048, 2048)])
 def test_gemm_that_adds_itself_into_the_residual(ops, m, n, k):
