@@ -127,6 +127,22 @@ def linear(m=8, n=16384, k=2048, iters=5, peaks=None, out_fp32=False, gated=0, s
             "shape": dict(m=m, n=n, k=k)}
 
 
+def linear_f32(m=2048, n=8192, k=2048, iters=5, peaks=None):
+    """The true 32-bit product (FFMA, no tensor-core mode) of the float32 path."""
+    from gllm_b200 import ops
+
+    x = torch.randn(m, k, device="cuda")
+    w = torch.randn(n, k, device="cuda") * 0.02
+    out = torch.empty(m, n, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    us = _time(lambda: ops.linear(x, w, out=out), iters, flush)
+    nbytes = (m * k + n * k + m * n) * 4
+    flops = 2.0 * m * n * k
+    return {"kernel": "linear_f32 (FFMA)", "us": round(us, 2), "achieved_tflops": round(flops / us / 1e6, 1),
+            "achieved_gbs": round(nbytes / us / 1e3, 1), "frac_of_hbm_peak": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4),
+            "shape": dict(m=m, n=n, k=k)}
+
+
 def add_rmsnorm(rows=8, hidden=2048, splits=8, iters=5, peaks=None):
     """resid += (sum of ``splits`` fp32 partial products, 0: a summed bf16 branch), then RMSNorm: the
     kernel between two products of a layer."""
@@ -162,6 +178,7 @@ KERNELS = {
     "attention_decode": attention_decode,
     "attention_prefill": attention_prefill,
     "linear": linear,
+    "linear_f32": linear_f32,
     "add_rmsnorm": add_rmsnorm,
     "argmax": argmax,
 }

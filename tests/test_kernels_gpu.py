@@ -121,14 +121,16 @@ def test_rope_store(ops, dtype, interleaved, hq, hkv, d, rot):
     assert torch.equal(untouched, ~seen)
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 311, 72), (7, 96, 160), (65, 130, 100), (200, 384, 96), (33, 1000, 515)])
+@pytest.mark.parametrize("m,n,k", [(1, 311, 72), (7, 96, 160), (65, 130, 100), (200, 384, 96), (33, 1000, 515),
+                                   (129, 260, 2048), (300, 1001, 520), (257, 128, 4)])
 def test_gemm_f32(ops, m, n, k):
     g = torch.Generator().manual_seed(4)
     a = torch.randn(m, k, generator=g).cuda()
     b = torch.randn(n, k, generator=g).cuda()
     got = ops.linear(a, b)
     want = a.double() @ b.double().T
-    torch.testing.assert_close(got.double(), want, rtol=1e-5, atol=1e-4)
+    # fp32 accumulation over k terms of unit scale: the rounding error grows with k (1e-4 up to k = 512)
+    torch.testing.assert_close(got.double(), want, rtol=1e-5, atol=1e-4 * max(1.0, k / 512))
     # a row's result does not depend on the rest of the batch: bitwise
     alone = ops.linear(a[m // 2:m // 2 + 1].contiguous(), b)
     assert torch.equal(alone[0], got[m // 2])
