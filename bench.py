@@ -388,6 +388,96 @@ def run_ours(args) -> dict:
     return record
 
 
+SCENARIOS = {
+    # BASELINE.json configs[3]: 64 requests at once, prompts uniform in 128..2,048 tokens, 256 generated tokens each
+    "llama-3.2-3b": dict(kind="mixed", requests=64, prompt=(128, 2048), new_tokens=256, max_batch=64, max_seq_len=4096,
+                         pool_fraction=1.0),
+    # BASELINE.json configs[4]: 128 requests arriving four at a time, prompts 512..8,192 tokens, 512 generated tokens;
+    # the pool holds a third of what they could grow to, so requests are preempted and recomputed
+    "llama-3.1-8b": dict(kind="staggered", requests=128, prompt=(512, 8192), new_tokens=512, max_batch=128,
+                         max_seq_len=8704, pool_fraction=1.0 / 3, arrivals_per_step=4),
+}
+
+
+def run_scenario(args) -> dict:
+    """A whole-engine run (scheduler on) at another model size: never the headline, a line of its own."""
+    import torch
+
+    from gllm_b200 import GenerationRequest, GeneratorParams, LLMEngine
+    from gllm_b200.config import load_config
+    from gllm_b200.config.presets import load_preset
+    from gllm_b200.weights import write_random_model
+
+    sc = SCENARIOS[args.preset]
+    raw = load_preset(args.preset)
+    full_layers = raw["num_hidden_layers"]
+    if args.layers:
+        raw["num_hidden_layers"] = args.layers
+    block_size = 16
+    worst_pages = sc["max_batch"] * -(-sc["max_seq_len"] // block_size)
+    num_blocks = max(-(-sc["max_seq_len"] // block_size) + 1, int(worst_pages * sc["pool_fraction"]))
+    tmp = tempfile.mkdtemp(prefix="gllm_b200_bench_")
+    try:
+        folder = write_random_model(os.path.join(tmp, args.preset), load_config(raw), seed=0, std=0.02)
+        params = GeneratorParams(block_size=block_size, max_batch_size=sc["max_batch"], max_seq_len=sc["max_seq_len"],
+                                 model_dtype="bfloat16", num_blocks=num_blocks, max_num_batched_tokens=8192,
+                                 prefill_chunk=2048)
+        engine = LLMEngine(folder, params, device="cuda:0")
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    g = torch.Generator().manual_seed(3)
+    vocab = engine.config.vocab_size
+    lo, hi = sc["prompt"]
+    lengths = torch.randint(lo, hi + 1, (sc["requests"],), generator=g).tolist()
+    requests = [GenerationRequest(prompt_token_ids=torch.randint(0, vocab, (n,), generator=g).tolist(),
+                                  max_new_tokens=sc["new_tokens"], temperature=0.0, ignore_eos=True) for n in lengths]
+    # warm-up: compile and capture what a short run needs
+    engine.generate([GenerationRequest(prompt_token_ids=list(range(1, 40)), max_new_tokens=4, temperature=0.0,
+                                       ignore_eos=True)])
+    for key in engine.counters:
+        engine.counters[key] = 0
+    sampler = ClockSampler(0)
+    sampler.start()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    states = []
+    pending = list(requests)
+    per_step = sc.get("arrivals_per_step", len(pending))
+    while pending or any(not s.is_finished for s in states):
+        for _ in range(min(per_step, len(pending))):
+            states.append(engine.submit(pending.pop(0)))
+        engine.step()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop()
+    generated = sum(len(s.generated_token_ids) for s in states)
+    assert generated == sc["requests"] * sc["new_tokens"], "a request ended early"
+    return {
+        "metric": f"generated tok/s, whole engine ({sc['kind']} arrival, {args.preset} sizes, random bf16 weights)",
+        "value": round(generated / wall, 1),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "higher_is_better": True,
+        "dtype": "bf16",
+        "data": "synthetic: uniform random token ids, random N(0,0.02) weights (seed 0)",
+        "config": {
+            "model": f"{args.preset} sizes", "layers": raw["num_hidden_layers"], "layers_of_full_model": full_layers,
+            "hidden": raw["hidden_size"], "heads": raw["num_attention_heads"], "kv_heads": raw["num_key_value_heads"],
+            "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"],
+            "requests": sc["requests"], "prompt_min": lo, "prompt_max": hi, "new_tokens": sc["new_tokens"],
+            "max_batch_size": sc["max_batch"], "max_seq_len": sc["max_seq_len"], "block_size": block_size,
+            "pool_pages": num_blocks, "arrival": sc["kind"],
+        },
+        "wall_s": round(wall, 3),
+        "prompt_tokens": int(sum(lengths)),
+        "prefill_tokens_run": int(engine.counters["prefill_tokens"]),
+        "decode_tokens_run": int(engine.counters["decode_tokens"]),
+        "steps": int(engine.counters["steps"]),
+        "preemptions": int(engine.scheduler.num_preemptions),
+        "clocks": clocks,
+    }
+
+
 def run_reference(args) -> dict:
     sys.path.insert(0, ROOT)
     from baseline import reference_arm
@@ -415,6 +505,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the full model (named in config)")
     ap.add_argument("--kernel", default=None, help="time one kernel alone (see gllm_b200/kernel_bench.py)")
     ap.add_argument("--shape", default="", help="with --kernel: overrides such as batch=8,context=2048")
+    ap.add_argument("--preset", default=None, choices=sorted(SCENARIOS),
+                    help="a whole-engine scenario at another model size (a line of its own, not the headline)")
     args = ap.parse_args()
     if args.kernel:
         from gllm_b200 import kernel_bench
@@ -425,6 +517,9 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py measures one GPU only: this engine does not run on {args.gpus} GPUs")
         return 2
+    if args.preset:
+        print(json.dumps(run_scenario(args)))
+        return 0
     args.warmup = max(3, args.warmup)
     # a repetition's context grows from `context + warmup` to `context + warmup + steps` tokens
     args.steps = max(1, min(args.steps, BENCH_SIZES["max_seq_len"] - BENCH_SIZES["context"] - args.warmup - 2))
