@@ -101,18 +101,22 @@ def attention_prefill(tokens=2048, context=0, hq=32, hkv=8, d=64, block_size=16,
             "shape": dict(tokens=tokens, context=context, heads=hq, kv_heads=hkv, head_dim=d, block_size=block_size)}
 
 
-def linear(m=8, n=16384, k=2048, iters=5, peaks=None, out_fp32=False, gated=0, split=0):
+def linear(m=8, n=16384, k=2048, iters=5, peaks=None, out_fp32=False, gated=0, split=0, acc=0):
     """x [m, k] times a [n, k] weight.  ``gated``: the weight is a gate/up stack (n = 2 x features) and
     the epilogue writes SiLU(gate) * up.  ``split``: a product cut along K leaves its splits unsummed,
-    as the decode step's products do (their consumers add them)."""
+    as the decode step's products do (their consumers add them).  ``acc``: the product adds itself into
+    an fp32 matrix (the residual stream), as the products that end a branch do for up to 64 tokens."""
     from gllm_b200 import ops
 
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
     out = torch.empty(m, n, dtype=torch.float32 if out_fp32 else torch.bfloat16, device="cuda")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    resid = torch.zeros(m, n, dtype=torch.float32, device="cuda")
     if gated:
         fn = lambda: ops.linear_gated(x, w)
+    elif acc:
+        fn = lambda: ops.linear(x, w, split_ok=True, add_into=resid)
     elif split:
         fn = lambda: ops.linear(x, w, split_ok=True)
     else:
@@ -121,7 +125,8 @@ def linear(m=8, n=16384, k=2048, iters=5, peaks=None, out_fp32=False, gated=0, s
     nbytes = (m * k + n * k) * 2 + out.numel() * out.element_size()
     flops = 2.0 * m * n * k
     gbs, tf = nbytes / us / 1e3, flops / us / 1e6
-    name = "linear (gated epilogue)" if gated else ("linear (unsummed splits)" if split else "linear")
+    name = "linear (gated epilogue)" if gated else ("linear (adds into the residual)" if acc else
+                                                     ("linear (unsummed splits)" if split else "linear"))
     return {"kernel": name, "us": round(us, 2), "achieved_gbs": round(gbs, 1), "achieved_tflops": round(tf, 1),
             "frac_of_hbm_peak": round(gbs / peaks["hbm_gbs"], 4), "frac_of_bf16_peak": round(tf / peaks["bf16_tflops"], 4),
             "shape": dict(m=m, n=n, k=k)}
@@ -141,6 +146,47 @@ def linear_f32(m=2048, n=8192, k=2048, iters=5, peaks=None):
     return {"kernel": "linear_f32 (FFMA)", "us": round(us, 2), "achieved_tflops": round(flops / us / 1e6, 1),
             "achieved_gbs": round(nbytes / us / 1e3, 1), "frac_of_hbm_peak": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4),
             "shape": dict(m=m, n=n, k=k)}
+
+
+def decode_step(batch=8, context=2048, layers=2, iters=3, peaks=None):
+    """Whole decode steps of a model with the Llama 3.2 1B layer sizes and ``layers`` layers, every kernel
+    launched on its own (no CUDA graph), so that a profiler lists them one by one."""
+    import os
+    import shutil
+    import tempfile
+
+    from gllm_b200 import GenerationRequest, GeneratorParams, LLMEngine
+    from gllm_b200.config import load_config
+    from gllm_b200.config.presets import load_preset
+    from gllm_b200.weights import write_random_model
+
+    raw = load_preset("llama-3.2-1b")
+    raw["num_hidden_layers"] = layers
+    tmp = tempfile.mkdtemp(prefix="gllm_b200_kernel_bench_")
+    try:
+        folder = write_random_model(os.path.join(tmp, "model"), load_config(raw), seed=0, std=0.02)
+        params = GeneratorParams(block_size=16, max_batch_size=max(batch, 8), max_seq_len=4096, model_dtype="bfloat16",
+                                 cuda_graphs=False)
+        engine = LLMEngine(folder, params, device="cuda:0")
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+    g = torch.Generator().manual_seed(0)
+    vocab = engine.config.vocab_size
+    states = [engine.submit(GenerationRequest(prompt_token_ids=torch.randint(0, vocab, (context,), generator=g).tolist(),
+                                              max_new_tokens=64, temperature=0.0, ignore_eos=True)) for _ in range(batch)]
+    while any(s.num_computed < len(s.prompt_token_ids) for s in states):
+        engine.step()
+    for _ in range(3):
+        engine.step()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        engine.step()
+    end.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(end) * 1e3 / iters
+    return {"kernel": "decode_step (no graph)", "us": round(us, 2), "shape": dict(batch=batch, context=context, layers=layers)}
 
 
 def add_rmsnorm(rows=8, hidden=2048, splits=8, iters=5, peaks=None):
@@ -179,6 +225,7 @@ KERNELS = {
     "attention_prefill": attention_prefill,
     "linear": linear,
     "linear_f32": linear_f32,
+    "decode_step": decode_step,
     "add_rmsnorm": add_rmsnorm,
     "argmax": argmax,
 }
