@@ -10,8 +10,13 @@ Here, per step, under a token budget (``max_num_batched_tokens``):
   2. running requests still in their prompt get a portion
      (<= ``prefill_chunk``, <= budget left);
   3. waiting requests are admitted first-come first-served while a state slot,
-     budget and pages for their first portion are there.  A full engine leaves
-     requests waiting; only impossible requests are refused at ``add``.
+     budget and pages are there: pages for the first portion now, and, beside
+     what the running requests still need for the rest of THEIR prompts, pages
+     for the rest of this one (so a prompt that is admitted can be finished;
+     without this reservation long prompts over a small pool were admitted on
+     their first portion, preempted on a later one and recomputed, again and
+     again).  A full engine leaves requests waiting; only impossible requests
+     are refused at ``add``.
 When pages run out while a running request needs one more, the most recently
 admitted running request is preempted: its pages and slot are given back at
 once, it returns to the head of the waiting queue and later recomputes its
@@ -167,6 +172,16 @@ class Scheduler:
                 self._preempt(victim, step)
                 if victim is req:
                     break
+        # pages the running requests will still ask for to hold the tokens they are known to have
+        # (the rest of their prompts), beyond what they hold and what this step promised them
+        reserved = {g: 0 for g in groups}
+        for req in self.running:
+            if req.id in self.cache.requests:
+                rest = self.cache.pages_needed(req.id, req.num_tokens - self.cache.requests[req.id].num_tokens)
+            else:
+                rest = self.cache.pages_for_admission(req.num_tokens)
+            for g, n in rest.items():
+                reserved[g] += max(0, n - promised.get(id(req), {}).get(g, 0))
         # 3: admissions, first come first served
         while self.waiting and budget > 0 and len(self.running) < self.params.max_batch_size:
             req = self.waiting[0]
@@ -178,6 +193,12 @@ class Scheduler:
             need = self.cache.pages_for_admission(n)
             if not fits(need):
                 break
+            whole = self.cache.pages_for_admission(req.num_tokens)
+            if self.running and not all(
+                    self.cache.groups[g].allocator.num_free - taken[g] - reserved[g] >= whole[g] for g in groups):
+                break  # its whole prompt would not fit beside what the running prompts still need
+            for g in groups:
+                reserved[g] += whole[g] - need[g]
             promise(req, need)
             new_slots += 1
             self.waiting.popleft()

@@ -206,3 +206,29 @@ def test_running_ahead_reads_tokens_one_step_late():
     assert a.num_inflight == 0 and b.num_inflight == 0
     assert cache.num_free_pages() == 32 and cache.slots.num_free == 4
     cache.check_invariants()
+
+
+def test_a_prompt_is_admitted_only_when_all_of_it_fits_beside_the_running_prompts():
+    # 10 pages of 4 tokens, portions of 8 tokens: three prompts of 24 tokens (6 pages each).  Admitted on their
+    # first portion alone, the second would take pages the first still needs and one of them would be preempted
+    # and recomputed; with the reservation the second waits until the first has finished, and nothing is preempted.
+    params, cache, sched = setup(num_blocks=10, budget=16, chunk=8, max_seq_len=40, max_batch=4)
+    reqs = [request(f"r{i}", 24, max_new=2) for i in range(3)]
+    for r in reqs:
+        sched.add(r)
+    steps = 0
+    most_running = 0
+    while sched.has_work:
+        step, _ = run_step(sched, cache)
+        most_running = max(most_running, len(sched.running))
+        assert not step.preempted
+        steps += 1
+        assert steps < 100
+    assert sched.num_preemptions == 0 and all(r.is_finished for r in reqs)
+    assert most_running == 1                       # 6 + 6 pages never fit the 10
+    # short prompts still share the engine: four of 8 tokens (2 pages each, 3 with their generated tokens)
+    params, cache, sched = setup(num_blocks=12, budget=32, chunk=8, max_seq_len=16, max_batch=4)
+    for i in range(4):
+        sched.add(request(f"s{i}", 8, max_new=3))
+    run_step(sched, cache)
+    assert len(sched.running) == 4
