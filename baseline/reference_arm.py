@@ -152,7 +152,7 @@ def decode_ms_per_step(engine, batch, context, vocab, warmup, steps, reps, block
     return diffs[len(diffs) // 2], shorts[len(shorts) // 2], len(diffs)
 
 
-def run(args, peaks: dict, raw_config: dict, sampler_cls, sizes: dict, bench_config) -> dict:
+def run(args, peaks: dict, raw_config: dict, sampler_cls, sizes: dict, bench_config, settle: int = 0) -> dict:
     if not os.path.isdir(os.path.join(REF_ROOT, "gllm", "engine")):
         return {"impl": "reference", "unavailable": "the reference's gllm/ tree is not under baseline/_ref"}
     tmp = tempfile.mkdtemp(prefix="gllm_ref_bench_")
@@ -166,6 +166,8 @@ def run(args, peaks: dict, raw_config: dict, sampler_cls, sizes: dict, bench_con
         block_size, prefill_tokens = sizes["block_size"], sizes["prefill_tokens"]
         vocab = raw_config["vocab_size"]
         reps = 3
+        # steps that are not timed after the prefill: this repository's arm lets the clocks settle first
+        warm = args.warmup + settle
         # one engine sized like this repository's arm (64 requests of 4,096 tokens) serves batch 1 and 8
         engine = make_engine(local_cache, 64, max_seq_len, block_size)
         blocks_left = [64 * max_seq_len // block_size - 1]
@@ -182,12 +184,12 @@ def run(args, peaks: dict, raw_config: dict, sampler_cls, sizes: dict, bench_con
         pf.sort()
         prefill_ms = pf[len(pf) // 2]
         points, points_ms = {}, {}
-        b1_ms, _, _ = decode_ms_per_step(engine, 1, context, vocab, args.warmup, args.steps, reps, blocks_left)
+        b1_ms, _, _ = decode_ms_per_step(engine, 1, context, vocab, warm, args.steps, reps, blocks_left)
         points["decode_b1"], points_ms["decode_b1"] = round(1000.0 / b1_ms, 1), round(b1_ms, 4)
         clock = sampler_cls(0)
         clock.start()
         batch = 8
-        dev_ms, t_short, n_pairs = decode_ms_per_step(engine, batch, context, vocab, args.warmup, args.steps, reps,
+        dev_ms, t_short, n_pairs = decode_ms_per_step(engine, batch, context, vocab, warm, args.steps, reps,
                                                       blocks_left)
         clocks = clock.stop()
         del engine
@@ -195,12 +197,12 @@ def run(args, peaks: dict, raw_config: dict, sampler_cls, sizes: dict, bench_con
         # batch 64 fills more than half of the pages of an engine made for 64 requests: one call per engine
         try:
             times = {}
-            for new_tokens in (1 + args.warmup, 1 + args.warmup + args.steps):
+            for new_tokens in (1 + warm, 1 + warm + args.steps):
                 engine = make_engine(local_cache, 64, max_seq_len, block_size)
                 times[new_tokens] = timed_generate(engine, _prompts(64, context, vocab, 300), new_tokens)
                 del engine
                 torch.cuda.empty_cache()
-            b64_ms = (times[1 + args.warmup + args.steps] - times[1 + args.warmup]) / args.steps
+            b64_ms = (times[1 + warm + args.steps] - times[1 + warm]) / args.steps
             points["decode_b64"], points_ms["decode_b64"] = round(64 * 1000.0 / b64_ms, 1), round(b64_ms, 4)
         except Exception as e:      # noqa: BLE001 - the headline does not depend on this point
             points["decode_b64"], points_ms["decode_b64"] = None, f"{type(e).__name__}: {e}"[:200]
@@ -212,7 +214,7 @@ def run(args, peaks: dict, raw_config: dict, sampler_cls, sizes: dict, bench_con
         * raw_config["head_dim"] + raw_config["num_attention_heads"] * raw_config["head_dim"] * raw_config["hidden_size"]
         + 3 * raw_config["hidden_size"] * raw_config["intermediate_size"]))
     kv_per_token = 2 * 2 * raw_config["num_hidden_layers"] * raw_config["num_key_value_heads"] * raw_config["head_dim"]
-    step_bytes = wbytes + batch * (context + args.warmup + args.steps // 2) * kv_per_token
+    step_bytes = wbytes + batch * (context + warm + args.steps // 2) * kv_per_token
     achieved = step_bytes / (dev_ms * 1e-3) / 1e9
     value = batch * 1000.0 / dev_ms
     return {
@@ -231,7 +233,7 @@ def run(args, peaks: dict, raw_config: dict, sampler_cls, sizes: dict, bench_con
         "data": "synthetic: uniform random token ids, random N(0,0.02) weights (seed 0)",
         "config": bench_config(raw_config, batch, peaks, "greedy (top_k=1), inside the step"),
         "timing": (f"stock LLMEngine.generate(), wall clock between synchronizes; ms_per_step = median of {n_pairs} "
-                   f"x (t({1 + args.warmup + args.steps} tokens) - t({1 + args.warmup} tokens)) / {args.steps}; "
+                   f"x (t({1 + warm + args.steps} tokens) - t({1 + warm} tokens)) / {args.steps}; "
                    "the reference has no llama3 frequency scaling (plain rope_theta)"),
         "e2e": {
             "value": round(value, 1),

@@ -175,9 +175,16 @@ def drain(engine, states):
         engine.abort(s.id)
 
 
+# Untimed decode steps between a repetition's prefill and its warm-up steps: the prefill of the batch
+# (16k tokens at batch 8) runs the GPU into its power cap, and the decode steps right after it run at
+# the lowered clock (1.09 ms a step instead of 0.96 for about thirty steps); a decode benchmark measures
+# the state decoding settles in.
+SETTLE_STEPS = 48
+
+
 def time_decode(engine, batch: int, context: int, steps: int, warmup: int, reps: int = 5):
-    """``reps`` repetitions of: fill the engine with ``batch`` requests of ``context`` cached tokens, ``warmup``
-    untimed steps, then ``steps`` timed ones.  Device time (CUDA events) and wall time (host clock, a
+    """``reps`` repetitions of: fill the engine with ``batch`` requests of ``context`` cached tokens,
+    ``SETTLE_STEPS`` + ``warmup`` untimed steps, then ``steps`` timed ones.  Device time (CUDA events) and wall time (host clock, a
     synchronize on both sides) are taken around the SAME loop of ``LLMEngine.step()`` calls, each of which
     copies the step's metadata from pinned host memory and reads the sampled tokens of the step before it.
     Returns the medians: (device ms per step, wall ms per step, launches per step, h2d, d2h)."""
@@ -189,7 +196,7 @@ def time_decode(engine, batch: int, context: int, steps: int, warmup: int, reps:
     launches = h2d = d2h = 0
     for _ in range(reps):
         states = fill_engine(engine, batch, context)
-        for _ in range(warmup):
+        for _ in range(SETTLE_STEPS + warmup):
             engine.step()
         torch.cuda.synchronize()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -283,6 +290,7 @@ def bench_config(raw: dict, batch: int, peaks: dict, sampling: str) -> dict:
         "sampling": sampling,
         "peaks": peaks["source"],
         "repetitions": "median of 5",
+        "settle_steps": SETTLE_STEPS,
     }
 
 
@@ -319,7 +327,7 @@ def run_ours(args) -> dict:
     reps = 5
 
     def step_bytes(b):
-        return wbytes + b * (context + args.warmup + steps // 2) * kv_per_token
+        return wbytes + b * (context + SETTLE_STEPS + args.warmup + steps // 2) * kv_per_token
 
     points, points_ms, rooflines, e2e_points = {}, {}, {}, {}
     for b in (1, 64):
@@ -488,7 +496,7 @@ def run_reference(args) -> dict:
     args.warmup_prefill = 3
     peaks = load_peaks()
     try:
-        return reference_arm.run(args, peaks, raw, ClockSampler, BENCH_SIZES, bench_config)
+        return reference_arm.run(args, peaks, raw, ClockSampler, BENCH_SIZES, bench_config, settle=SETTLE_STEPS)
     except Exception as e:      # noqa: BLE001 - the arm reports why it has no number instead of failing the run
         import traceback
 
@@ -522,7 +530,7 @@ def main() -> int:
         return 0
     args.warmup = max(3, args.warmup)
     # a repetition's context grows from `context + warmup` to `context + warmup + steps` tokens
-    args.steps = max(1, min(args.steps, BENCH_SIZES["max_seq_len"] - BENCH_SIZES["context"] - args.warmup - 2))
+    args.steps = max(1, min(args.steps, BENCH_SIZES["max_seq_len"] - BENCH_SIZES["context"] - SETTLE_STEPS - args.warmup - 2))
     if args.impl == "reference":
         print(json.dumps(run_reference(args)))
         return 0
