@@ -35,6 +35,33 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Two fp32 operations in one instruction (sm_100: fma.rn.f32x2, add.rn.f32x2 on register pairs) and
+// the maximum of three: the softmax below is bound by the number of instructions it issues per score.
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  unsigned long long ra, rb, rc, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  unsigned long long ra, rb, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <int D>
 struct TShape {
   static constexpr int DB = D / 64;                     // 64-wide blocks of the head dimension
@@ -271,7 +298,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+          for (int i = 0; i < 32; i += 2) mx = fmax3(mx, v[i], v[i + 1]);
         }
       }
       row_max[hsel][row] = mx;
@@ -318,15 +345,18 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
           }
         } else {
+          float2 lsum = make_float2(l0, l1);
+          const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(neg_mc, neg_mc);
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float p0 = fast_exp2(fmaf(v[i], scale_log2, neg_mc));
-            const float p1 = fast_exp2(fmaf(v[i + 1], scale_log2, neg_mc));
-            l0 += p0;
-            l1 += p1;
-            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            const float2 t = ffma2(make_float2(v[i], v[i + 1]), sc2, nm2);
+            const float2 pr = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+            lsum = fadd2(lsum, pr);
+            __nv_bfloat162 h = __floats2bfloat162_rn(pr.x, pr.y);
             packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
           }
+          l0 = lsum.x;
+          l1 = lsum.y;
         }
         tmem_st16_b32(tmem_p + (uint32_t)(c >> 1), packed);   // keys c .. c+31 = 16 columns of two bf16
       }
