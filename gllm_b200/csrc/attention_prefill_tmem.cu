@@ -304,7 +304,11 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       row_max[hsel][row] = mx;
       asm volatile("bar.sync 2, 256;" ::: "memory");
       mx = fmaxf(mx, row_max[hsel ^ 1][row]);
-      const float m_new = fmaxf(m, mx);
+      // The reference maximum moves only when the row's maximum has grown by more than 2^8 in the
+      // exponent: until then the exponentials are taken against the old one (they stay below 256, exact
+      // enough in fp32 and bf16, and the final division by the row's sum takes the common factor out),
+      // and the output so far needs no rescaling, which is the usual case after a row's first tiles.
+      const float m_new = (m == -INFINITY || (mx - m) * scale_log2 > 8.0f) ? fmaxf(m, mx) : m;
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       const float corr = m == -INFINITY ? 0.f : fast_exp2((m - m_use) * scale_log2);
       const float neg_mc = -m_use * scale_log2;
