@@ -270,7 +270,7 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
   const float* ml = part_ml + ((int64_t)n * hq + h) * num_chunks * 2;
   const float* po = part_o + ((int64_t)n * hq + h) * num_chunks * D;
   float mm = -INFINITY, o = 0.f, l = 0.f;
-  constexpr int B = 8;                                    // chunks whose loads are in flight together
+  constexpr int B = 16;                                   // chunks whose loads are in flight together
   for (int s0 = first; s0 < last; s0 += B) {
     float ms[B], ls[B], os[B];
 #pragma unroll
