@@ -269,28 +269,67 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
           }
         } else {
-          // rows 0..63 of the tile are gates, rows 64..127 the ups of the same 64 features: the
-          // upper half hands its values to the lower half through shared memory
+          // rows 0..63 of the tile are gates, rows 64..127 the ups of the same 64 features.  The two
+          // halves trade values through shared memory so that both work: of every 32 token columns the
+          // gate rows finish the first 16 (with the ups handed over) and the up rows the second 16 (with
+          // the gates handed over); with 16 columns in all only the gate rows have work.
           __shared__ float exch[64][(BN <= 64 ? BN : 1) + 1];
+          constexpr int CH = BN >= 32 ? 32 : 16;
+          const int f = item.a_row0 / 2 + (row & 63);
 #pragma unroll 1
-          for (int c = 0; c < BN; c += 16) {
-            float v[16];
-            tmem_ld16(taddr + (uint32_t)c, v);
+          for (int c = 0; c < BN; c += CH) {
+            float v[CH];
+            tmem_ld_cols(taddr + (uint32_t)c, v);
             if (row >= 64) {
 #pragma unroll
               for (int i = 0; i < 16; ++i) exch[row - 64][c + i] = v[i];
+            } else if (CH == 32) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) exch[row][c + 16 + i] = v[CH - 16 + i];
             }
             epilogue_sync();
-            if (row < 64) {
-              const int f = item.a_row0 / 2 + row;
-              if (f < n_out) {
+            if (f < n_out && (row < 64 || CH == 32)) {
+              const int off = row < 64 ? 0 : 16;               // which 16 columns this thread finishes
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                  const int m = item.b_row0 + c + i;
-                  if (m < M) {
-                    const float g = v[i], u = exch[row][c + i];
-                    out[(int64_t)m * ldo + f] = cast_out<OutT>(g / (1.0f + __expf(-g)) * u);
-                  }
+              for (int i = 0; i < 16; ++i) {
+                const int m = item.b_row0 + c + off + i;
+                if (m < M) {
+                  const float mine_v = row < 64 ? v[i] : v[CH - 16 + i], other = exch[row & 63][c + off + i];
+                  const float g = row < 64 ? mine_v : other, u = row < 64 ? other : mine_v;
+                  out[(int64_t)m * ldo + f] = cast_out<OutT>(g / (1.0f + __expf(-g)) * u);
+                }
+              }
+            }
+          }
+        }
+      } else if (SWAPPED) {
+        // the accumulator's rows are weight rows, its columns tokens: 32 columns a load where there are that many
+        constexpr int CH = BN >= 32 ? 32 : 16;
+        const int n = item.a_row0 + row;                 // weight row
+#pragma unroll 1
+        for (int c = 0; c < BN; c += CH) {
+          float v[CH];
+          if (has_k) {
+            tmem_ld_cols(taddr + (uint32_t)c, v);
+          } else {
+#pragma unroll
+            for (int i = 0; i < CH; ++i) v[i] = 0.f;
+          }
+          if (n < N) {
+#pragma unroll
+            for (int i = 0; i < CH; ++i) {
+              const int m = item.b_row0 + c + i;         // token
+              if (m < M) {
+                const float val = v[i];
+                if (accumulate) {
+                  // every split adds its part into the fp32 matrix itself (a warp's 32 rows are contiguous)
+                  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(reinterpret_cast<float*>(out) + (int64_t)m * ldo + n),
+                               "f"(val)
+                               : "memory");
+                } else if (splits > 1) {
+                  mine[(int64_t)m * N + n] = val;
+                } else {
+                  out[(int64_t)m * ldo + n] = cast_out<OutT>(val);
                 }
               }
             }
@@ -306,61 +345,38 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
           for (int i = 0; i < 16; ++i) v[i] = 0.f;
         }
-        if (!SWAPPED) {
-          const int m = item.a_row0 + row, n0 = item.b_row0 + c;
-          if (m < M && n0 < N) {
-            if (splits > 1) {
-              float* dst = mine + (int64_t)m * N + n0;
-              if (n0 + 16 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+        const int m = item.a_row0 + row, n0 = item.b_row0 + c;
+        if (m < M && n0 < N) {
+          if (splits > 1) {
+            float* dst = mine + (int64_t)m * N + n0;
+            if (n0 + 16 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            } else {
+              for (int i = 0; i < 16 && n0 + i < N; ++i) dst[i] = v[i];
+            }
+          } else {
+            OutT* dst = out + (int64_t)m * ldo + n0;
+            if (n0 + 16 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+              if (sizeof(OutT) == 2) {
+                uint4 p0, p1;
+                __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&p0);
+                __nv_bfloat162* h1 = reinterpret_cast<__nv_bfloat162*>(&p1);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  h0[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                  h1[i] = __floats2bfloat162_rn(v[8 + 2 * i], v[8 + 2 * i + 1]);
+                }
+                reinterpret_cast<uint4*>(dst)[0] = p0;
+                reinterpret_cast<uint4*>(dst)[1] = p1;
+              } else {
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
                   reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-              } else {
-                for (int i = 0; i < 16 && n0 + i < N; ++i) dst[i] = v[i];
               }
             } else {
-              OutT* dst = out + (int64_t)m * ldo + n0;
-              if (n0 + 16 <= N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-                if (sizeof(OutT) == 2) {
-                  uint4 p0, p1;
-                  __nv_bfloat162* h0 = reinterpret_cast<__nv_bfloat162*>(&p0);
-                  __nv_bfloat162* h1 = reinterpret_cast<__nv_bfloat162*>(&p1);
-#pragma unroll
-                  for (int i = 0; i < 4; ++i) {
-                    h0[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-                    h1[i] = __floats2bfloat162_rn(v[8 + 2 * i], v[8 + 2 * i + 1]);
-                  }
-                  reinterpret_cast<uint4*>(dst)[0] = p0;
-                  reinterpret_cast<uint4*>(dst)[1] = p1;
-                } else {
-#pragma unroll
-                  for (int i = 0; i < 4; ++i)
-                    reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                }
-              } else {
-                for (int i = 0; i < 16 && n0 + i < N; ++i) dst[i] = cast_out<OutT>(v[i]);
-              }
-            }
-          }
-        } else {
-          const int n = item.a_row0 + row;               // weight row
-          if (n < N) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int m = item.b_row0 + c + i;         // token
-              if (m < M) {
-                const float val = v[i];
-                if (accumulate) {
-                  // every split adds its part into the fp32 matrix itself (a warp's 32 rows are contiguous)
-                  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(reinterpret_cast<float*>(out) + (int64_t)m * ldo + n),
-                               "f"(val)
-                               : "memory");
-                } else if (splits > 1) {
-                  mine[(int64_t)m * N + n] = val;
-                } else {
-                  out[(int64_t)m * ldo + n] = cast_out<OutT>(val);
-                }
-              }
+              for (int i = 0; i < 16 && n0 + i < N; ++i) dst[i] = cast_out<OutT>(v[i]);
             }
           }
         }

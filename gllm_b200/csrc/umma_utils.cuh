@@ -184,3 +184,6 @@ static __device__ __forceinline__ void tmem_ld_fence16(float* v) {
                     "+f"(v[8]), "+f"(v[9]), "+f"(v[10]), "+f"(v[11]), "+f"(v[12]), "+f"(v[13]), "+f"(v[14]),
                     "+f"(v[15])::"memory");
 }
+// One waited load of as many columns as the array holds (16 or 32).
+static __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, float (&v)[16]) { tmem_ld16(taddr, v); }
+static __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, float (&v)[32]) { tmem_ld32(taddr, v); }
