@@ -24,6 +24,11 @@
 // multiplied, so stale pool contents never reach the output.  Every mbarrier wait is bounded.
 // No TMA load uses cluster multicast.
 #include "umma_utils.cuh"
+#include <type_traits>
+
+#ifndef GLLM_PREFILL_SPECULATE
+#define GLLM_PREFILL_SPECULATE (NB == 1)
+#endif
 
 namespace {
 constexpr int BM = 128, BN = 128, THREADS = 320;       // TMA warp, MMA warp, eight softmax warps
@@ -60,6 +65,42 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
+}
+
+// One chunk of 32 scores of a row.  MASKED: key i of the chunk is seen iff (unsigned)(key_rel + i) <= span.
+// WITH_MAX: the maximum of the seen scores joins mx.  WITH_EXP: probabilities 2^(v * scale_log2 + neg_mc) of
+// the seen scores (0 for the others) are summed into lsum (two running sums) and packed as bf16 pairs.
+template <bool MASKED, bool WITH_MAX, bool WITH_EXP>
+__device__ __forceinline__ void softmax_chunk(const float (&v)[32], int key_rel, unsigned span, float scale_log2,
+                                              float neg_mc, float& mx, float2& lsum, uint32_t (&packed)[16]) {
+  if (MASKED) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      const bool s0 = (unsigned)(key_rel + i) <= span, s1 = (unsigned)(key_rel + i + 1) <= span;
+      if (WITH_MAX) mx = fmax3(mx, s0 ? v[i] : -INFINITY, s1 ? v[i + 1] : -INFINITY);
+      if (WITH_EXP) {
+        const float p0 = s0 ? fast_exp2(fmaf(v[i], scale_log2, neg_mc)) : 0.f;
+        const float p1 = s1 ? fast_exp2(fmaf(v[i + 1], scale_log2, neg_mc)) : 0.f;
+        lsum.x += p0;
+        lsum.y += p1;
+        __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+  } else {
+    const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(neg_mc, neg_mc);
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      if (WITH_MAX) mx = fmax3(mx, v[i], v[i + 1]);
+      if (WITH_EXP) {
+        const float2 t = ffma2(make_float2(v[i], v[i + 1]), sc2, nm2);
+        const float2 pr = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+        lsum = fadd2(lsum, pr);
+        __nv_bfloat162 h = __floats2bfloat162_rn(pr.x, pr.y);
+        packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+      }
+    }
+  }
 }
 
 template <int D>
@@ -210,45 +251,71 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
   } else if (active && warp == 1) {
     // -------------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = umma_idesc(BM, BN);
+    // The whole warp runs the loop with warp-uniform values and waits on the barriers; one elected thread
+    // issues the products and their commits (in a branch that only lane 0 takes, every tcgen05.mma cost
+    // about 110 cycles to issue, whatever its size; here about 40).
+    {
+      const bool leader = elect_one();
+      const int n_tiles_u = __shfl_sync(0xffffffffu, n_tiles, 0);
+      auto wait_u = [&](uint64_t* bar, uint32_t parity) -> bool {
+        // every lane waits: a single waiting lane under a branch made each wait several hundred cycles longer
+        const bool good = mbar_wait(smem_addr(bar), parity, status, &abort_flag);
+        return __all_sync(0xffffffffu, good) != 0;
+      };
       constexpr uint32_t idesc_o = umma_idesc_b_mn(BM, 64);
+      constexpr uint32_t idesc_s = umma_idesc(BM, BN);
       const uint32_t tmem_s = tmem_base + S::COL_S, tmem_o = tmem_base + S::COL_O, tmem_p = tmem_base + S::COL_P;
-      auto issue_s = [&](int j) -> bool {
+      // descriptors once: a tile's address sits in the low 14 bits (in units of 16 bytes), so the other
+      // tiles' descriptors are this one plus a constant
+      const uint64_t desc_q = umma_desc(base + S::OFF_Q), desc_k = umma_desc(base + S::OFF_K),
+                     desc_v = umma_desc(base + S::OFF_V);
+      auto wait_k = [&](int j) -> bool { return wait_u(&k_full[j % KS], (uint32_t)(j / KS) & 1u); };
+      auto issue_s = [&](int j) -> bool {                // after wait_k(j)
         const int s = j % KS, sb = j % NB;
-        if (!mbar_wait(smem_addr(&k_full[s]), (uint32_t)(j / KS) & 1u, status, &abort_flag)) return false;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t dk = desc_k + (uint64_t)((s * S::KV_STAGE) >> 4);
+        if (leader) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int db = 0; db < S::DB; ++db)
+          for (int db = 0; db < S::DB; ++db)
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem_s + sb * BN, umma_desc(base + S::OFF_Q + db * S::TILE + k * 32),
-                      umma_desc(base + S::OFF_K + s * S::KV_STAGE + db * S::TILE + k * 32), idesc_s,
-                      (db > 0 || k > 0) ? 1u : 0u);
-        umma_commit(smem_addr(&k_empty[s]));            // K of this stage is consumed
-        umma_commit(smem_addr(&s_full[sb]));
+            for (int k = 0; k < 4; ++k)
+              umma_bf16(tmem_s + sb * BN, desc_q + (uint64_t)((db * S::TILE + k * 32) >> 4),
+                        dk + (uint64_t)((db * S::TILE + k * 32) >> 4), idesc_s, (db > 0 || k > 0) ? 1u : 0u);
+          umma_commit(smem_addr(&k_empty[s]));            // K of this stage is consumed
+          umma_commit(smem_addr(&s_full[sb]));
+        }
+        __syncwarp();
         return true;
       };
-      // scores run one tile ahead of the softmax: S(j+1) is computed while tile j is exponentiated
-      bool ok = mbar_wait(smem_addr(&q_full), 0u, status, &abort_flag);
-      if (ok) ok = issue_s(0);
-      if (NB > 1 && ok && n_tiles > 1) ok = issue_s(1);
-      for (int j = 0; j < n_tiles && ok; ++j) {
+      // Scores run ahead of the softmax.  Two score buffers: S(j+1) is computed while tile j is
+      // exponentiated.  One buffer: S(j+1) is issued as soon as the softmax has read S(j), BEFORE P(j) V(j),
+      // so that the softmax of tile j+1 starts while that product still runs (it waits for it before it
+      // overwrites P).
+      bool ok = wait_u(&q_full, 0u);
+      if (ok) ok = wait_k(0) && issue_s(0);
+      if (NB > 1 && ok && n_tiles_u > 1) ok = wait_k(1) && issue_s(1);
+      for (int j = 0; j < n_tiles_u && ok; ++j) {
         const int s = j % KS;
-        ok = mbar_wait(smem_addr(&p_full), (uint32_t)j & 1u, status, &abort_flag);   // P(j) written, S(j) read
-        if (ok) ok = mbar_wait(smem_addr(&v_full[s]), (uint32_t)(j / KS) & 1u, status, &abort_flag);
+        // (the keys of the next tile arrive long before the softmax is done: wait for them first)
+        if (NB == 1 && j + 1 < n_tiles_u) ok = wait_k(j + 1);
+        if (ok) ok = wait_u(&p_full, (uint32_t)j & 1u);  // P(j) written, S(j) read
+        if (NB == 1 && ok && j + 1 < n_tiles_u) ok = issue_s(j + 1);
+        if (ok) ok = wait_u(&v_full[s], (uint32_t)(j / KS) & 1u);
         if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint64_t dv = desc_v + (uint64_t)((s * S::KV_STAGE) >> 4);
+        if (leader) {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-        for (int db = 0; db < S::DB; ++db)
+          for (int db = 0; db < S::DB; ++db)
 #pragma unroll
-          for (int k = 0; k < 8; ++k)      // 16 keys per MMA: 8 columns of P (two bf16 each); V rows 16 k ..
-            umma_bf16_ts(tmem_o + db * 64, tmem_p + k * 8,
-                         umma_desc(base + S::OFF_V + s * S::KV_STAGE + db * S::TILE + k * 16 * 128), idesc_o,
-                         (j > 0 || k > 0) ? 1u : 0u);
-        umma_commit(smem_addr(&v_empty[s]));            // V of this stage is consumed
-        umma_commit(smem_addr(&o_ready));               // O holds tiles 0 .. j, P may be overwritten
-        if (j + NB < n_tiles) ok = issue_s(j + NB);
+            for (int k = 0; k < 8; ++k)    // 16 keys per MMA: 8 columns of P (two bf16 each); V rows 16 k ..
+              umma_bf16_ts(tmem_o + db * 64, tmem_p + k * 8, dv + (uint64_t)((db * S::TILE + k * 16 * 128) >> 4),
+                           idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+          umma_commit(smem_addr(&v_empty[s]));            // V of this stage is consumed
+          umma_commit(smem_addr(&o_ready));               // O holds tiles 0 .. j, P may be overwritten
+        }
+        __syncwarp();
+        if (NB > 1 && j + NB < n_tiles_u) ok = wait_k(j + NB) && issue_s(j + NB);
       }
     }
   } else if (active && warp >= 2) {
@@ -270,6 +337,11 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const uint32_t tmem_p = tmem_base + S::COL_P + lane_addr + (uint32_t)(hsel * HK / 2);
     float m = -INFINITY, l = 0.f;
     bool ok = true;
+    // Head size 64: one pass per tile.  The probabilities are taken against the reference maximum the row
+    // already has while the tile's maximum is found on the side; only when some row's maximum has outgrown
+    // its reference (or the row had none) does the warp take the tile again against the new one.
+    constexpr bool SPECULATE = GLLM_PREFILL_SPECULATE;
+    enum { CHUNK_SKIP = 0, CHUNK_FAST = 1, CHUNK_MASK = 2 };
     for (int j = 0; j < n_tiles; ++j) {
       const int kv0 = (tile_first + j) * BN + hsel * HK;  // this thread's first key of the tile
       const uint32_t tmem_s = tmem_s0 + (uint32_t)((j % NB) * BN);
@@ -277,95 +349,107 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight warps go on together
       if (abort_flag) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // keys this row sees in the tile: lo <= key <= hi (hi < lo: none).  A tile that every row of the
-      // CTA sees whole takes the plain path.
-      const bool need_mask = ((tile_first + j) * BN + BN - 1 > pos_first) || window > 0 || t_count < qt;
+      // keys this row sees in the tile: lo <= key <= hi (hi < lo: none)
       const int hi = row_ok ? qpos : -1;
       const int lo = window > 0 ? max(0, qpos - window + 1) : 0;
       const unsigned span = hi >= lo ? (unsigned)(hi - lo) : 0u;
       const int lo_eff = hi >= lo ? lo : 0x7fffff00;     // no key passes when the row sees nothing
-      // pass 1: the maximum of this thread's half of the row, then of the row
-      float mx = -INFINITY;
+      // Each chunk of 32 keys is, for all rows of the CTA alike: seen by no row (nothing is computed, its
+      // probabilities are 0), seen whole by every row (no mask; rows past the portion's end compute values
+      // that are never stored), or in between (masked key by key).
+      int cls[HK / 32];
 #pragma unroll
-      for (int c = 0; c < HK; c += 32) {
-        float v[32];
-        tmem_ld32(tmem_s + (uint32_t)c, v);
-        if (need_mask) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const bool seen = (unsigned)(kv0 + c + i - lo_eff) <= span;
-            mx = fmaxf(mx, seen ? v[i] : -INFINITY);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) mx = fmax3(mx, v[i], v[i + 1]);
-        }
+      for (int ci = 0; ci < HK / 32; ++ci) {
+        const int k0 = kv0 + ci * 32;
+        const bool none = k0 > pos_last || k0 + 31 < kv_lo;
+        const bool all = k0 + 31 <= pos_first && (window <= 0 || k0 >= pos_last - window + 1);
+        cls[ci] = none ? CHUNK_SKIP : all ? CHUNK_FAST : CHUNK_MASK;
       }
+      // the tile's scores -> (maximum) and/or (probabilities in tensor memory, their sums)
+      auto pass = [&](auto with_max, auto with_exp, bool wait_o, float neg_mc, float& mx, float2& lsum) {
+        constexpr bool WM = decltype(with_max)::value, WE = decltype(with_exp)::value;
+        float v[HK / 32][32];
+#pragma unroll
+        for (int ci = 0; ci < HK / 32; ++ci) tmem_ld32_nowait(tmem_s + (uint32_t)(ci * 32), v[ci]);
+        tmem_wait_ld();
+#pragma unroll
+        for (int ci = 0; ci < HK / 32; ++ci) {
+          tmem_ld_fence16(&v[ci][0]);
+          tmem_ld_fence16(&v[ci][16]);
+        }
+#pragma unroll
+        for (int ci = 0; ci < HK / 32; ++ci) {
+          uint32_t packed[16];
+          if (cls[ci] == CHUNK_FAST) {
+            softmax_chunk<false, WM, WE>(v[ci], 0, 0u, scale_log2, neg_mc, mx, lsum, packed);
+          } else if (cls[ci] == CHUNK_MASK) {
+            softmax_chunk<true, WM, WE>(v[ci], kv0 + ci * 32 - lo_eff, span, scale_log2, neg_mc, mx, lsum, packed);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) packed[i] = 0u;
+          }
+          if (WE) {
+            if (ci == 0 && wait_o) {
+              // the previous tile's P V must be done before its P is overwritten
+              mbar_wait(smem_addr(&o_ready), (uint32_t)(j - 1) & 1u, status, &abort_flag);
+              asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            tmem_st16_b32(tmem_p + (uint32_t)(ci * 16), packed);   // 32 keys = 16 columns of two bf16
+          }
+        }
+      };
+      using Yes = std::true_type;
+      using No = std::false_type;
+      const bool speculate = SPECULATE && j > 0;
+      float mx = -INFINITY;
+      float2 lsum = make_float2(0.f, 0.f);
+      if (speculate) {
+        pass(Yes{}, Yes{}, true, -(m == -INFINITY ? 0.f : m) * scale_log2, mx, lsum);
+      } else {
+        pass(Yes{}, No{}, false, 0.f, mx, lsum);
+      }
+      // the two warps of a row exchange their maxima: each arrives on its own barrier when its maximum is
+      // written and waits on the other's (two barriers of 64 threads per pair of warps); the stores of the
+      // probabilities complete meanwhile
       row_max[hsel][row] = mx;
-      asm volatile("bar.sync 2, 256;" ::: "memory");
+      asm volatile("bar.arrive %0, 64;" ::"r"(2 + 2 * quarter + hsel) : "memory");
+      if (speculate) tmem_wait_st();
+      asm volatile("bar.sync %0, 64;" ::"r"(2 + 2 * quarter + (hsel ^ 1)) : "memory");
       mx = fmaxf(mx, row_max[hsel ^ 1][row]);
       // The reference maximum moves only when the row's maximum has grown by more than 2^8 in the
       // exponent: until then the exponentials are taken against the old one (they stay below 256, exact
       // enough in fp32 and bf16, and the final division by the row's sum takes the common factor out),
       // and the output so far needs no rescaling, which is the usual case after a row's first tiles.
-      const float m_new = (m == -INFINITY || (mx - m) * scale_log2 > 8.0f) ? fmaxf(m, mx) : m;
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float corr = m == -INFINITY ? 0.f : fast_exp2((m - m_use) * scale_log2);
-      const float neg_mc = -m_use * scale_log2;
-      // the previous tile's P V must be done before P is overwritten and the output touched; the
-      // output so far is rescaled when some row of the warp saw its maximum move
-      if (j > 0) {
-        mbar_wait(smem_addr(&o_ready), (uint32_t)(j - 1) & 1u, status, &abort_flag);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (__any_sync(0xffffffffu, corr != 1.f)) {
+      const bool moves = mx > -INFINITY && (m == -INFINITY || (mx - m) * scale_log2 > 8.0f);
+      const float m_new = moves ? fmaxf(m, mx) : m;
+      if (!speculate || __any_sync(0xffffffffu, moves)) {
+        const float m_use = m_new == -INFINITY ? 0.f : m_new;
+        const float corr = m == -INFINITY ? 0.f : fast_exp2((m - m_use) * scale_log2);
+        // the output so far is rescaled when some row of the warp saw its maximum move
+        if (j > 0) {
+          if (!speculate) {
+            mbar_wait(smem_addr(&o_ready), (uint32_t)(j - 1) & 1u, status, &abort_flag);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          }
+          if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll
-          for (int c = 0; c < HD; c += 32) {
-            float v[32];
-            tmem_ld32(tmem_o + (uint32_t)c, v);
+            for (int c = 0; c < HD; c += 32) {
+              float v[32];
+              tmem_ld32(tmem_o + (uint32_t)c, v);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] *= corr;
-            tmem_st32(tmem_o + (uint32_t)c, v);
+              for (int i = 0; i < 32; ++i) v[i] *= corr;
+              tmem_st32(tmem_o + (uint32_t)c, v);
+            }
           }
         }
+        l *= corr;
+        lsum = make_float2(0.f, 0.f);
+        float unused = 0.f;
+        pass(No{}, Yes{}, false, -m_use * scale_log2, unused, lsum);
+        tmem_wait_st();
       }
       m = m_new;
-      l *= corr;
-      // pass 2: probabilities -> tensor memory (bf16 pairs: the A operand of the second product)
-      float l0 = 0.f, l1 = 0.f;
-#pragma unroll
-      for (int c = 0; c < HK; c += 32) {
-        float v[32];
-        tmem_ld32(tmem_s + (uint32_t)c, v);
-        uint32_t packed[16];
-        if (need_mask) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const bool s0 = (unsigned)(kv0 + c + i - lo_eff) <= span, s1 = (unsigned)(kv0 + c + i + 1 - lo_eff) <= span;
-            const float p0 = s0 ? fast_exp2(fmaf(v[i], scale_log2, neg_mc)) : 0.f;
-            const float p1 = s1 ? fast_exp2(fmaf(v[i + 1], scale_log2, neg_mc)) : 0.f;
-            l0 += p0;
-            l1 += p1;
-            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
-          }
-        } else {
-          float2 lsum = make_float2(l0, l1);
-          const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(neg_mc, neg_mc);
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float2 t = ffma2(make_float2(v[i], v[i + 1]), sc2, nm2);
-            const float2 pr = make_float2(fast_exp2(t.x), fast_exp2(t.y));
-            lsum = fadd2(lsum, pr);
-            __nv_bfloat162 h = __floats2bfloat162_rn(pr.x, pr.y);
-            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
-          }
-          l0 = lsum.x;
-          l1 = lsum.y;
-        }
-        tmem_st16_b32(tmem_p + (uint32_t)(c >> 1), packed);   // keys c .. c+31 = 16 columns of two bf16
-      }
-      l += l0 + l1;
-      tmem_wait_st();
+      l += lsum.x + lsum.y;
       // value rows of keys the request does not hold (a page's unwritten tail, a page that was not
       // read): zero them, so that probability 0 times a stale value never reaches the output
       const int tile0 = (tile_first + j) * BN;

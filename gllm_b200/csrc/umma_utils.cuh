@@ -187,3 +187,12 @@ static __device__ __forceinline__ void tmem_ld_fence16(float* v) {
 // One waited load of as many columns as the array holds (16 or 32).
 static __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, float (&v)[16]) { tmem_ld16(taddr, v); }
 static __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, float (&v)[32]) { tmem_ld32(taddr, v); }
+// One thread of a converged warp (every lane must call it).  Code under `if (elect_one())` is known to run in
+// one thread, so the operands of the tcgen05 instructions in it need no per-lane handling.
+static __device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
