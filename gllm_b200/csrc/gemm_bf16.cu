@@ -180,7 +180,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
+    // The whole warp runs the loop with warp-uniform values and waits on the barriers; one elected thread
+    // issues the products and their commits (in a branch that only lane 0 takes, a tcgen05.mma costs about
+    // 110 cycles to issue, whatever its size; this way about 40).
+    {
+      const bool leader = elect_one();
+      auto wait_u = [&](uint64_t* bar, uint32_t parity) -> bool {
+        const bool good = mbar_wait(smem_addr(bar), parity, status, &abort_flag);
+        return __all_sync(0xffffffffu, good) != 0;
+      };
       constexpr uint32_t idesc = umma_idesc(BM, BN);
       uint32_t it = 0, n_used = 0;                       // k-blocks consumed; accumulators handed over
       bool ok = true;
@@ -191,25 +199,29 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (kb_end <= kb_begin) continue;                // an empty K range: the epilogue writes zeros
         const uint32_t acc = n_used & 1u;
         // the epilogue must have drained this accumulator (two uses ago)
-        ok = mbar_wait(smem_addr(&tmem_empty_bar[acc]), ((n_used >> 1) & 1u) ^ 1u, status, &abort_flag);
+        ok = wait_u(&tmem_empty_bar[acc], ((n_used >> 1) & 1u) ^ 1u);
         if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const uint32_t s = it % S::STAGES;
-          ok = mbar_wait(smem_addr(&full_bar[s]), (it / S::STAGES) & 1u, status, &abort_flag);
+          ok = wait_u(&full_bar[s], (it / S::STAGES) & 1u);
           if (!ok) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = tile_base + s * S::STAGE;
-          const uint32_t b_addr = a_addr + S::STAGE_A;
+          const uint64_t a_desc = umma_desc(tile_base + s * S::STAGE);
+          const uint64_t b_desc = umma_desc(tile_base + s * S::STAGE + S::STAGE_A);
+          if (leader) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            umma_bf16(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
-                      (kb > kb_begin || k > 0) ? 1u : 0u);
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              // (a tile's address sits in the descriptor's low bits in units of 16 bytes)
+              umma_bf16(tmem_d, a_desc + (uint64_t)((k * UMMA_K * 2) >> 4), b_desc + (uint64_t)((k * UMMA_K * 2) >> 4), idesc,
+                        (kb > kb_begin || k > 0) ? 1u : 0u);
+            }
+            umma_commit(smem_addr(&empty_bar[s]));       // the stage is free once these MMAs have read it
           }
-          umma_commit(smem_addr(&empty_bar[s]));         // the stage is free once these MMAs have read it
+          __syncwarp();
         }
-        if (ok) umma_commit(smem_addr(&tmem_full_bar[acc]));   // the accumulator is complete
+        if (ok && leader) umma_commit(smem_addr(&tmem_full_bar[acc]));   // the accumulator is complete
+        __syncwarp();
         ++n_used;
       }
     }

@@ -169,30 +169,40 @@ umma_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer (first CTA only)
-    if (lane == 0 && rank == 0) {
+    // The whole warp runs the loop with warp-uniform values and waits on the barriers; one elected thread
+    // issues the products and their commits.
+    if (rank == 0) {
+      const bool leader = elect_one();
+      auto wait_u = [&](uint64_t* bar, uint32_t parity) -> bool {
+        const bool good = mbar_wait(smem_addr(bar), parity, status, &abort_flag);
+        return __all_sync(0xffffffffu, good) != 0;
+      };
       constexpr uint32_t idesc = umma_idesc(2 * BM, BN);
       uint32_t it = 0, n_used = 0;
       bool ok = true;
       for (int w = pair; w < num_items && ok; w += num_pairs) {
         const uint32_t acc = n_used & 1u;
-        ok = mbar_wait(smem_addr(&tmem_empty_bar[acc]), ((n_used >> 1) & 1u) ^ 1u, status, &abort_flag);
+        ok = wait_u(&tmem_empty_bar[acc], ((n_used >> 1) & 1u) ^ 1u);
         if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const uint32_t s = it % STAGES;
-          ok = mbar_wait(smem_addr(&full_bar[s]), (it / STAGES) & 1u, status, &abort_flag);
+          ok = wait_u(&full_bar[s], (it / STAGES) & 1u);
           if (!ok) break;
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_addr = tile_base + s * STAGE;
-          const uint32_t b_addr = a_addr + STAGE_A;
+          const uint64_t a_desc = umma_desc(tile_base + s * STAGE);
+          const uint64_t b_desc = umma_desc(tile_base + s * STAGE + STAGE_A);
+          if (leader) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_bf16_pair(tmem_d, umma_desc(a_addr + k * UMMA_K * 2), umma_desc(b_addr + k * UMMA_K * 2), idesc,
-                           (kb > 0 || k > 0) ? 1u : 0u);
-          umma_commit_pair(smem_addr(&empty_bar[s]));      // both CTAs' stages are free once these MMAs have read them
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              umma_bf16_pair(tmem_d, a_desc + (uint64_t)((k * UMMA_K * 2) >> 4), b_desc + (uint64_t)((k * UMMA_K * 2) >> 4),
+                             idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma_commit_pair(smem_addr(&empty_bar[s]));    // both CTAs' stages are free once these MMAs have read them
+          }
+          __syncwarp();
         }
-        if (ok) umma_commit_pair(smem_addr(&tmem_full_bar[acc]));
+        if (ok && leader) umma_commit_pair(smem_addr(&tmem_full_bar[acc]));
+        __syncwarp();
         ++n_used;
       }
     }
