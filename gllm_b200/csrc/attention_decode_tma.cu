@@ -187,9 +187,8 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap map_kv, const __nv_bflo
           const uint32_t bar = smem_addr(&full_bar[s]);
           const uint32_t stage = base + s * plan.stage_bytes;
           if (pass == 1 && round > 0) {
-            int go = 1;
-            if (lane == 0) go = mbar_wait(smem_addr(&empty_bar[s]), (round & 1u) ^ 1u, status, &abort_flag) ? 1 : 0;
-            ok = __shfl_sync(0xffffffffu, go, 0) != 0;
+            // (every lane waits: one waiting lane under a branch makes the wait several hundred cycles longer)
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_addr(&empty_bar[s]), (round & 1u) ^ 1u, status, &abort_flag)) != 0;
             if (!ok) break;
           }
           if (lane == 0 && (pass == 0 || round > 0))

@@ -223,14 +223,12 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int s = j % KS;
       const uint32_t full = smem_addr(plane ? &v_full[s] : &k_full[s]);
       const int n_present = __popc(__ballot_sync(0xffffffffu, page >= 0));
-      int ok = 1;
-      if (lane == 0) {
-        ok = mbar_wait(smem_addr(plane ? &v_empty[s] : &k_empty[s]), ((uint32_t)(j / KS) & 1u) ^ 1u, status, &abort_flag)
-                 ? 1 : 0;
-        if (ok) mbar_expect_tx(full, (uint32_t)n_present * page_bytes);
-      }
-      ok = __shfl_sync(0xffffffffu, ok, 0);             // also orders the expect before every lane's copies
+      // (every lane waits: one waiting lane under a branch makes the wait several hundred cycles longer)
+      const bool ok = __all_sync(0xffffffffu, mbar_wait(smem_addr(plane ? &v_empty[s] : &k_empty[s]),
+                                                        ((uint32_t)(j / KS) & 1u) ^ 1u, status, &abort_flag)) != 0;
       if (!ok) return false;
+      if (lane == 0) mbar_expect_tx(full, (uint32_t)n_present * page_bytes);
+      __syncwarp();                                     // the expectation is posted before any lane's copies
       if (page >= 0) {
         const int row0 = ((page * 2 + plane) * hkv + kvh) * block_size;
         const uint32_t dst = base + (plane ? S::OFF_V : S::OFF_K) + (uint32_t)(s * S::KV_STAGE + lane * block_size * 128);
