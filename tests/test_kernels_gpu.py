@@ -371,6 +371,52 @@ def test_attention_prefill_long_context(ops, kernel, d):
             off += nq
 
 
+@pytest.mark.parametrize("kernel", ["mma_sync", "tcgen05"])
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("trend", ["rising", "falling"])
+def test_attention_prefill_scores_with_a_trend(ops, kernel, d, trend):
+    """Scores that rise by about 8 nats from one tile of 128 keys to the next: every row's maximum outgrows
+    the reference it was exponentiated against in tile after tile (the tcgen05 kernel takes such a tile a
+    second time and rescales its output, which random scores never ask of it after a row's first tile).
+    Falling scores: the first keys keep all the weight and later tiles add almost nothing."""
+    from gllm_b200.ops import attention_bf16
+
+    g = torch.Generator().manual_seed(23)
+    hq, hkv, bs = 8, 2, 16
+    lens, q_counts = [700, 900], [700, 300]
+    pool, table, ks, vs, qs, pos, rows = _paged_case(g, torch.bfloat16, lens, hq, hkv, d, bs, q_counts)
+    u = torch.randn(d, generator=g)
+    u = u / u.norm()
+    scale = 1.0 / math.sqrt(d)
+    for r, n in enumerate(lens):
+        ramp = torch.arange(n, dtype=torch.float32) * (0.06 / scale)          # +7.7 nats per 128 keys
+        if trend == "falling":
+            ramp = ramp.flip(0)
+        ks[r] = (torch.randn(n, hkv, d, generator=g) * 0.5 + ramp[:, None, None] * u).to(torch.bfloat16)
+        qs[r] = (torch.randn(q_counts[r], hq, d, generator=g) * 0.5 + u).to(torch.bfloat16)
+        for b in range(-(-n // bs)):
+            chunk = slice(b * bs, min(n, (b + 1) * bs))
+            pool[table[r + 1, b], 0, :, : chunk.stop - chunk.start] = ks[r][chunk].transpose(0, 1)
+    pool = torch.cat([pool, torch.zeros(1, *pool.shape[1:], dtype=pool.dtype)], 0)
+    n = pos.numel()
+    qkv = torch.zeros(n, (hq + 2 * hkv) * d, dtype=torch.bfloat16)
+    qkv[:, : hq * d] = torch.cat(qs).reshape(n, hq * d)
+    cu = torch.tensor([0] + list(torch.tensor(q_counts).cumsum(0)), dtype=torch.int32).cuda()
+    ctx = torch.tensor([a - b for a, b in zip(lens, q_counts)], dtype=torch.int32).cuda()
+    slots = torch.arange(1, len(lens) + 1, dtype=torch.int32).cuda()
+    out = torch.full((n, hq * d), float("nan"), dtype=torch.bfloat16, device="cuda")
+    run = attention_bf16.prefill_attention if kernel == "mma_sync" else attention_bf16.prefill_attention_tmem
+    run(qkv.cuda(), qkv.shape[1], pool.cuda(), table.cuda(), cu, ctx, slots, len(lens), max(q_counts), hq, scale, 0, out)
+    ops.check_status()
+    off = 0
+    for r, nq in enumerate(q_counts):
+        want = _plain_attn(qs[r], ks[r], vs[r], pos[off:off + nq].long(), None, scale)
+        got = out[off:off + nq].double().cpu().view(nq, hq, d)
+        assert not got.isnan().any(), r
+        torch.testing.assert_close(got, want, **tol(torch.bfloat16))
+        off += nq
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 311, 72), (8, 3072, 2048), (7, 96, 160), (13, 2048, 8192), (33, 1000, 520),
                                    (64, 16384, 2048), (50, 130, 104), (3, 128256, 256), (65, 520, 200),
                                    (128, 256, 64), (300, 777, 1000), (2048, 3072, 2048), (1000, 16384, 2048)])
