@@ -16,6 +16,13 @@ Where the reference computes in the model dtype (norm statistics, softmax, the
 cos/sin table) this file computes in the dtype it is called with (float32 or
 float64): it is the exact-arithmetic meaning of the formulas, which the engine's
 fp32 path must match to rounding.
+
+``plain_forward(..., stored=torch.bfloat16)`` is the same arithmetic with every activation that a bfloat16
+model keeps between two operations rounded to bfloat16 where it is kept: the outputs of the norms, of the
+q/k/v projections, of the rotation, of the attention, and SiLU(gate) * up.  The residual stream, the
+statistics, the softmax and the logits stay in the dtype of the call.  It is what a bfloat16 engine
+computes up to the order of its sums, so a bfloat16 run can be held to a much closer bound than against
+the exact arithmetic.
 """
 
 from __future__ import annotations
@@ -90,7 +97,12 @@ def plain_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_positio
     return torch.einsum("hqk,khd->qhd", probs, v)
 
 
-def plain_attention_layer(x, w, prefix, cfg, positions, inv_freq, window, kv_from=None):
+def _kept(x: torch.Tensor, stored) -> torch.Tensor:
+    """x as it reads back after being kept in ``stored`` (None: kept as it is)."""
+    return x if stored is None else x.to(stored).to(x.dtype)
+
+
+def plain_attention_layer(x, w, prefix, cfg, positions, inv_freq, window, kv_from=None, stored=None):
     """q/k/v projections without bias (gllm/model/layers/attention.py:139-142),
     heads split along the feature axis (:145-148), rotation of q and k (:151),
     attention, output projection (:181-182).  Returns (out, (k, v)); with
@@ -98,28 +110,29 @@ def plain_attention_layer(x, w, prefix, cfg, positions, inv_freq, window, kv_fro
     hq, hkv = cfg["num_attention_heads"], cfg.get("num_key_value_heads", cfg["num_attention_heads"])
     d = cfg.get("head_dim") or cfg["hidden_size"] // hq
     t = x.shape[0]
-    q = (x @ w[f"{prefix}.q_proj.weight"].T).view(t, hq, d)
-    q = plain_rope(q, positions, inv_freq)
+    q = _kept(x @ w[f"{prefix}.q_proj.weight"].T, stored).view(t, hq, d)
+    q = _kept(plain_rope(q, positions, inv_freq), stored)
     if kv_from is None:
-        k = (x @ w[f"{prefix}.k_proj.weight"].T).view(t, hkv, d)
-        v = (x @ w[f"{prefix}.v_proj.weight"].T).view(t, hkv, d)
-        k = plain_rope(k, positions, inv_freq)
+        k = _kept(x @ w[f"{prefix}.k_proj.weight"].T, stored).view(t, hkv, d)
+        v = _kept(x @ w[f"{prefix}.v_proj.weight"].T, stored).view(t, hkv, d)
+        k = _kept(plain_rope(k, positions, inv_freq), stored)
     else:
         k, v = kv_from
-    o = plain_attention(q, k, v, positions, positions, window)
+    o = _kept(plain_attention(q, k, v, positions, positions, window), stored)
     return o.reshape(t, hq * d) @ w[f"{prefix}.o_proj.weight"].T, (k, v)
 
 
 # --------------------------------------------------------------- feed-forward
-def plain_mlp(x, w, prefix):
+def plain_mlp(x, w, prefix, stored=None):
     """down(silu(gate(x)) * up(x))  (gllm/model/layers/mlp.py:44-47)."""
     g = x @ w[f"{prefix}.gate_proj.weight"].T
     u = x @ w[f"{prefix}.up_proj.weight"].T
-    return (g * torch.sigmoid(g) * u) @ w[f"{prefix}.down_proj.weight"].T
+    return _kept(g * torch.sigmoid(g) * u, stored) @ w[f"{prefix}.down_proj.weight"].T
 
 
 # ---------------------------------------------------------------------- model
-def plain_forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, plan=None, rows=None) -> torch.Tensor:
+def plain_forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, plan=None, rows=None,
+                  stored=None) -> torch.Tensor:
     """Logits [T, V] of one whole sequence (with ``rows``: only at those positions, [len(rows), V];
     the sequence is still run whole).
 
@@ -129,7 +142,8 @@ def plain_forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, plan=No
     (gllm/model/model.py:228-239) or norm_f(x) W_head^T when the head is untied.
 
     ``plan``: list of (layer, reads_cache_of) in running order; default each
-    layer once in order.
+    layer once in order.  ``stored``: the dtype activations are kept in between operations (see the
+    head of this file); None keeps them in ``dtype``.
     """
     w = {k: v.to(dtype) for k, v in weights.items()}
     tokens = torch.as_tensor(tokens, dtype=torch.long)
@@ -146,16 +160,16 @@ def plain_forward(cfg: dict, weights: dict, tokens, dtype=torch.float64, plan=No
     for layer, reads in plan:
         p = f"model.layers.{layer}"
         window = cfg.get("sliding_window") if layer_types[layer] == "sliding_attention" else None
-        h = plain_rmsnorm(x, w[f"{p}.input_layernorm.weight"], eps)
+        h = _kept(plain_rmsnorm(x, w[f"{p}.input_layernorm.weight"], eps), stored)
         a, kv = plain_attention_layer(h, w, f"{p}.self_attn", cfg, positions, inv_freq, window,
-                                      kv_from=None if reads is None else kv_of_entry[reads])
+                                      kv_from=None if reads is None else kv_of_entry[reads], stored=stored)
         kv_of_entry.append(kv)
         x = x + a
-        h = plain_rmsnorm(x, w[f"{p}.post_attention_layernorm.weight"], eps)
-        x = x + plain_mlp(h, w, f"{p}.mlp")
+        h = _kept(plain_rmsnorm(x, w[f"{p}.post_attention_layernorm.weight"], eps), stored)
+        x = x + plain_mlp(h, w, f"{p}.mlp", stored=stored)
     if rows is not None:
         x = x[torch.as_tensor(rows, dtype=torch.long)]
-    x = plain_rmsnorm(x, w["model.norm.weight"], eps)
+    x = _kept(plain_rmsnorm(x, w["model.norm.weight"], eps), stored)
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else w["lm_head.weight"]
     return x @ head.T
 

@@ -82,6 +82,11 @@ LENGTHS = {"a": 150, "b": 97, "c": 64, "d": 33, "e": 210}
 FP32_TOL = 2e-4
 BF16_TOL_MAX = 5e-2
 BF16_TOL_MEAN = 1e-2
+# a bfloat16 run against the plain implementation that keeps its activations in bfloat16 where a bfloat16
+# model keeps them (plain_forward(..., stored=torch.bfloat16)): what is left is the order of the sums, the
+# bfloat16 probabilities of the tensor-core attention and the bfloat16 outputs of some products
+BF16_KEPT_TOL_MAX = 2e-2
+BF16_KEPT_TOL_MEAN = 2e-3
 
 
 def sequences(vocab: int, seed: int):
@@ -190,6 +195,8 @@ def compare(results, index, plain, tol_max, tol_mean=None):
         worst = max(worst, e)
         total += float(err.mean())
         count += 1
+    print(f"compare: worst {worst / scale:.2e}, mean {total / count / scale:.2e} of the scale {scale:.3g} "
+          f"(bounds {tol_max:.1e}, {tol_mean if tol_mean is not None else float('nan'):.1e})")
     if tol_mean is not None:
         assert total / count <= tol_mean * scale, f"mean error {total / count:.3e}"
     return worst

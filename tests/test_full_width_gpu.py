@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from plain_llama import plain_forward
-from replay_helpers import (BF16_TOL_MAX, BF16_TOL_MEAN, compare, mixed_steps, run_steps, sequences,
+from replay_helpers import (BF16_KEPT_TOL_MAX, BF16_KEPT_TOL_MEAN, BF16_TOL_MAX, BF16_TOL_MEAN, compare, mixed_steps, run_steps, sequences,
                             single_request_steps)
 
 pytestmark = pytest.mark.gpu
@@ -42,7 +42,8 @@ def full_width_sequences(full_width_model):
     folder, cfg, _, _, weights = full_width_model
     seqs = sequences(cfg["vocab_size"], seed=8)
     plain = {k: plain_forward(cfg, weights, v, torch.float32) for k, v in seqs.items()}
-    return seqs, plain
+    kept = {k: plain_forward(cfg, weights, v, torch.float32, stored=torch.bfloat16) for k, v in seqs.items()}
+    return seqs, plain, kept
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -54,9 +55,11 @@ def test_full_width_every_cut_against_the_plain_implementation(full_width_model,
     from gllm_b200.engine.replay import build_runner
 
     folder, cfg, _, _, _ = full_width_model
-    seqs, plain = full_width_sequences
-    # the plain side is float32 here (float64 over this vocabulary takes minutes on the CPU)
-    tol = (5e-4, None) if dtype == "float32" else (BF16_TOL_MAX, BF16_TOL_MEAN)
+    seqs, plain, kept = full_width_sequences
+    # the plain side is float32 here (float64 over this vocabulary takes minutes on the CPU); the bfloat16 run
+    # is held to the plain implementation that keeps its activations in bfloat16
+    tol = (5e-4, None) if dtype == "float32" else (BF16_KEPT_TOL_MAX, BF16_KEPT_TOL_MEAN)
+    plain = plain if dtype == "float32" else kept
     _, runner = build_runner(folder, dtype, max_tokens=448)
     steps, index = single_request_steps(seqs)
     compare(run_steps(runner, steps), index, plain, *tol)

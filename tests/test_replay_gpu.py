@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from plain_llama import plain_forward
-from replay_helpers import (BF16_TOL_MAX, BF16_TOL_MEAN, FP32_TOL, LENGTHS, compare, mixed_steps, replay, rounded,
+from replay_helpers import (BF16_KEPT_TOL_MAX, BF16_KEPT_TOL_MEAN, FP32_TOL, LENGTHS, compare, mixed_steps, replay, rounded,
                             run_steps, sequences, single_request_steps)
 from tiny_models import read_raw, write_tiny
 
@@ -24,8 +24,11 @@ def test_replay_all_cuts(name, dtype, tmp_path):
     cfg, weights = read_raw(folder, round_to_bf16=(dtype == "bfloat16"))
     vocab = cfg["vocab_size"]
     seqs = sequences(vocab, seed=5)
-    plain = {k: plain_forward(cfg, weights, v, torch.float64) for k, v in seqs.items()}
-    tol = (FP32_TOL, None) if dtype == "float32" else (BF16_TOL_MAX, BF16_TOL_MEAN)
+    # float32 against the exact arithmetic; bfloat16 against the same arithmetic with the activations kept in
+    # bfloat16, which a bfloat16 run follows five times closer than the exact one
+    stored = None if dtype == "float32" else torch.bfloat16
+    plain = {k: plain_forward(cfg, weights, v, torch.float64, stored=stored) for k, v in seqs.items()}
+    tol = (FP32_TOL, None) if dtype == "float32" else (BF16_KEPT_TOL_MAX, BF16_KEPT_TOL_MEAN)
 
     steps, index = single_request_steps(seqs)
     results = replay(folder, dtype, steps, str(tmp_path / "out1"), max_tokens=rounded(max(LENGTHS.values())), vocab=vocab,
@@ -56,7 +59,7 @@ def test_decoding_across_the_sequence_bucket_of_the_decode_graph(dtype, name, tm
     cfg, weights = read_raw(folder, round_to_bf16=(dtype == "bfloat16"))
     g = torch.Generator().manual_seed(21)
     toks = torch.randint(0, cfg["vocab_size"], (1040,), generator=g).tolist()
-    plain = {"x": plain_forward(cfg, weights, toks, torch.float64)}
+    plain = {"x": plain_forward(cfg, weights, toks, torch.float64, stored=None if dtype == "float32" else torch.bfloat16)}
     _, runner = build_runner(folder, dtype, max_tokens=2048, block_size=PAGE[name])
     steps = [{"step": 0, "entries": [{"id": "r", "tokens": toks[:1010], "want": [1009]}], "end": []}]
     index = [(0, 0, "x", 1009)]
@@ -64,7 +67,7 @@ def test_decoding_across_the_sequence_bucket_of_the_decode_graph(dtype, name, tm
         steps.append({"step": i + 1, "entries": [{"id": "r", "tokens": [toks[p]], "want": [0]}], "end": []})
         index.append((i + 1, 0, "x", p))
     results = run_steps(runner, steps)
-    tol = (FP32_TOL, None) if dtype == "float32" else (BF16_TOL_MAX, BF16_TOL_MEAN)
+    tol = (FP32_TOL, None) if dtype == "float32" else (BF16_KEPT_TOL_MAX, BF16_KEPT_TOL_MEAN)
     compare(results, index, plain, *tol)
     keys = [k for k in runner._graphs if k[0] == "decode"]
     assert {k[2] for k in keys} == {1024, 2048}, keys
@@ -84,11 +87,11 @@ def test_replay_through_the_stream_decode_kernel(tmp_path, monkeypatch, pair_gem
     cfg, weights = read_raw(folder, round_to_bf16=True)
     vocab = cfg["vocab_size"]
     seqs = sequences(vocab, seed=5)
-    plain = {k: plain_forward(cfg, weights, v, torch.float64) for k, v in seqs.items()}
+    plain = {k: plain_forward(cfg, weights, v, torch.float64, stored=torch.bfloat16) for k, v in seqs.items()}
     steps, index = single_request_steps(seqs)
     results = replay(folder, "bfloat16", steps, str(tmp_path / "out1"), max_tokens=rounded(max(LENGTHS.values())),
                      vocab=vocab)
-    compare(results, index, plain, BF16_TOL_MAX, BF16_TOL_MEAN)
+    compare(results, index, plain, BF16_KEPT_TOL_MAX, BF16_KEPT_TOL_MEAN)
     steps, index = mixed_steps(seqs, max_tokens=448, seed=9)
     results = replay(folder, "bfloat16", steps, str(tmp_path / "out2"), max_tokens=448, vocab=vocab)
-    compare(results, index, plain, BF16_TOL_MAX, BF16_TOL_MEAN)
+    compare(results, index, plain, BF16_KEPT_TOL_MAX, BF16_KEPT_TOL_MEAN)
