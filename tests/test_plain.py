@@ -165,6 +165,20 @@ def test_untied_head_and_plan(tmp_path):
     assert float((shared - base).abs().max()) > 1e-4
 
 
+def test_activations_kept_in_bfloat16(tmp_path):
+    """``stored``: keeping activations in the dtype of the call changes nothing; keeping them in bfloat16 moves
+    the logits by bfloat16 rounding (a part in a hundred at most here), not by more."""
+    folder = write_tiny("A", str(tmp_path / "m"))
+    cfg, w = read_raw(folder, round_to_bf16=True)
+    g = torch.Generator().manual_seed(3)
+    toks = torch.randint(0, cfg["vocab_size"], (40,), generator=g).tolist()
+    exact = plain_forward(cfg, w, toks)
+    assert torch.equal(plain_forward(cfg, w, toks, stored=torch.float64), exact)
+    kept = plain_forward(cfg, w, toks, stored=torch.bfloat16)
+    err = float((kept - exact).abs().max()) / float(exact.abs().max())
+    assert 1e-5 < err < 2e-2, err
+
+
 def test_sampler_distribution_rules():
     logits = torch.tensor([2.0, 1.0, 0.0, -1.0, 3.0])
     p, n = plain_sampling_distribution(logits, 1.0, 0, 1.0)
