@@ -18,6 +18,11 @@
 //           P (bf16) back into tensor memory, from where the second product takes it as its A
 //           operand; at the end O / sum -> global.
 //
+// A grid so small that twice as many CTAs still fit the GPU at once is launched as pairs of CTAs (clusters of
+// two) with the same rows: rows with ten key tiles or more have their tiles dealt out to the two CTAs in
+// turn, and the first merges the two (reference maximum, sum, output) through distributed shared memory
+// at the end; the chain of tiles, which bounds a small grid, is half as long.
+//
 // V is used as it lies in the cache ([key][dim], i.e. the "MN-major" operand of the second
 // product); nothing is transposed or gathered.  Keys outside a row's view get probability 0 and the
 // value rows that hold no key of the request are zeroed in shared memory before they are
@@ -130,7 +135,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     __nv_bfloat16* __restrict__ out, int64_t out_stride, const int* __restrict__ block_table,
                     int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ ctx_lens,
                     const int* __restrict__ slots, int hq, int hkv, int gp, int block_size, int num_pages,
-                    float scale_log2, int window, int* __restrict__ status) {
+                    float scale_log2, int window, int* __restrict__ status, int pair, int split_min) {
   using S = TShape<D>;
   constexpr int NB = S::NBUF;                            // score buffers in tensor memory
   constexpr int KS = S::KV_STAGES;                       // K (and V) stages in shared memory
@@ -149,8 +154,15 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int r = blockIdx.z;
   const int group = hq / hkv;
   const int tiles_per_kv = group / gp;
-  const int kvh = blockIdx.x / tiles_per_kv;
-  const int h0 = kvh * group + (blockIdx.x - kvh * tiles_per_kv) * gp;
+  // pair == 2: the kernel runs as clusters of two CTAs that have the same rows.  Where the rows have `split_min` key
+  // tiles or more, the CTA of rank k takes the tiles first + k, first + k + 2, .. and the first CTA merges the two
+  // results at the end (a small grid is bound by its longest chain of tiles); where they have fewer, the first
+  // CTA takes them all and the second leaves at once.
+  uint32_t rank = 0;
+  if (pair > 1) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int head_tile = (int)blockIdx.x / pair;
+  const int kvh = head_tile / tiles_per_kv;
+  const int h0 = kvh * group + (head_tile - kvh * tiles_per_kv) * gp;
   const int qt = BM / gp;                               // query tokens per CTA
 
   if (threadIdx.x == 0) {
@@ -181,15 +193,19 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
   const int tok_begin = cu_q[r], q_len = cu_q[r + 1] - tok_begin;
   const int n_qtiles = (q_len + qt - 1) / qt;
-  const bool active = (int)blockIdx.y < n_qtiles;       // uniform over the CTA
+  const bool has_rows = (int)blockIdx.y < n_qtiles;     // uniform over the CTA (and over the pair)
   const int qtile = n_qtiles - 1 - (int)blockIdx.y;     // longest rows first (y is the slower grid axis)
   const int t0 = qtile * qt;
-  const int t_count = active ? min(qt, q_len - t0) : 0;
+  const int t_count = has_rows ? min(qt, q_len - t0) : 0;
   const int ctx = ctx_lens[r];
   const int pos_first = ctx + t0, pos_last = ctx + t0 + t_count - 1;
   const int kv_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
   const int tile_first = kv_lo / BN, tile_last = pos_last / BN;
-  const int n_tiles = active ? tile_last - tile_first + 1 : 0;
+  const int n_all = has_rows ? tile_last - tile_first + 1 : 0;        // key tiles of these rows
+  const int nsplit = (pair > 1 && n_all >= split_min) ? 2 : 1;        // the same in both CTAs of a pair
+  const bool active = has_rows && (nsplit == 2 || rank == 0);
+  const int n_tiles = active ? (n_all - (int)rank + nsplit - 1) / nsplit : 0;   // this CTA's: tile_of(0), tile_of(1), ..
+  auto tile_of = [&](int j) { return tile_first + (int)rank + nsplit * j; };
 
   if (active && warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -199,7 +215,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int* bt = block_table + (int64_t)slots[r] * bt_stride;
     const int pages_per_tile = BN / block_size;
     const uint32_t page_bytes = (uint32_t)(S::DB * block_size * 128);
-    if (lane == 0) {
+    if (lane == 0 && n_tiles > 0) {
       mbar_expect_tx(smem_addr(&q_full), (uint32_t)S::Q_BYTES);
       for (int db = 0; db < S::DB; ++db)
         tma_load_3d(base + S::OFF_Q + db * S::TILE, &map_q, db * 64, h0, tok_begin + t0, smem_addr(&q_full));
@@ -207,7 +223,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // this lane's page of tile j (-1: nothing to read) and how many lanes have one
     auto lookup = [&](int j) -> int {
       int page = -1;
-      const int key = (tile_first + j) * BN + lane * block_size;
+      const int key = tile_of(j) * BN + lane * block_size;
       if (j < n_tiles && lane < pages_per_tile && key <= pos_last && key + block_size > kv_lo) {
         page = bt[key / block_size];
         if (page >= num_pages) {
@@ -289,7 +305,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // exponentiated.  One buffer: S(j+1) is issued as soon as the softmax has read S(j), BEFORE P(j) V(j),
       // so that the softmax of tile j+1 starts while that product still runs (it waits for it before it
       // overwrites P).
-      bool ok = wait_u(&q_full, 0u);
+      bool ok = n_tiles_u > 0 && wait_u(&q_full, 0u);     // (the second CTA of a pair may have no tile)
       if (ok) ok = wait_k(0) && issue_s(0);
       if (NB > 1 && ok && n_tiles_u > 1) ok = wait_k(1) && issue_s(1);
       for (int j = 0; j < n_tiles_u && ok; ++j) {
@@ -341,7 +357,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     constexpr bool SPECULATE = GLLM_PREFILL_SPECULATE;
     enum { CHUNK_SKIP = 0, CHUNK_FAST = 1, CHUNK_MASK = 2 };
     for (int j = 0; j < n_tiles; ++j) {
-      const int kv0 = (tile_first + j) * BN + hsel * HK;  // this thread's first key of the tile
+      const int kv0 = tile_of(j) * BN + hsel * HK;        // this thread's first key of the tile
       const uint32_t tmem_s = tmem_s0 + (uint32_t)((j % NB) * BN);
       mbar_wait(smem_addr(&s_full[j % NB]), (uint32_t)(j / NB) & 1u, status, &abort_flag);
       asm volatile("bar.sync 1, 256;" ::: "memory");     // the eight warps go on together
@@ -450,7 +466,7 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       l += lsum.x + lsum.y;
       // value rows of keys the request does not hold (a page's unwritten tail, a page that was not
       // read): zero them, so that probability 0 times a stale value never reaches the output
-      const int tile0 = (tile_first + j) * BN;
+      const int tile0 = tile_of(j) * BN;
       if (tile0 + BN - 1 > pos_last || tile0 < kv_lo) {
         mbar_wait(smem_addr(&v_full[j % KS]), (uint32_t)(j / KS) & 1u, status, &abort_flag);
         const int key = tile0 + row;                     // thread <-> key row of the V tile (lower-half warps)
@@ -469,34 +485,101 @@ prefill_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (lane == 0) mbar_arrive(smem_addr(&p_full));
     }
     // ---- O / l -> global: the row's sum is the two halves' sums
-    if (ok && n_tiles > 0) {
-      mbar_wait(smem_addr(&o_ready), (uint32_t)(n_tiles - 1) & 1u, status, &abort_flag);
-      row_max[hsel][row] = l;                            // (the exchange buffer is free: every maximum was read)
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (!abort_flag) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const float l_row = l + row_max[hsel ^ 1][row];
+    if (n_tiles > 0) mbar_wait(smem_addr(&o_ready), (uint32_t)(n_tiles - 1) & 1u, status, &abort_flag);
+    row_max[hsel][row] = l;                              // (the exchange buffer is free: every maximum was read)
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const float l_row = l + row_max[hsel ^ 1][row];
+    __nv_bfloat16* dst = out + (int64_t)(tok_begin + t0 + tl) * out_stride + (int64_t)(h0 + g) * D + hsel * HD;
+    auto store32 = [&](int c, const float (&v)[32], float inv) {
+      if (row_ok) {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 pk;
+          __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[q4 * 8 + 2 * i] * inv, v[q4 * 8 + 2 * i + 1] * inv);
+          *reinterpret_cast<uint4*>(dst + c + q4 * 8) = pk;
+        }
+      }
+    };
+    if (nsplit == 1) {
+      if (ok && n_tiles > 0 && !abort_flag) {
         const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
-        __nv_bfloat16* dst = out + (int64_t)(tok_begin + t0 + tl) * out_stride + (int64_t)(h0 + g) * D + hsel * HD;
 #pragma unroll 1
         for (int c = 0; c < HD; c += 32) {
           float v[32];
           tmem_ld32(tmem_o + (uint32_t)c, v);            // every lane takes part in the load
-          if (row_ok) {
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              uint4 pk;
-              __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                h[i] = __floats2bfloat162_rn(v[q4 * 8 + 2 * i] * inv, v[q4 * 8 + 2 * i + 1] * inv);
-              *reinterpret_cast<uint4*>(dst + c + q4 * 8) = pk;
-            }
-          }
+          store32(c, v, inv);
         }
       }
+    } else {
+      // The second CTA leaves its rows' reference maximum, sum and unnormalised output in its own shared memory
+      // (the K stages, free now: column-major, so that a warp's rows lie side by side); after the cluster's
+      // barrier the first CTA reads them there, brings both results to one reference and stores the rows; a
+      // second barrier keeps the second CTA's memory alive until it has.
+      float* xo = reinterpret_cast<float*>(base_ptr + S::OFF_K);
+      asm volatile("bar.sync 1, 256;" ::: "memory");     // every l was read: row_max carries m and l now
+      if (rank == 1) {
+        if (hsel == 0) {
+          row_max[0][row] = m;
+          row_max[1][row] = l_row;
+        }
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+          float v[32];
+          if (n_tiles > 0) {
+            tmem_ld32(tmem_o + (uint32_t)c, v);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) xo[(hsel * HD + c + i) * BM + row] = v[i];
+        }
+      }
+      asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+      if (rank == 0) {
+        uint32_t r_m, r_l, r_o;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, 1;" : "=r"(r_m) : "r"(smem_addr(&row_max[0][row])));
+        asm volatile("mapa.shared::cluster.u32 %0, %1, 1;" : "=r"(r_l) : "r"(smem_addr(&row_max[1][row])));
+        asm volatile("mapa.shared::cluster.u32 %0, %1, 1;" : "=r"(r_o) : "r"(base + S::OFF_K + (uint32_t)row * 4u));
+        float m1, l1;
+        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(m1) : "r"(r_m) : "memory");
+        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(l1) : "r"(r_l) : "memory");
+        // (this CTA has a tile whenever the rows have one; a row that saw nothing keeps m = -inf, l = 0)
+        const float mm = fmaxf(m, m1);
+        const float a0 = m == -INFINITY ? 0.f : fast_exp2((m - mm) * scale_log2);
+        const float a1 = m1 == -INFINITY ? 0.f : fast_exp2((m1 - mm) * scale_log2);
+        const float l_all = a0 * l_row + a1 * l1;
+        const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
+        const bool good = ok && !abort_flag;
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+          float v[32];
+          tmem_ld32(tmem_o + (uint32_t)c, v);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float o1;
+            asm volatile("ld.shared::cluster.f32 %0, [%1];"
+                         : "=f"(o1) : "r"(r_o + (uint32_t)((hsel * HD + c + i) * BM * 4)) : "memory");
+            v[i] = a0 * v[i] + a1 * o1;
+          }
+          if (good) store32(c, v, inv);
+        }
+      }
+      asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  }
+  if (active && nsplit > 1 && warp < 2) {
+    // the loading and the issuing warp take part in the cluster's two barriers
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
   }
   __syncthreads();
   if (warp == 1) {
@@ -564,9 +647,28 @@ int prefill_tmem_launch(const __nv_bfloat16* q, int64_t q_stride, __nv_bfloat16*
     attr_set = true;
   }
   dim3 grid(hkv * (group / gp), (max_q_len + qt - 1) / qt, num_requests);
+  // A small grid is bound by its longest CTA's chain of key tiles, not by the SMs' throughput.  Where twice the grid
+  // still fits the GPU at once (two CTAs per SM at head size 64), the kernel runs as pairs of CTAs; a pair whose rows
+  // have `split_min` key tiles or more shares them (the kernel decides from the lengths it reads on the device, so
+  // the launch depends on the step's sizes only).  Measured at head size 64: 512 tokens over 1,536 cached 35.8 -> 29.7 us,
+  // 256 over 3,840 58.4 -> 37.9 us; pairs that do not fit at once cost more than they give (1,024 tokens: 25.6 -> 35.8 us).
+  static int pair_on = -1, split_min = -1;
+  if (pair_on < 0) {
+    const char* e = getenv("GLLM_B200_PREFILL_PAIR");
+    pair_on = e ? atoi(e) : 1;
+    const char* m = getenv("GLLM_B200_PREFILL_SPLIT_MIN_TILES");
+    split_min = m ? atoi(m) : 10;
+  }
+  const int64_t places = (int64_t)gllm_sm_count() * S::CTAS_PER_SM;
+  if (pair_on && 2 * (int64_t)grid.x * grid.y * grid.z <= places) {
+    grid.x *= 2;
+    return gllm_launch_cluster(prefill_tmem_kernel<D>, grid, dim3(THREADS), (size_t)S::SMEM, stream, 2u, map_q, map_kv, out,
+                               out_stride, block_table, bt_stride, cu_q, ctx_lens, slots, hq, hkv, gp, block_size,
+                               num_pages, scale * 1.4426950408889634f, window, status, 2, split_min);
+  }
   return gllm_launch(prefill_tmem_kernel<D>, grid, dim3(THREADS), (size_t)S::SMEM, stream, map_q, map_kv, out,
                      out_stride, block_table, bt_stride, cu_q, ctx_lens, slots, hq, hkv, gp, block_size, num_pages,
-                     scale * 1.4426950408889634f, window, status);
+                     scale * 1.4426950408889634f, window, status, 1, split_min);
 }
 }  // namespace
 

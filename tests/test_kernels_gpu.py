@@ -378,12 +378,14 @@ def test_attention_prefill_scores_with_a_trend(ops, kernel, d, trend):
     """Scores that rise by about 8 nats from one tile of 128 keys to the next: every row's maximum outgrows
     the reference it was exponentiated against in tile after tile (the tcgen05 kernel takes such a tile a
     second time and rescales its output, which random scores never ask of it after a row's first tile).
-    Falling scores: the first keys keep all the weight and later tiles add almost nothing."""
+    Falling scores: the first keys keep all the weight and later tiles add almost nothing.  The first request
+    is long enough (12 key tiles) for the tcgen05 kernel to split its last rows' key tiles between two CTAs,
+    whose reference maxima then differ by dozens of nats when they are merged."""
     from gllm_b200.ops import attention_bf16
 
     g = torch.Generator().manual_seed(23)
     hq, hkv, bs = 8, 2, 16
-    lens, q_counts = [700, 900], [700, 300]
+    lens, q_counts = [1500, 900], [1500, 300]
     pool, table, ks, vs, qs, pos, rows = _paged_case(g, torch.bfloat16, lens, hq, hkv, d, bs, q_counts)
     u = torch.randn(d, generator=g)
     u = u / u.norm()
