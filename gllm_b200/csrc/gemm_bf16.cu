@@ -488,11 +488,16 @@ int umma_launch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int M
                      reduce_in_kernel, status, accumulate);
 }
 
-// Width of the weight tile for more than 64 tokens: 256 rows, or 64 for a single tile of tokens
-// (65 .. 128) times a narrow weight, where 256 would leave most SMs without a tile: more tiles, and
-// less to write and read back where the product is cut along K as well.
+// Width of the weight tile for more than 64 tokens: 256 rows; 64 for a single tile of tokens (65 .. 128) times a
+// narrow weight, where 256 would leave most SMs without a tile (more tiles, and less to write and read back where
+// the product is cut along K as well); 128 for 129 .. 512 tokens, and for up to 256 tokens of the gated product:
+// twice the work items of half the size, each with a longer range of K (measured alone, 256 -> 128 wide: q/k/v at
+// 256 tokens 23.6 -> 17.4 us, o 19.5 -> 15.4, down 25.6 -> 23.6, gate/up at 128 tokens 35.8 -> 27.7; from 768 tokens on
+// the wide tile wins again: gate/up 58 against 65 us).
 static int normal_tile_rows(int M, int N, bool gated) {
-  return (!gated && M <= BM && (N + 255) / 256 < 64) ? 64 : 256;   // measured: wider is quicker from 129 tokens on
+  if (gated) return M <= 256 ? 128 : 256;
+  if (M <= BM) return (N + 255) / 256 < 64 ? 64 : 256;
+  return M <= 512 ? 128 : 256;
 }
 
 template <typename OutT, bool GATED>
@@ -506,6 +511,7 @@ int umma_dispatch(const __nv_bfloat16* X, const __nv_bfloat16* W, OutT* out, int
   if (M <= 32) GLLM_UMMA(32, true);
   if (M <= 64) GLLM_UMMA(64, true);
   if (normal_tile_rows(M, N, GATED) == 64) GLLM_UMMA(64, false);
+  if (normal_tile_rows(M, N, GATED) == 128) GLLM_UMMA(128, false);
   GLLM_UMMA(256, false);
 #undef GLLM_UMMA
 }
