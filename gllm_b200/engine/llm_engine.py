@@ -130,7 +130,7 @@ class LLMEngine(LLMEngineBase):
         else:
             raise ValueError("a request needs prompt or prompt_token_ids")
         vocab = self.config.vocab_size
-        if any(t < 0 or t >= vocab for t in prompt):
+        if prompt and not (0 <= min(prompt) and max(prompt) < vocab):
             raise ValueError(f"a prompt token id lies outside the vocabulary of {vocab}")
         stop = set(int(t) for t in req.stop_token_ids)
         if not req.ignore_eos:
