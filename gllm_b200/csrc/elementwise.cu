@@ -162,6 +162,91 @@ GLLM_API int gllm_scale_softcap_f32(float* x, int64_t n, float scale, float cap,
                      x, n, scale, cap);
 }
 
+// ------------------------------------------------------------ bias of a product
+// x[r][c] += bias[c], in place, the sum rounded to T (a projection with a bias: the reference has none,
+// gllm/model/layers/linear.py:20; other architectures do).
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ x, int64_t stride, const float* __restrict__ bias, int rows, int n) {
+  pdl_trigger();
+  pdl_wait();
+  for (int r = blockIdx.y; r < rows; r += gridDim.y) {
+    T* row = x + (int64_t)r * stride;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < n; c += gridDim.x * blockDim.x)
+      row[c] = from_float<T>(to_float(row[c]) + bias[c]);
+  }
+}
+template <typename T>
+static int add_bias_launch(T* x, int64_t stride, const float* bias, int rows, int n, cudaStream_t stream) {
+  if (rows <= 0 || n <= 0) return 0;
+  const int bx = (n + 255) / 256;
+  return gllm_launch(add_bias_kernel<T>, dim3(bx < 64 ? bx : 64, rows < 4096 ? rows : 4096), dim3(256), 0, stream, x,
+                     stride, bias, rows, n);
+}
+GLLM_API int gllm_add_bias_f32(float* x, int64_t stride, const float* bias, int rows, int n, cudaStream_t stream) {
+  return add_bias_launch<float>(x, stride, bias, rows, n, stream);
+}
+GLLM_API int gllm_add_bias_bf16(__nv_bfloat16* x, int64_t stride, const float* bias, int rows, int n,
+                                cudaStream_t stream) {
+  return add_bias_launch<__nv_bfloat16>(x, stride, bias, rows, n, stream);
+}
+
+// ------------------------------------------------------- RMSNorm of every head
+// Heads first_head .. first_head + n_heads - 1 of every row of x (a row is heads of d columns side by side): each
+// head's d values are divided by sqrt(mean of their squares + eps) and multiplied by weight[0 .. d) (or 1 + weight),
+// in place; statistics in fp32.  One warp per (row, head); d up to 256.  (A norm of the queries and the keys before
+// the rotation: the reference has none; other architectures do.)
+template <typename T>
+__global__ void rmsnorm_heads_kernel(T* __restrict__ x, int64_t stride, const float* __restrict__ weight, int rows,
+                                     int first_head, int n_heads, int d, float eps, int unit_offset) {
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  float w[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int c = lane + 32 * k;
+    w[k] = c < d ? (unit_offset ? 1.0f + weight[c] : weight[c]) : 0.f;
+  }
+  pdl_wait();
+  if (item >= (int64_t)rows * n_heads) return;
+  const int r = (int)(item / n_heads), h = (int)(item - (int64_t)r * n_heads);
+  T* v = x + (int64_t)r * stride + (int64_t)(first_head + h) * d;
+  float a[8], ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int c = lane + 32 * k;
+    a[k] = c < d ? to_float(v[c]) : 0.f;
+    ss += a[k] * a[k];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int c = lane + 32 * k;
+    if (c < d) v[c] = from_float<T>(a[k] * inv * w[k]);
+  }
+}
+template <typename T>
+static int rmsnorm_heads_launch(T* x, int64_t stride, const float* weight, int rows, int first_head, int n_heads, int d,
+                                float eps, int unit_offset, cudaStream_t stream) {
+  if (rows <= 0 || n_heads <= 0) return 0;
+  if (d <= 0 || d > 256 || first_head < 0) return (int)cudaErrorInvalidValue;
+  const int64_t items = (int64_t)rows * n_heads;
+  const int64_t blocks = (items + 7) / 8;                 // eight warps a block
+  if (blocks > 0x7fffffff) return (int)cudaErrorInvalidValue;
+  return gllm_launch(rmsnorm_heads_kernel<T>, dim3((unsigned)blocks), dim3(256), 0, stream, x, stride, weight, rows,
+                     first_head, n_heads, d, eps, unit_offset);
+}
+GLLM_API int gllm_rmsnorm_heads_f32(float* x, int64_t stride, const float* weight, int rows, int first_head, int n_heads,
+                                    int d, float eps, int unit_offset, cudaStream_t stream) {
+  return rmsnorm_heads_launch<float>(x, stride, weight, rows, first_head, n_heads, d, eps, unit_offset, stream);
+}
+GLLM_API int gllm_rmsnorm_heads_bf16(__nv_bfloat16* x, int64_t stride, const float* weight, int rows, int first_head,
+                                     int n_heads, int d, float eps, int unit_offset, cudaStream_t stream) {
+  return rmsnorm_heads_launch<__nv_bfloat16>(x, stride, weight, rows, first_head, n_heads, d, eps, unit_offset, stream);
+}
+
 // ------------------------------------------------------ add + RMSNorm (fused)
 // For output row i (source row r = rows ? rows[i] : i):
 //   x = resid[r] (+ branch[r])            fp32

@@ -39,6 +39,8 @@ __all__ = [
     "as_tensor",
     "linear_gated",
     "interleave_gate_up",
+    "add_bias",
+    "rmsnorm_heads",
 ]
 
 P = c_void_p
@@ -47,6 +49,8 @@ _SIGNATURES = {
         "gllm_embedding_{t}": [P, P, P, P, P, c_int, c_int, c_int, c_float, P, P],
         "gllm_scale_softcap_f32": [P, c_int64, c_float, c_float, P],
         "gllm_scatter_i32": [P, c_int64, P, P, c_int, P, P],
+        "gllm_add_bias_{t}": [P, c_int64, P, c_int, c_int, P],
+        "gllm_rmsnorm_heads_{t}": [P, c_int64, P, c_int, c_int, c_int, c_int, c_float, c_int, P],
         "gllm_add_rmsnorm_{t}": [P, P, c_int, c_int64, P, P, P, P, c_int, c_int, c_float, c_int, P],
         "gllm_sum_parts_{t}": [P, c_int, c_int64, P, c_int64, P],
         "gllm_silu_mul_{t}": [P, P, c_int, c_int, c_int, P],
@@ -316,6 +320,36 @@ def scale_softcap(logits: torch.Tensor, scale: float = 1.0, cap: float | None = 
     return logits
 
 
+# ------------------------------------------------- bias, norm of every head
+def add_bias(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """``x[r] += bias`` in place (``bias`` fp32, one value per column): the bias of a projection.  The
+    reference's projections have none (gllm/model/layers/linear.py:20)."""
+    _cuda(x, "x", contiguous=False)
+    _cuda(bias, "bias", torch.float32)
+    if x.dim() != 2 or x.stride(1) != 1 or bias.numel() != x.shape[1]:
+        raise ValueError("add_bias takes rows of contiguous columns and one bias value per column")
+    f = _fn("elementwise", f"gllm_add_bias_{_suffix(x.dtype)}")
+    _check(f(x.data_ptr(), x.stride(0), bias.data_ptr(), x.shape[0], x.shape[1], _stream()), "add_bias")
+    return x
+
+
+def rmsnorm_heads(x: torch.Tensor, weight: torch.Tensor, eps: float, first_head: int, num_heads: int, head_dim: int,
+                  unit_offset: bool = False) -> torch.Tensor:
+    """RMSNorm of each of ``num_heads`` heads of ``head_dim`` columns, from head ``first_head`` on, of every row
+    of ``x``, in place, with one weight of ``head_dim`` values for all of them; statistics in fp32.  (A norm of
+    the queries and keys before their rotation; the reference has none.)"""
+    _cuda(x, "x", contiguous=False)
+    _cuda(weight, "weight", torch.float32)
+    if x.dim() != 2 or x.stride(1) != 1 or (first_head + num_heads) * head_dim > x.shape[1]:
+        raise ValueError("the heads do not lie inside the rows of x")
+    if weight.numel() != head_dim or head_dim > 256:
+        raise ValueError("rmsnorm_heads takes one weight value per column of a head, for heads of up to 256 columns")
+    f = _fn("elementwise", f"gllm_rmsnorm_heads_{_suffix(x.dtype)}")
+    _check(f(x.data_ptr(), x.stride(0), weight.data_ptr(), x.shape[0], int(first_head), int(num_heads), int(head_dim),
+             float(eps), int(unit_offset), _stream()), "rmsnorm_heads")
+    return x
+
+
 # ------------------------------------------------------------- add + RMSNorm
 def add_rmsnorm(
     branch: torch.Tensor | None,
@@ -457,14 +491,18 @@ ACCUMULATE_IN_PRODUCT = os.environ.get("GLLM_B200_FUSE_ADD", "1") != "0"
 
 
 def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None,
-           out: torch.Tensor | None = None, split_ok: bool = False, add_into: torch.Tensor | None = None):
+           out: torch.Tensor | None = None, split_ok: bool = False, add_into: torch.Tensor | None = None,
+           bias: torch.Tensor | None = None):
     """``x @ weight.T`` with ``weight`` stored ``[out, in]``
     (gllm/model/layers/linear.py:20).  fp32 inputs run the FFMA kernel (no
     tensor-core mode); bf16 inputs run the tensor-core kernels with fp32
     accumulation.  With ``split_ok`` the result may be a SplitSum (for callers
     that hand it to ``add_rmsnorm`` or ``rope_store``).  With ``add_into``
     (fp32 ``[m, n]``, the residual stream) the product may add itself there
-    and return ``ADDED``; when it returns anything else, nothing was added."""
+    and return ``ADDED``; when it returns anything else, nothing was added.  With ``bias`` (fp32, one
+    value per output column) the result is an ordinary tensor with the bias added."""
+    if bias is not None:
+        return add_bias(linear(x, weight, out_dtype=out_dtype, out=out), bias)
     _cuda(x, "x")
     _cuda(weight, "weight", x.dtype)
     m, k = x.shape

@@ -598,3 +598,27 @@ def test_gemm_that_adds_itself_into_the_residual(ops, m, n, k):
     acc2 = torch.zeros(65, n).cuda()
     out = ops.linear(x2, w, split_ok=True, add_into=acc2)
     assert out is not ops.ADDED and float(acc2.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_bias_and_norm_of_every_head(ops, dtype):
+    """``add_bias`` on a strided view, and ``rmsnorm_heads`` on some of the heads of each row (head sizes that
+    are no multiple of 32 among them), against their formulas in float64."""
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(37, 200, generator=g).to(dtype)
+    bias = torch.randn(120, generator=g)
+    xd = x.cuda()
+    view = xd[:, 40:160]
+    ops.add_bias(view, bias.cuda())
+    want = x.double()
+    want[:, 40:160] += bias.double()
+    torch.testing.assert_close(xd.double().cpu(), want.to(dtype).double(), **tol(dtype))
+    for d, heads, first, n, unit in [(64, 5, 0, 3, False), (48, 6, 2, 4, True), (16, 9, 8, 1, False), (256, 2, 1, 1, False)]:
+        y = torch.randn(11, heads * d, generator=g).to(dtype)
+        wgt = torch.randn(d, generator=g)
+        yd = y.cuda()
+        ops.rmsnorm_heads(yd, wgt.cuda(), 1e-5, first, n, d, unit_offset=unit)
+        z = y.double().view(11, heads, d).clone()
+        part = z[:, first:first + n]
+        z[:, first:first + n] = part / torch.sqrt((part * part).mean(-1, keepdim=True) + 1e-5) * ((1.0 + wgt.double()) if unit else wgt.double())
+        torch.testing.assert_close(yd.double().cpu().view(11, heads, d), z.to(dtype).double(), **tol(dtype))

@@ -210,3 +210,119 @@ def test_an_unsummed_product_read_too_late_raises():
     ops.linear(x, w, split_ok=True)
     with pytest.raises(RuntimeError, match="overwritten"):
         first.tensor()
+
+
+# ------------------------------------------------------------------------------------------------
+# Attention with biased projections and a norm of every query and key head before the rotation: options of the
+# built-in attention part that Llama does not use, through a toy architecture registered from here.
+QK_EPS = 1e-6
+
+
+def register_biased():
+    from gllm_b200.config import register_architecture
+    from gllm_b200.config.model_config import ModelConfig
+    from gllm_b200.models.spec import LayerSpec, ModelSpec, PartSpec, PlanEntry
+
+    @dataclass(frozen=True)
+    class BiasedConfig(ModelConfig):
+        intermediate_size: int = 0
+        num_heads: int = 0
+        num_kv_heads: int = 0
+        head_dim: int = 0
+        num_layers: int = 0
+        eps: float = 1e-5
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(architecture=d["architectures"][0], vocab_size=d["vocab_size"], hidden_size=d["hidden_size"],
+                       dtype=d["torch_dtype"], eos_token_ids=(), intermediate_size=d["intermediate_size"],
+                       num_heads=d["num_heads"], num_kv_heads=d["num_kv_heads"], head_dim=d["head_dim"],
+                       num_layers=d["num_layers"], eps=d["eps"])
+
+        def to_dict(self):
+            return dict(architectures=[self.architecture], vocab_size=self.vocab_size, hidden_size=self.hidden_size,
+                        torch_dtype=self.dtype, intermediate_size=self.intermediate_size, num_heads=self.num_heads,
+                        num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, num_layers=self.num_layers, eps=self.eps)
+
+    def build_spec(cfg):
+        h = cfg.hidden_size
+        norm = lambda name: PartSpec("rmsnorm", dict(size=h, eps=cfg.eps), {"weight": name})
+
+        def layer(i):
+            p = f"layers.{i}"
+            names = {n: f"{p}.attn.{n}.weight" for n in "qkvo"}
+            names.update({f"{n}_bias": f"{p}.attn.{n}.bias" for n in "qkvo"})
+            names.update({"q_norm": f"{p}.attn.q_norm.weight", "k_norm": f"{p}.attn.k_norm.weight"})
+            attn = PartSpec("attention", dict(hidden_size=h, num_heads=cfg.num_heads, num_kv_heads=cfg.num_kv_heads,
+                                              head_dim=cfg.head_dim, bias=True, output_bias=True, qk_norm_eps=QK_EPS,
+                                              position=PartSpec("rotary", dict(head_dim=cfg.head_dim, theta=10000.0))),
+                            names)
+            ffn = PartSpec("swiglu", dict(hidden_size=h, intermediate_size=cfg.intermediate_size),
+                           {n: f"{p}.mlp.{n}_proj.weight" for n in ("gate", "up", "down")})
+            return LayerSpec("prenorm", dict(mixer_norm=norm(f"{p}.n1.weight"), mixer=attn,
+                                             feed_forward_norm=norm(f"{p}.n2.weight"), feed_forward=ffn))
+
+        return ModelSpec(hidden_size=h, vocab_size=cfg.vocab_size, layers=tuple(layer(i) for i in range(cfg.num_layers)),
+                         plan=tuple(PlanEntry(i) for i in range(cfg.num_layers)), final_norm=norm("norm.weight"),
+                         embedding_name="embed.weight", head_name="head.weight")
+
+    register_architecture("ToyBiasedLM", BiasedConfig, build_spec)
+
+
+def plain_biased_forward(cfg, w, tokens):
+    """Whole sequence, float64, no cache: q = norm_head(W_q x + b_q), k likewise, v = W_v x + b_v, rotation,
+    attention, W_o a + b_o."""
+    from plain_llama import plain_attention, plain_rope
+
+    w = {k: v.double() for k, v in w.items()}
+    x = w["embed.weight"][torch.tensor(tokens)]
+    t = x.shape[0]
+    hq, hkv, d = cfg["num_heads"], cfg["num_kv_heads"], cfg["head_dim"]
+    pos = torch.arange(t)
+    inv_freq = plain_inverse_frequencies(dict(head_dim=d, rope_theta=10000.0, hidden_size=cfg["hidden_size"],
+                                              num_attention_heads=hq))
+    head_norm = lambda z, g: z / torch.sqrt((z * z).mean(-1, keepdim=True) + QK_EPS) * g
+    for i in range(cfg["num_layers"]):
+        p = f"layers.{i}"
+        h = plain_rmsnorm(x, w[f"{p}.n1.weight"], cfg["eps"])
+        q = (h @ w[f"{p}.attn.q.weight"].T + w[f"{p}.attn.q.bias"]).view(t, hq, d)
+        k = (h @ w[f"{p}.attn.k.weight"].T + w[f"{p}.attn.k.bias"]).view(t, hkv, d)
+        v = (h @ w[f"{p}.attn.v.weight"].T + w[f"{p}.attn.v.bias"]).view(t, hkv, d)
+        q = plain_rope(head_norm(q, w[f"{p}.attn.q_norm.weight"]), pos, inv_freq)
+        k = plain_rope(head_norm(k, w[f"{p}.attn.k_norm.weight"]), pos, inv_freq)
+        a = plain_attention(q, k, v, pos, pos).reshape(t, hq * d)
+        x = x + a @ w[f"{p}.attn.o.weight"].T + w[f"{p}.attn.o.bias"]
+        h = plain_rmsnorm(x, w[f"{p}.n2.weight"], cfg["eps"])
+        x = x + plain_mlp(h, w, f"{p}.mlp")
+    return plain_rmsnorm(x, w["norm.weight"], cfg["eps"]) @ w["head.weight"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads,kv_heads,head_dim", [(4, 2, 64), (3, 1, 48)])
+def test_attention_with_biases_and_a_norm_of_every_head(dtype, heads, kv_heads, head_dim, tmp_path):
+    from safetensors.torch import load_file
+
+    from gllm_b200.config import ARCHITECTURES, load_config
+    from gllm_b200.engine.replay import build_runner
+    from gllm_b200.weights import write_random_model
+
+    register_biased()
+    try:
+        raw = dict(architectures=["ToyBiasedLM"], vocab_size=300, hidden_size=96, torch_dtype="bfloat16",
+                   intermediate_size=128, num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, num_layers=2,
+                   eps=1e-5)
+        # vectors (norm weights and biases alike) are drawn around one: biases that are far from zero
+        folder = write_random_model(str(tmp_path / "toy"), load_config(raw), seed=11, std=0.08, norm_jitter=0.3)
+        weights = {k: v.float() for k, v in load_file(f"{folder}/model.safetensors").items()}
+        assert float(weights["layers.0.attn.q.bias"].abs().min()) > 0.0
+        _, runner = build_runner(folder, dtype, max_tokens=448, block_size=16)
+        seqs = sequences(300, seed=4)
+        plain = {k: plain_biased_forward(raw, weights, v) for k, v in seqs.items()}
+        tol = (FP32_TOL, None) if dtype == "float32" else (BF16_TOL_MAX, BF16_TOL_MEAN)
+        steps, index = single_request_steps(seqs)
+        compare(run_steps(runner, steps), index, plain, *tol)
+        steps, index = mixed_steps(seqs, max_tokens=448, seed=9)
+        compare(run_steps(runner, steps), index, plain, *tol)
+        assert runner.graph_replays > 0
+    finally:
+        ARCHITECTURES.pop("ToyBiasedLM", None)
