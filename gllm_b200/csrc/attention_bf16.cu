@@ -48,11 +48,14 @@ decode_split_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride,
   __shared__ float red_m[W][ROWS], red_l[W][ROWS];
 
   pdl_trigger();
-  const int split = blockIdx.x;
+  // chunk-major: all (request, kv head) pairs of chunk 0 come first, and the chunks past every request's end (the
+  // grid is sized for the longest sequence of the step's bucket) come last: 0.913 -> 0.900 ms per decode step at
+  // batch 8, 0.780 -> 0.765 at batch 1, against the chunks of one request side by side
+  const int split = blockIdx.y;
   const int group = hq / hkv;
   const int head_tiles = (group + ROWS - 1) / ROWS;
-  const int kvh = blockIdx.y / head_tiles, tile_idx = blockIdx.y - kvh * head_tiles;
-  const int n = blockIdx.z;
+  const int n = (int)blockIdx.x / (hkv * head_tiles), by = (int)blockIdx.x - n * (hkv * head_tiles);
+  const int kvh = by / head_tiles, tile_idx = by - kvh * head_tiles;
   const int h0 = kvh * group + tile_idx * ROWS;
   const int heads = min(ROWS, group - tile_idx * ROWS);
 
@@ -307,7 +310,7 @@ int decode_launch(const __nv_bfloat16* q, int64_t q_stride, __nv_bfloat16* out, 
     cudaError_t e = cudaFuncSetAttribute(decode_split_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
     if (e != cudaSuccess) return (int)e;
   }
-  dim3 grid(num_chunks, hkv * head_tiles, num_queries);
+  dim3 grid((unsigned)(hkv * head_tiles * num_queries), num_chunks);
   int e = gllm_launch(decode_split_kernel<D>, grid, dim3(S::W * 32), (size_t)S::SMEM, stream, q, q_stride, cache,
                       block_table, bt_stride, positions, token_row, part_o, part_ml, hq, hkv, block_size, num_pages,
                       num_chunks, scale * 1.4426950408889634f, window, status);
@@ -338,7 +341,7 @@ GLLM_API int gllm_attention_decode_bf16(const __nv_bfloat16* q, int64_t q_stride
                                         int block_size, int num_pages, int num_chunks, float scale, int window,
                                         int* status, cudaStream_t stream) {
   if (num_queries <= 0) return 0;
-  if (hq <= 0 || hkv <= 0 || hq % hkv || num_chunks <= 0 || num_queries > 65535 || (q_stride % 8) ||
+  if (hq <= 0 || hkv <= 0 || hq % hkv || num_chunks <= 0 || num_chunks > 65535 || num_queries > 65535 || (q_stride % 8) ||
       ((block_size * d) % 8))
     return (int)cudaErrorInvalidValue;
 #define GLLM_DEC_D(DD)                                                                                         \
