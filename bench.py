@@ -176,10 +176,10 @@ def drain(engine, states):
 
 
 # Untimed decode steps between a repetition's prefill and its warm-up steps: the prefill of the batch
-# (16k tokens at batch 8) runs the GPU into its power cap, and the decode steps right after it run at
-# the lowered clock (1.09 ms a step instead of 0.96 for about thirty steps); a decode benchmark measures
-# the state decoding settles in.
-SETTLE_STEPS = 48
+# (16k tokens at batch 8) runs the GPU into its power cap, and the decode steps after it run at the
+# lowered clock for a while (measured in groups of 20 steps after the prefill: 0.917, 0.914, 0.905, 0.897 ms
+# a step, then 0.893 from the eightieth step on); a decode benchmark measures the state decoding settles in.
+SETTLE_STEPS = 96
 
 
 def time_decode(engine, batch: int, context: int, steps: int, warmup: int, reps: int = 5):
