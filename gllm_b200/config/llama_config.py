@@ -53,6 +53,11 @@ class LlamaConfig(ModelConfig):
     # and which layers use it ("full_attention" | "sliding_attention").
     sliding_window: int | None = None
     layer_types: tuple[str, ...] = field(default_factory=tuple)
+    # Biases on the four attention projections / on the three feed-forward projections.  False in every
+    # Llama 3.x checkpoint and not read by the reference (gllm/model/layers/attention.py:139-142,
+    # gllm/model/layers/mlp.py:44-47 multiply by the weights only).
+    attention_bias: bool = False
+    mlp_bias: bool = False
 
     @classmethod
     def from_dict(cls, d: dict[str, Any]) -> "LlamaConfig":
@@ -80,8 +85,8 @@ class LlamaConfig(ModelConfig):
             # gllm/model/layers/mlp.py:38-41 accepts only silu as well.
             raise ConfigError(f"hidden_act {act!r} is not supported (only 'silu')")
         for bias_key in ("attention_bias", "mlp_bias"):
-            if d.get(bias_key):
-                raise ConfigError(f"{bias_key}=true is not supported: the projections have no bias")
+            if not isinstance(d.get(bias_key, False), bool):
+                raise ConfigError(f"{bias_key} must be true or false")
         dtype_name = d.get("torch_dtype", d.get("dtype", "bfloat16"))
         if dtype_name not in DTYPE_NAMES:
             raise ConfigError(f"torch_dtype {dtype_name!r} is not one of {sorted(DTYPE_NAMES)}")
@@ -147,6 +152,8 @@ class LlamaConfig(ModelConfig):
             bos_token_id=d.get("bos_token_id"),
             sliding_window=None if window is None else int(window),
             layer_types=layer_types,
+            attention_bias=bool(d.get("attention_bias", False)),
+            mlp_bias=bool(d.get("mlp_bias", False)),
         )
 
     def to_dict(self) -> dict[str, Any]:
@@ -168,8 +175,8 @@ class LlamaConfig(ModelConfig):
             "tie_word_embeddings": self.tie_word_embeddings,
             "torch_dtype": self.dtype,
             "eos_token_id": list(self.eos_token_ids),
-            "attention_bias": False,
-            "mlp_bias": False,
+            "attention_bias": self.attention_bias,
+            "mlp_bias": self.mlp_bias,
         }
         if self.max_position_embeddings is not None:
             d["max_position_embeddings"] = self.max_position_embeddings

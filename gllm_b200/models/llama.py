@@ -42,21 +42,20 @@ def build_llama_spec(cfg: LlamaConfig) -> ModelSpec:
                 head_dim=cfg.head_dim,
                 position=rope,
                 window=cfg.sliding_window if sliding else None,
+                bias=cfg.attention_bias,
+                output_bias=cfg.attention_bias,
             ),
             {
-                "q": f"{p}.self_attn.q_proj.weight",
-                "k": f"{p}.self_attn.k_proj.weight",
-                "v": f"{p}.self_attn.v_proj.weight",
-                "o": f"{p}.self_attn.o_proj.weight",
+                **{n: f"{p}.self_attn.{n}_proj.weight" for n in "qkvo"},
+                **({f"{n}_bias": f"{p}.self_attn.{n}_proj.bias" for n in "qkvo"} if cfg.attention_bias else {}),
             },
         )
         ffn = PartSpec(
             "swiglu",
-            dict(hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size),
+            dict(hidden_size=cfg.hidden_size, intermediate_size=cfg.intermediate_size, bias=cfg.mlp_bias),
             {
-                "gate": f"{p}.mlp.gate_proj.weight",
-                "up": f"{p}.mlp.up_proj.weight",
-                "down": f"{p}.mlp.down_proj.weight",
+                **{n: f"{p}.mlp.{n}_proj.weight" for n in ("gate", "up", "down")},
+                **({f"{n}_bias": f"{p}.mlp.{n}_proj.bias" for n in ("gate", "up", "down")} if cfg.mlp_bias else {}),
             },
         )
         norm = dict(size=cfg.hidden_size, eps=cfg.rms_norm_eps)

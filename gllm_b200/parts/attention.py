@@ -76,11 +76,11 @@ class Attention(Mixer):
             self.names["o"]: TensorExpectation((self.hidden_size, qd)),
         }
         if self.bias:
-            exp[self.names["q_bias"]] = TensorExpectation((qd,), "vector")
-            exp[self.names["k_bias"]] = TensorExpectation((kd,), "vector")
-            exp[self.names["v_bias"]] = TensorExpectation((kd,), "vector")
+            exp[self.names["q_bias"]] = TensorExpectation((qd,), "bias")
+            exp[self.names["k_bias"]] = TensorExpectation((kd,), "bias")
+            exp[self.names["v_bias"]] = TensorExpectation((kd,), "bias")
         if self.output_bias:
-            exp[self.names["o_bias"]] = TensorExpectation((self.hidden_size,), "vector")
+            exp[self.names["o_bias"]] = TensorExpectation((self.hidden_size,), "bias")
         if self.qk_norm_eps is not None:
             exp[self.names["q_norm"]] = TensorExpectation((self.head_dim,), "vector")
             exp[self.names["k_norm"]] = TensorExpectation((self.head_dim,), "vector")
@@ -93,9 +93,9 @@ class Attention(Mixer):
         self.w_qkv = torch.cat([q, k, v], dim=0).contiguous()
         self.w_o = get(self.names["o"], "matrix").contiguous()
         if self.bias:
-            self.b_qkv = torch.cat([get(self.names[n], "vector") for n in ("q_bias", "k_bias", "v_bias")]).contiguous()
+            self.b_qkv = torch.cat([get(self.names[n], "bias") for n in ("q_bias", "k_bias", "v_bias")]).contiguous()
         if self.output_bias:
-            self.b_o = get(self.names["o_bias"], "vector").contiguous()
+            self.b_o = get(self.names["o_bias"], "bias").contiguous()
         if self.qk_norm_eps is not None:
             self.w_q_norm = get(self.names["q_norm"], "vector").contiguous()
             self.w_k_norm = get(self.names["k_norm"], "vector").contiguous()

@@ -34,7 +34,8 @@ class TensorExpectation:
 
     role "matrix": operand of a matrix product or an embedding table, held in
     the compute dtype.  "vector": small per-channel tensor (norm weight), held
-    in fp32 whatever the compute dtype is.  "int_table": integer table, int32.
+    in fp32 whatever the compute dtype is.  "bias": the bias of a projection, held in fp32
+    as well (random weights draw it around zero, a vector around one).  "int_table": integer table, int32.
     """
 
     shape: tuple[int, ...]

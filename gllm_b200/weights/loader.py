@@ -100,7 +100,7 @@ class Checkpoint:
 
         def get(name: str, role: str = "matrix") -> torch.Tensor:
             t = self.tensor(name)
-            if role == "vector":
+            if role in ("vector", "bias"):
                 t = t.to(torch.float32)
             elif role == "int_table":
                 t = t.to(torch.int32)

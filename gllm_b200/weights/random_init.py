@@ -46,7 +46,7 @@ def random_tensors(
             t = torch.ones(exp.shape, dtype=torch.float32)
             if norm_jitter:
                 t = t + torch.randn(exp.shape, generator=gen, dtype=torch.float32) * norm_jitter
-        elif exp.role == "matrix":
+        elif exp.role in ("matrix", "bias"):
             s = std
             for pattern, value in (std_overrides or {}).items():
                 if pattern in name:

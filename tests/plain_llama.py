@@ -102,6 +102,13 @@ def _kept(x: torch.Tensor, stored) -> torch.Tensor:
     return x if stored is None else x.to(stored).to(x.dtype)
 
 
+def _proj(x, w, name):
+    """x W^T, plus the bias ``<name>.bias`` where the checkpoint has one (``attention_bias`` / ``mlp_bias`` in
+    config.json; the reference's projections have none, gllm/model/layers/linear.py:20)."""
+    y = x @ w[f"{name}.weight"].T
+    return y + w[f"{name}.bias"] if f"{name}.bias" in w else y
+
+
 def plain_attention_layer(x, w, prefix, cfg, positions, inv_freq, window, kv_from=None, stored=None):
     """q/k/v projections without bias (gllm/model/layers/attention.py:139-142),
     heads split along the feature axis (:145-148), rotation of q and k (:151),
@@ -110,24 +117,24 @@ def plain_attention_layer(x, w, prefix, cfg, positions, inv_freq, window, kv_fro
     hq, hkv = cfg["num_attention_heads"], cfg.get("num_key_value_heads", cfg["num_attention_heads"])
     d = cfg.get("head_dim") or cfg["hidden_size"] // hq
     t = x.shape[0]
-    q = _kept(x @ w[f"{prefix}.q_proj.weight"].T, stored).view(t, hq, d)
+    q = _kept(_proj(x, w, f"{prefix}.q_proj"), stored).view(t, hq, d)
     q = _kept(plain_rope(q, positions, inv_freq), stored)
     if kv_from is None:
-        k = _kept(x @ w[f"{prefix}.k_proj.weight"].T, stored).view(t, hkv, d)
-        v = _kept(x @ w[f"{prefix}.v_proj.weight"].T, stored).view(t, hkv, d)
+        k = _kept(_proj(x, w, f"{prefix}.k_proj"), stored).view(t, hkv, d)
+        v = _kept(_proj(x, w, f"{prefix}.v_proj"), stored).view(t, hkv, d)
         k = _kept(plain_rope(k, positions, inv_freq), stored)
     else:
         k, v = kv_from
     o = _kept(plain_attention(q, k, v, positions, positions, window), stored)
-    return o.reshape(t, hq * d) @ w[f"{prefix}.o_proj.weight"].T, (k, v)
+    return _proj(o.reshape(t, hq * d), w, f"{prefix}.o_proj"), (k, v)
 
 
 # --------------------------------------------------------------- feed-forward
 def plain_mlp(x, w, prefix, stored=None):
     """down(silu(gate(x)) * up(x))  (gllm/model/layers/mlp.py:44-47)."""
-    g = x @ w[f"{prefix}.gate_proj.weight"].T
-    u = x @ w[f"{prefix}.up_proj.weight"].T
-    return _kept(g * torch.sigmoid(g) * u, stored) @ w[f"{prefix}.down_proj.weight"].T
+    g = _proj(x, w, f"{prefix}.gate_proj")
+    u = _proj(x, w, f"{prefix}.up_proj")
+    return _proj(_kept(g * torch.sigmoid(g) * u, stored), w, f"{prefix}.down_proj")
 
 
 # ---------------------------------------------------------------------- model

@@ -43,13 +43,29 @@ def test_defaults_and_window():
     assert load_config(only_window).layer_types == ("sliding_attention",) * 2
 
 
+def test_bias_keys_are_read_and_written_back(tmp_path):
+    """``attention_bias`` / ``mlp_bias``: false where absent (every Llama 3.x checkpoint), carried through
+    ``to_dict``, and the random-weights mode writes the bias tensors the keys ask for and no others."""
+    from safetensors.torch import load_file
+
+    from gllm_b200.weights import write_random_model
+
+    assert not load_config(dict(TINY_A)).attention_bias and not load_config(dict(TINY_A)).mlp_bias
+    c = load_config(dict(TINY_C))
+    assert c.attention_bias and not c.mlp_bias
+    assert load_config(c.to_dict()) == c
+    names = set(load_file(write_random_model(str(tmp_path / "m"), c, seed=1) + "/model.safetensors"))
+    assert "model.layers.0.self_attn.o_proj.bias" in names and "model.layers.2.self_attn.k_proj.bias" in names
+    assert not any("mlp" in n and n.endswith(".bias") for n in names)
+
+
 @pytest.mark.parametrize("change,match", [
     (dict(hidden_size=None), "hidden_size"),
     (dict(rms_norm_eps=None), "rms_norm_eps"),
     (dict(vocab_size=None), "vocab_size"),
     (dict(num_key_value_heads=3), "multiple"),
     (dict(hidden_act="gelu"), "hidden_act"),
-    (dict(attention_bias=True), "attention_bias"),
+    (dict(attention_bias="yes"), "attention_bias"),
     (dict(torch_dtype="float16"), "torch_dtype"),
     (dict(rope_scaling=dict(rope_type="yarn", factor=2.0)), "rope_scaling"),
     (dict(rope_scaling=dict(rope_type="llama3", factor=2.0)), "low_freq_factor"),

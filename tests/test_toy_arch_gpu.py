@@ -311,7 +311,6 @@ def test_attention_with_biases_and_a_norm_of_every_head(dtype, heads, kv_heads, 
         raw = dict(architectures=["ToyBiasedLM"], vocab_size=300, hidden_size=96, torch_dtype="bfloat16",
                    intermediate_size=128, num_heads=heads, num_kv_heads=kv_heads, head_dim=head_dim, num_layers=2,
                    eps=1e-5)
-        # vectors (norm weights and biases alike) are drawn around one: biases that are far from zero
         folder = write_random_model(str(tmp_path / "toy"), load_config(raw), seed=11, std=0.08, norm_jitter=0.3)
         weights = {k: v.float() for k, v in load_file(f"{folder}/model.safetensors").items()}
         assert float(weights["layers.0.attn.q.bias"].abs().min()) > 0.0

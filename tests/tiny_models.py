@@ -32,13 +32,13 @@ TINY_C = dict(
     architectures=["LlamaForCausalLM"], hidden_size=72, head_dim=16, intermediate_size=104, hidden_act="silu",
     num_hidden_layers=3, num_attention_heads=5, num_key_value_heads=5, rms_norm_eps=3e-5, eos_token_id=[1, 2],
     torch_dtype="bfloat16", rope_theta=30000.0, vocab_size=311, tie_word_embeddings=True,
-    sliding_window=24, layer_types=["full_attention", "sliding_attention", "full_attention"],
+    sliding_window=24, layer_types=["full_attention", "sliding_attention", "full_attention"], attention_bias=True,
 )
 TINY_D = dict(
     architectures=["LlamaForCausalLM"], hidden_size=128, head_dim=64, intermediate_size=200, hidden_act="silu",
     num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1, rms_norm_eps=1e-5, eos_token_id=[0],
     torch_dtype="bfloat16", rope_theta=10000.0, vocab_size=500, tie_word_embeddings=True,
-    sliding_window=40, layer_types=["sliding_attention", "full_attention"],
+    sliding_window=40, layer_types=["sliding_attention", "full_attention"], mlp_bias=True,
 )
 TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 # how each one's random weights are drawn
